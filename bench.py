@@ -1,0 +1,380 @@
+#!/usr/bin/env python
+"""Benchmark of the KLA scan hot path on B200: forward + backward of the fused
+scan at the headline raw-op workload (B=8, T=4096, M=1024, S=16, float32).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One "step" is one forward + one backward pass of the scan over one batch of
+synthetic input. With N > 1 (launched under torch.distributed.run) every rank
+scans its own batch shard of the same size -- lanes are independent over
+(batch, channel), so there is no data-path collective -- and the value is the
+total over ranks divided by the slowest rank's time (weak scaling).
+
+Prints ONE JSON line (rank 0). ``--impl reference`` times the CPU oracle (a
+port of the reference's sequential float32 scan and its adjoint) on the host
+cores instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# The workload: BASELINE config 2, "raw op pair, fp32".
+WORK = dict(B=8, L=4096, M=1024, S=16)
+METRIC = "KLA scan fwd+bwd tokens/s"
+UNIT = "tokens/s"
+
+
+def algorithmic_bytes_per_token(M, S, esz=4):
+    """Compulsory HBM bytes of the fused op per (b, t) token: forward reads v,
+    lambda_v (2M) and k, q (2S) and writes y, y_var (2M); backward reads dy,
+    dyvar, v, lambda_v (4M) and k, q (2S) and writes dv, dlambda_v (2M) and dk,
+    dq (2S). Checkpoints, re-reads and anything [B,L,M,S]-shaped are overhead."""
+    fwd = esz * (4 * M + 2 * S)
+    bwd = esz * (6 * M + 4 * S)
+    return fwd, bwd
+
+
+# ncu-measured DRAM traffic per launch at the bench workload (bytes), copied
+# from the summaries under profiles/; None until a capture exists.
+NCU_TRAFFIC = {"kla_bwd_kernel": None, "kla_fwd_kernel": None}
+
+
+def make_inputs(seed=0, **w):
+    """Seeded synthetic inputs with the coefficient distributions the workload
+    names: a = sigmoid(N(0,1)), p = softplus(N(0,1)), lambda_v = 1/softplus(N(0,1)),
+    v ~ N(0,1), l2-normalised k, q ~ N(0,1) (as the reference layer does with
+    qk_norm); upstream gradients ~ N(0,1) from seed+1."""
+    import torch
+    import torch.nn.functional as F
+
+    B, L, M, S = w["B"], w["L"], w["M"], w["S"]
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    v = torch.randn(B, L, M, generator=g)
+    lambda_v = 1.0 / F.softplus(torch.randn(B, L, M, generator=g))
+    k = torch.randn(B, L, S, generator=g)
+    q = torch.randn(B, L, S, generator=g)
+    k = k / k.norm(dim=-1, keepdim=True)
+    q = q / q.norm(dim=-1, keepdim=True)
+    a = torch.sigmoid(torch.randn(M, S, generator=g))
+    p = F.softplus(torch.randn(M, S, generator=g))
+    g1 = torch.Generator(device="cpu").manual_seed(seed + 1)
+    dy = torch.randn(B, L, M, generator=g1)
+    dyvar = torch.randn(B, L, M, generator=g1)
+    return dict(v=v, lambda_v=lambda_v, k=k, q=q, a=a, p=p, dy=dy, dyvar=dyvar)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.gpu)],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for n, val in zip(names, f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(n)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            sm.sort()
+            out.update(sm_mhz=sm[len(sm) // 2], sm_max_mhz=max(mx), samples=len(sm))
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def cpu_oracle_run(sample, threads=None):
+    """Time the CPU oracle (float32, forward + backward) on `sample`; returns
+    (tokens_per_s_at_full_width, seconds, threads). The sample keeps B*L tokens
+    but may hold fewer channels than the workload: lanes are independent over
+    channels, so cost is linear in M and the rate is scaled by M_sample/M."""
+    import numpy as np
+
+    from oracle import kla_oracle as O
+
+    ins = make_inputs(**sample)
+    arr = {n: t.numpy() for n, t in ins.items()}
+    t0 = time.perf_counter()
+    O.scan_fwd(arr["v"], arr["lambda_v"], arr["k"], arr["q"], arr["a"], arr["p"], dtype=np.float32)
+    O.scan_bwd(arr["v"], arr["lambda_v"], arr["k"], arr["q"], arr["a"], arr["p"], arr["dy"], arr["dyvar"],
+               dtype=np.float32)
+    dt = time.perf_counter() - t0
+    tokens = sample["B"] * sample["L"] * (sample["M"] / WORK["M"])
+    return tokens / dt, dt, int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+
+
+def run_reference(args):
+    """The reference arm: the reference's CPU algorithm (oracle port, float32,
+    OpenMP over channels) on the host cores, same workload definition."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    # bounded sample: one batch element, all T, a channel block; calibrate its width
+    sample = dict(B=1, L=WORK["L"], M=64, S=WORK["S"])
+    rate, dt, _ = cpu_oracle_run(sample)
+    # aim at ~5 s of CPU work per step: widen the channel block, then the batch
+    units = max(1.0, 5.0 / max(dt, 1e-3))  # in 64-channel blocks of one batch element
+    sample["M"] = int(min(WORK["M"], 64 * round(units)))
+    sample["B"] = int(min(WORK["B"], max(1, round(units * 64 / WORK["M"]))))
+    for _ in range(max(args.warmup, 1) if args.warmup else 0):
+        cpu_oracle_run(sample)
+    times, rates = [], []
+    for _ in range(args.steps):
+        r, dt, _ = cpu_oracle_run(sample)
+        rates.append(r)
+        times.append(dt)
+    tot_tokens = sample["B"] * sample["L"] * (sample["M"] / WORK["M"]) * args.steps
+    value = tot_tokens / sum(times)
+    desc = (f"B={sample['B']} x T={sample['L']} x M={sample['M']} of {WORK['M']} channels x S={sample['S']} per step, "
+            f"rate scaled by M/{WORK['M']} (lanes independent over channels)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "raw KLA scan fwd+bwd, B=8 T=4096 M=1024 S=16, fp32 (CPU: bounded sample)", **WORK},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    import kla_b200
+    lib = __import__("importlib").import_module("kalman-linear-attention_b200._lib")
+    L = lib.load()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU fallback)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    B, T, M, S = WORK["B"], WORK["L"], WORK["M"], WORK["S"]
+    host = make_inputs(seed=rank, **WORK)
+    d = {n: t.to(dev) for n, t in host.items()}
+    # preallocated outputs and scratch: the C-ABI allocates nothing
+    f32 = dict(device=dev, dtype=torch.float32)
+    y, y_var = torch.empty(B, T, M, **f32), torch.empty(B, T, M, **f32)
+    lam_fin, eta_fin = torch.empty(B, M, S, **f32), torch.empty(B, M, S, **f32)
+    ckpt = torch.empty(L.kla_b200_ckpt_bytes(B, T, M, S), device=dev, dtype=torch.uint8)
+    dv, dlv = torch.empty(B, T, M, **f32), torch.empty(B, T, M, **f32)
+    dk, dq = torch.empty(B, T, S, **f32), torch.empty(B, T, S, **f32)
+    da, dp = torch.empty(M, S, **f32), torch.empty(M, S, **f32)
+    dlam0, deta0 = torch.empty(B, M, S, **f32), torch.empty(B, M, S, **f32)
+
+    def t3(t):
+        return lib.Tensor3(t.data_ptr(), t.stride(0), t.stride(1))
+
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    fa = lib.FwdArgs(B=B, L=T, M=M, S=S, in_dtype=0, out_dtype=0, decode_from_prior=0,
+                     v=t3(d["v"]), lambda_v=t3(d["lambda_v"]), k=t3(d["k"]), q=t3(d["q"]),
+                     a=P(d["a"]), p=P(d["p"]), lam0=None, eta0=None, y=t3(y), y_var=t3(y_var),
+                     lam_fin=P(lam_fin), eta_fin=P(eta_fin), ckpt=P(ckpt))
+    ba = lib.BwdArgs(B=B, L=T, M=M, S=S, in_dtype=0, out_dtype=0, decode_from_prior=0,
+                     v=t3(d["v"]), lambda_v=t3(d["lambda_v"]), k=t3(d["k"]), q=t3(d["q"]),
+                     a=P(d["a"]), p=P(d["p"]), lam0=None, eta0=None, ckpt=P(ckpt),
+                     dy=t3(d["dy"]), dy_var=t3(d["dyvar"]), dlam_fin=None, deta_fin=None,
+                     dv=t3(dv), dlambda_v=t3(dlv), dk=P(dk), dq=P(dq), da=P(da), dp=P(dp),
+                     dlam0=P(dlam0), deta0=P(deta0))
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+    def step():
+        lib.check(L.kla_b200_scan_fwd(ctypes.byref(fa), stream))
+        lib.check(L.kla_b200_scan_bwd(ctypes.byref(ba), stream))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+
+    # ---- device-resident timing: K steps, CUDA events on the launching stream.
+    # Inputs and gradients (4 x 134 MB read per step, 4 x 134 MB written) exceed
+    # the 126 MB L2, so no explicit flush is needed between iterations.
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
+    launches0 = L.kla_b200_launch_count()
+    barrier()
+    ev[0].record()
+    for i in range(args.steps):
+        lib.check(L.kla_b200_scan_fwd(ctypes.byref(fa), stream))
+        ev[2 * i + 1].record()
+        lib.check(L.kla_b200_scan_bwd(ctypes.byref(ba), stream))
+        ev[2 * i + 2].record()
+    barrier()
+    launches = L.kla_b200_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = ev[0].elapsed_time(ev[-1])
+    fwd_ms = sum(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(args.steps)) / args.steps
+    bwd_ms = sum(ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(args.steps)) / args.steps
+
+    # ---- end to end through the public API with HOST buffers: pinned inputs
+    # copied in, kla_scan_b200 + autograd, every result copied back out.
+    pin = {n: t.pin_memory() for n, t in host.items()}
+    outs_host = None
+    e2e_steps = max(1, min(args.steps, 5))
+
+    def e2e_step():
+        nonlocal outs_host
+        g = {n: t.to(dev, non_blocking=True) for n, t in pin.items()}
+        ins = [g[n].requires_grad_(True) for n in ("v", "lambda_v", "k", "q", "a", "p")]
+        yy, yv, _ = kla_b200.kla_scan_b200(*ins)
+        grads = torch.autograd.grad([yy, yv], ins, [g["dy"], g["dyvar"]])
+        res = [yy, yv, *grads]
+        if outs_host is None:
+            outs_host = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in res]
+        for h, t in zip(outs_host, res):
+            h.copy_(t.detach(), non_blocking=True)
+        return res
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    h2d = sum(t.numel() * t.element_size() for t in pin.values())
+    d2h = sum(t.numel() * t.element_size() for t in outs_host)
+
+    # ---- max over ranks
+    tm = torch.tensor([total_ms, fwd_ms, bwd_ms, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+    total_ms, fwd_ms, bwd_ms, e2e_ms = tm.tolist()
+    tokens_step = B * T * world
+    value = tokens_step * args.steps / (total_ms * 1e-3)
+    e2e_value = tokens_step / (e2e_ms * 1e-3)
+
+    if rank == 0:
+        peak, peak_src = peaks()
+        fb, bb = algorithmic_bytes_per_token(M, S)
+        bwd_bytes, fwd_bytes = bb * B * T, fb * B * T
+        ach_bwd = bwd_bytes / (bwd_ms * 1e-3) / 1e9
+        ach_fwd = fwd_bytes / (fwd_ms * 1e-3) / 1e9
+        ach_step = (fwd_bytes + bwd_bytes) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "raw KLA scan fwd+bwd, B=8 T=4096 M=1024 S=16 per GPU, fp32 I/O and state",
+                       **WORK, "sharding": "batch shard per rank, no collective",
+                       "l2": "inputs+outputs per step (1.1 GB) exceed the 126 MB L2; no explicit flush"},
+            "roofline": {"bound": "hbm", "kernel": "kla_bwd_kernel", "achieved": ach_bwd, "peak": peak,
+                         "unit": "GB/s", "frac": ach_bwd / peak, "traffic": NCU_TRAFFIC["kla_bwd_kernel"],
+                         "peak_source": peak_src, "algorithmic_bytes": bwd_bytes, "ms": bwd_ms,
+                         "nominal_peak_gbs": 8000.0, "frac_of_nominal": ach_bwd / 8000.0},
+            "roofline_fwd": {"bound": "hbm", "kernel": "kla_fwd_kernel", "achieved": ach_fwd, "peak": peak,
+                             "unit": "GB/s", "frac": ach_fwd / peak, "traffic": NCU_TRAFFIC["kla_fwd_kernel"],
+                             "algorithmic_bytes": fwd_bytes, "ms": fwd_ms},
+            "roofline_step": {"achieved": ach_step, "peak": peak, "unit": "GB/s", "frac": ach_step / peak},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            sample = dict(B=1, L=T, M=128, S=S)
+            rate, dt, cores = cpu_oracle_run(sample)
+            if dt < 3.0:  # grow the sample towards ~10 s of CPU work
+                sample["M"] = int(min(M, 128 * max(1, round(8.0 / max(dt, 1e-3)))))
+                rate, dt, cores = cpu_oracle_run(sample)
+            line["cpu_baseline"] = {
+                "value": rate, "unit": UNIT, "cores": cores, "kind": "port",
+                "sample": f"B=1 x T={T} x M={sample['M']} of {M} channels x S={S}, float32 oracle fwd+bwd, "
+                          f"{dt:.1f} s; rate scaled by M/{M} (lanes independent over channels)"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,155 @@
+/*
+ * kla_b200.h -- C ABI of the B200 (sm_100a) backend for the Kalman Linear
+ * Attention scan.
+ *
+ * The library replaces one path of the reference package `kla`: the fused scan
+ * `kla.ops.kla_scan` (forward and backward) and the single-token decode step
+ * `kla.ops.kla_step`. Every entry point takes plain device pointers, sizes and
+ * element strides; none takes or returns a torch type; none allocates device
+ * memory (the caller owns outputs and scratch); none throws. All work is
+ * enqueued on the CUDA stream passed in (`stream` is a `cudaStream_t` cast to
+ * `void*`; NULL is the default stream) on the current device.
+ *
+ * Notation follows the reference (src/kla/ops/kla_ops.py:1-32):
+ *   B batch, L sequence length, M channels, S states per channel
+ *   v, lambda_v, y, y_var : [B, L, M]   k, q : [B, L, S]   a, p : [M, S]
+ *   filter state (lam, eta): [B, M, S]
+ * Strides are in ELEMENTS. The innermost dimension always has unit stride.
+ *
+ * Return value: 0 on success, a KLA_B200_E* code otherwise (see
+ * kla_b200_strerror). Errors are detected before any kernel is launched.
+ */
+#ifndef KLA_B200_H
+#define KLA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KLA_B200_OK 0
+#define KLA_B200_EINVAL 1      /* NULL pointer, negative size, bad stride or flag */
+#define KLA_B200_EUNSUPPORTED 2 /* S above KLA_B200_MAX_DSTATE, unknown dtype */
+#define KLA_B200_ECUDA 3       /* a CUDA runtime call failed (cudaGetLastError text via strerror) */
+#define KLA_B200_EALIGN 4      /* pointer not aligned to its element size */
+
+/* Largest d_state the kernels are instantiated for. The reference's fused
+ * kernels have the same kind of cap (src/kla/ops/cuda_backend.py:134,274-275). */
+#define KLA_B200_MAX_DSTATE 128
+
+/* Element types of the activation tensors. `in_dtype` is the type of v,
+ * lambda_v, k, q (and of the gradients dv, dlambda_v); `out_dtype` is the type
+ * of y, y_var (and of the incoming dy, dy_var). The recurrence itself always
+ * runs in float32, as in the reference (src/kla/ops/kla_ops.py:126-137), which
+ * also returns float32 for low-precision inputs -- the (BF16, F32) pair.
+ * Supported pairs: (F32, F32), (BF16, F32), (BF16, BF16). */
+#define KLA_B200_F32 0
+#define KLA_B200_BF16 1
+
+/* A [B, L, X] activation tensor: base pointer plus batch and time strides. */
+typedef struct kla_b200_tensor3 {
+    void *ptr;
+    int64_t stride_b;
+    int64_t stride_t;
+} kla_b200_tensor3;
+
+/*
+ * Forward scan. Replaces the backend callable the reference dispatches to from
+ * kla_scan (src/kla/ops/kla_ops.py:486-541; contract of the callable:
+ * kla_scan_torch, src/kla/ops/kla_ops.py:188-290), including the fold
+ * v*lambda_v (kla_ops.py:177), the floor on p (kla_ops.py:181-185), the floor
+ * on a*a (kla_ops.py:240) and the optional read-out from the one-step-ahead
+ * prior (kla_ops.py:284-286).
+ */
+typedef struct kla_b200_fwd_args {
+    int64_t B, L, M, S;
+    int32_t in_dtype, out_dtype; /* KLA_B200_F32 or KLA_B200_BF16 */
+    int32_t decode_from_prior;
+    kla_b200_tensor3 v, lambda_v; /* in  [B, L, M] */
+    kla_b200_tensor3 k, q;        /* in  [B, L, S] */
+    const float *a, *p;           /* in  [M, S] contiguous float32 */
+    const float *lam0, *eta0;     /* in  [B, M, S] contiguous float32, or both NULL = unit prior (kla_ops.py:54-61) */
+    kla_b200_tensor3 y, y_var;    /* out [B, L, M] */
+    float *lam_fin, *eta_fin;     /* out [B, M, S] contiguous float32 */
+    void *ckpt;                   /* out scratch of kla_b200_ckpt_bytes(), or NULL when no backward will follow */
+} kla_b200_fwd_args;
+
+/* Bytes of the checkpoint scratch the forward writes for the backward:
+ * the filter state of every lane once per kla_b200_ckpt_interval() steps. */
+size_t kla_b200_ckpt_bytes(int64_t B, int64_t L, int64_t M, int64_t S);
+int64_t kla_b200_ckpt_interval(void);
+
+int kla_b200_scan_fwd(const kla_b200_fwd_args *args, void *stream);
+
+/*
+ * Backward scan: exact adjoint of kla_b200_scan_fwd. Replaces what torch
+ * autograd does for the reference's CPU path and what the reference's
+ * hand-written fused adjoint does on its GPU paths
+ * (src/kla/ops/kernels/mps/fused_kla_scan.metal:135-324; autograd wrapper
+ * src/kla/ops/cuda_backend.py:196-236). Gradients flow into the carried state
+ * (dlam0, deta0) and out of the returned one (dlam_fin, deta_fin), as the
+ * reference requires (tests/test_backends.py:802-839).
+ *
+ * dk, dq, da, dp are accumulated with atomic adds after the library zeroes
+ * them; dv, dlambda_v, dlam0, deta0 are written outright.
+ */
+typedef struct kla_b200_bwd_args {
+    int64_t B, L, M, S;
+    int32_t in_dtype, out_dtype;
+    int32_t decode_from_prior;
+    kla_b200_tensor3 v, lambda_v, k, q; /* in, as in the forward */
+    const float *a, *p;
+    const float *lam0, *eta0;           /* or both NULL */
+    const void *ckpt;                   /* in: what the forward wrote */
+    kla_b200_tensor3 dy;                /* in  [B, L, M] */
+    kla_b200_tensor3 dy_var;            /* in  [B, L, M], ptr may be NULL = zero */
+    const float *dlam_fin, *deta_fin;   /* in  [B, M, S] contiguous, or both NULL = zero */
+    kla_b200_tensor3 dv, dlambda_v;     /* out [B, L, M] */
+    float *dk, *dq;                     /* out [B, L, S] contiguous float32 */
+    float *da, *dp;                     /* out [M, S] contiguous float32 */
+    float *dlam0, *deta0;               /* out [B, M, S] contiguous float32 */
+} kla_b200_bwd_args;
+
+int kla_b200_scan_bwd(const kla_b200_bwd_args *args, void *stream);
+
+/*
+ * One decode step. Replaces kla_step (src/kla/ops/kla_ops.py:293-331), which
+ * the reference layer calls directly for single-token decode
+ * (src/kla/layers/kla_layer.py:277-293). phi is floored at 1e-12 as there
+ * (kla_ops.py:310-312). lam_out/eta_out may alias lam/eta (in-place update).
+ * v, lambda_v, y, y_var: [B, M] with a batch stride; k, q: [B, S].
+ */
+typedef struct kla_b200_step_args {
+    int64_t B, M, S;
+    int32_t in_dtype, out_dtype;
+    int32_t decode_from_prior;
+    const void *v, *lambda_v;     /* [B, M] */
+    int64_t v_stride_b, lambda_v_stride_b;
+    const void *k, *q;            /* [B, S] */
+    int64_t k_stride_b, q_stride_b;
+    const float *a, *p;           /* [M, S] */
+    const float *lam, *eta;       /* [B, M, S] */
+    void *y, *y_var;              /* [B, M] contiguous */
+    float *lam_out, *eta_out;     /* [B, M, S] */
+} kla_b200_step_args;
+
+int kla_b200_step(const kla_b200_step_args *args, void *stream);
+
+/* Human-readable text for a return code; for KLA_B200_ECUDA it includes the
+ * CUDA error string of the failing call on this thread. */
+const char *kla_b200_strerror(int code);
+
+/* Library version, major*100 + minor. */
+int kla_b200_version(void);
+
+/* Number of kernels the library has launched in this process so far
+ * (memsets are not counted). Used by the benchmark to report its launch count. */
+int64_t kla_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* KLA_B200_H */

@@ -1,0 +1,119 @@
+"""ctypes view of ``libkla_b200.so``: the structs and prototypes of
+``include/kla_b200.h``. Loading fails loudly when the library has not been
+built; there is no fallback implementation."""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, Structure, c_char_p, c_int, c_int32, c_int64, c_size_t, c_void_p
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libkla_b200.so")
+
+F32, BF16 = 0, 1
+MAX_DSTATE = 128
+
+SYMBOLS = (
+    "kla_b200_ckpt_bytes",
+    "kla_b200_ckpt_interval",
+    "kla_b200_scan_fwd",
+    "kla_b200_scan_bwd",
+    "kla_b200_step",
+    "kla_b200_strerror",
+    "kla_b200_version",
+    "kla_b200_launch_count",
+)
+
+
+class Tensor3(Structure):
+    _fields_ = [("ptr", c_void_p), ("stride_b", c_int64), ("stride_t", c_int64)]
+
+
+class FwdArgs(Structure):
+    _fields_ = [
+        ("B", c_int64), ("L", c_int64), ("M", c_int64), ("S", c_int64),
+        ("in_dtype", c_int32), ("out_dtype", c_int32), ("decode_from_prior", c_int32),
+        ("v", Tensor3), ("lambda_v", Tensor3), ("k", Tensor3), ("q", Tensor3),
+        ("a", c_void_p), ("p", c_void_p), ("lam0", c_void_p), ("eta0", c_void_p),
+        ("y", Tensor3), ("y_var", Tensor3),
+        ("lam_fin", c_void_p), ("eta_fin", c_void_p), ("ckpt", c_void_p),
+    ]
+
+
+class BwdArgs(Structure):
+    _fields_ = [
+        ("B", c_int64), ("L", c_int64), ("M", c_int64), ("S", c_int64),
+        ("in_dtype", c_int32), ("out_dtype", c_int32), ("decode_from_prior", c_int32),
+        ("v", Tensor3), ("lambda_v", Tensor3), ("k", Tensor3), ("q", Tensor3),
+        ("a", c_void_p), ("p", c_void_p), ("lam0", c_void_p), ("eta0", c_void_p),
+        ("ckpt", c_void_p),
+        ("dy", Tensor3), ("dy_var", Tensor3),
+        ("dlam_fin", c_void_p), ("deta_fin", c_void_p),
+        ("dv", Tensor3), ("dlambda_v", Tensor3),
+        ("dk", c_void_p), ("dq", c_void_p), ("da", c_void_p), ("dp", c_void_p),
+        ("dlam0", c_void_p), ("deta0", c_void_p),
+    ]
+
+
+class StepArgs(Structure):
+    _fields_ = [
+        ("B", c_int64), ("M", c_int64), ("S", c_int64),
+        ("in_dtype", c_int32), ("out_dtype", c_int32), ("decode_from_prior", c_int32),
+        ("v", c_void_p), ("lambda_v", c_void_p),
+        ("v_stride_b", c_int64), ("lambda_v_stride_b", c_int64),
+        ("k", c_void_p), ("q", c_void_p),
+        ("k_stride_b", c_int64), ("q_stride_b", c_int64),
+        ("a", c_void_p), ("p", c_void_p), ("lam", c_void_p), ("eta", c_void_p),
+        ("y", c_void_p), ("y_var", c_void_p), ("lam_out", c_void_p), ("eta_out", c_void_p),
+    ]
+
+
+_lib = None
+
+
+class LibraryMissing(RuntimeError):
+    pass
+
+
+def load() -> ctypes.CDLL:
+    """Load the library once; raise :class:`LibraryMissing` if it is not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise LibraryMissing(
+            f"{LIB_PATH} is not built. Build it with "
+            "`python kalman-linear-attention_b200/build.py` (needs nvcc; no GPU needed to build). "
+            "The b200 backend has no CPU or Triton fallback."
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.kla_b200_ckpt_bytes.restype = c_size_t
+    lib.kla_b200_ckpt_bytes.argtypes = [c_int64] * 4
+    lib.kla_b200_ckpt_interval.restype = c_int64
+    lib.kla_b200_scan_fwd.restype = c_int
+    lib.kla_b200_scan_fwd.argtypes = [POINTER(FwdArgs), c_void_p]
+    lib.kla_b200_scan_bwd.restype = c_int
+    lib.kla_b200_scan_bwd.argtypes = [POINTER(BwdArgs), c_void_p]
+    lib.kla_b200_step.restype = c_int
+    lib.kla_b200_step.argtypes = [POINTER(StepArgs), c_void_p]
+    lib.kla_b200_strerror.restype = c_char_p
+    lib.kla_b200_strerror.argtypes = [c_int]
+    lib.kla_b200_version.restype = c_int
+    lib.kla_b200_launch_count.restype = c_int64
+    _lib = lib
+    return lib
+
+
+def check(code: int) -> None:
+    """Map a C-ABI status to the reference's exception convention:
+    unsupported configuration -> NotImplementedError (src/kla/ops/cuda_backend.py:239-242),
+    bad argument -> ValueError, CUDA failure -> RuntimeError."""
+    if code == 0:
+        return
+    msg = load().kla_b200_strerror(code).decode()
+    if code == 2:
+        raise NotImplementedError(f"The b200 KLA backend: {msg}. Use backend='torch' for this case.")
+    if code in (1, 4):
+        raise ValueError(f"kla_b200: {msg}")
+    raise RuntimeError(f"kla_b200: {msg}")

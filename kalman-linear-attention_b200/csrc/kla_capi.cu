@@ -1,0 +1,288 @@
+// extern "C" entry points of libkla_b200.so: argument checks, kernel-shape
+// selection and launches. No torch types, no allocation, no exceptions.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/kla_b200.h"
+#include "kla_bwd.cuh"
+#include "kla_fwd.cuh"
+#include "kla_step.cuh"
+
+namespace {
+
+using namespace kla;
+
+constexpr int kNW = 4;                 // warps per CTA
+constexpr int kTT = kCkptInterval;     // steps per tile
+constexpr int kSPT = 4;                // states per thread
+constexpr int kCH = 1;                 // channels per thread
+
+std::atomic<long long> g_launches{0};
+thread_local cudaError_t g_last_cuda = cudaSuccess;
+thread_local char g_errbuf[256];
+
+int cuda_fail(cudaError_t e) {
+    g_last_cuda = e;
+    return KLA_B200_ECUDA;
+}
+
+Tensor3 t3(const kla_b200_tensor3 &t) { return Tensor3{t.ptr, t.stride_b, t.stride_t}; }
+
+bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// 16-byte staging is legal when every row start of the tensor is 16-byte aligned.
+template <typename T>
+int vec_ok(const kla_b200_tensor3 &t, int64_t M) {
+    constexpr int VEC = 16 / sizeof(T);
+    return t.ptr != nullptr && aligned(t.ptr, 16) && (t.stride_b % VEC) == 0 && (t.stride_t % VEC) == 0 &&
+           (M % VEC) == 0;
+}
+
+int lpc_for(int64_t S) {
+    int lpc = 1;
+    while ((int64_t)kSPT * lpc < S) lpc *= 2;
+    return lpc;  // 1..32 for S <= 128
+}
+
+int check_common(int64_t B, int64_t L, int64_t M, int64_t S, int32_t in_dtype, int32_t out_dtype) {
+    if (B < 0 || L < 0 || M < 0 || S < 0) return KLA_B200_EINVAL;
+    if (S > KLA_B200_MAX_DSTATE) return KLA_B200_EUNSUPPORTED;
+    if (in_dtype != KLA_B200_F32 && in_dtype != KLA_B200_BF16) return KLA_B200_EUNSUPPORTED;
+    if (out_dtype != KLA_B200_F32 && out_dtype != KLA_B200_BF16) return KLA_B200_EUNSUPPORTED;
+    if (in_dtype == KLA_B200_F32 && out_dtype == KLA_B200_BF16) return KLA_B200_EUNSUPPORTED;
+    if (B > 65535 || L > (1 << 30) || M > (1 << 30)) return KLA_B200_EUNSUPPORTED;
+    return KLA_B200_OK;
+}
+
+int check_t3(const kla_b200_tensor3 &t, size_t esz, bool required) {
+    if (t.ptr == nullptr) return required ? KLA_B200_EINVAL : KLA_B200_OK;
+    if (!aligned(t.ptr, esz)) return KLA_B200_EALIGN;
+    if (t.stride_b < 0 || t.stride_t < 0) return KLA_B200_EINVAL;
+    return KLA_B200_OK;
+}
+
+template <typename T, typename TO, int LPC, bool PRIOR>
+int launch_fwd(const FwdParams &prm, cudaStream_t st) {
+    using Sh = ScanShape<kSPT, LPC, kCH, kNW, kTT>;
+    auto kern = kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kTT, PRIOR>;
+    const size_t smem = sizeof(float4) * 2 * kTT * Sh::kSPad + sizeof(T) * 4 * kTT * Sh::kMC;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_fail(e);
+    dim3 grid((unsigned)((prm.M + Sh::kMC - 1) / Sh::kMC), (unsigned)prm.B);
+    kern<<<grid, Sh::kThreads, smem, st>>>(prm);
+    g_launches++;
+    e = cudaGetLastError();
+    return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
+}
+
+template <typename T, typename TO, int LPC, bool PRIOR>
+int launch_bwd(const BwdParams &prm, cudaStream_t st) {
+    using Sh = ScanShape<kSPT, LPC, kCH, kNW, kTT>;
+    auto kern = kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kTT, PRIOR>;
+    const size_t smem = sizeof(float4) * 2 * kTT * Sh::kSPad + sizeof(float2) * kTT * kCH * kSPT * Sh::kThreads +
+                        (sizeof(T) + sizeof(TO)) * 4 * kTT * Sh::kMC;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_fail(e);
+    dim3 grid((unsigned)((prm.M + Sh::kMC - 1) / Sh::kMC), (unsigned)prm.B);
+    kern<<<grid, Sh::kThreads, smem, st>>>(prm);
+    g_launches++;
+    e = cudaGetLastError();
+    return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
+}
+
+template <typename T, typename TO, int LPC, bool PRIOR>
+int launch_step(const StepParams &prm, cudaStream_t st) {
+    const long long threads = (long long)prm.B * prm.M * LPC;
+    const unsigned blocks = (unsigned)((threads + 127) / 128);
+    kla_step_kernel<T, TO, LPC, PRIOR><<<blocks, 128, 0, st>>>(prm);
+    g_launches++;
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
+}
+
+// Expand (dtype pair, lanes per channel, prior flag) into a template instantiation.
+#define KLA_DISPATCH_LPC(FN, T, TO, PRIOR, lpc, ...)          \
+    switch (lpc) {                                            \
+        case 1: return FN<T, TO, 1, PRIOR>(__VA_ARGS__);      \
+        case 2: return FN<T, TO, 2, PRIOR>(__VA_ARGS__);      \
+        case 4: return FN<T, TO, 4, PRIOR>(__VA_ARGS__);      \
+        case 8: return FN<T, TO, 8, PRIOR>(__VA_ARGS__);      \
+        case 16: return FN<T, TO, 16, PRIOR>(__VA_ARGS__);    \
+        case 32: return FN<T, TO, 32, PRIOR>(__VA_ARGS__);    \
+        default: return KLA_B200_EUNSUPPORTED;                \
+    }
+#define KLA_DISPATCH_PRIOR(FN, T, TO, prior, lpc, ...)                  \
+    if (prior) { KLA_DISPATCH_LPC(FN, T, TO, true, lpc, __VA_ARGS__) }  \
+    else { KLA_DISPATCH_LPC(FN, T, TO, false, lpc, __VA_ARGS__) }
+#define KLA_DISPATCH(FN, din, dout, prior, lpc, ...)                                         \
+    do {                                                                                     \
+        if ((din) == KLA_B200_F32 && (dout) == KLA_B200_F32) {                               \
+            KLA_DISPATCH_PRIOR(FN, float, float, prior, lpc, __VA_ARGS__)                    \
+        } else if ((din) == KLA_B200_BF16 && (dout) == KLA_B200_F32) {                       \
+            KLA_DISPATCH_PRIOR(FN, __nv_bfloat16, float, prior, lpc, __VA_ARGS__)            \
+        } else if ((din) == KLA_B200_BF16 && (dout) == KLA_B200_BF16) {                      \
+            KLA_DISPATCH_PRIOR(FN, __nv_bfloat16, __nv_bfloat16, prior, lpc, __VA_ARGS__)    \
+        } else {                                                                             \
+            return KLA_B200_EUNSUPPORTED;                                                    \
+        }                                                                                    \
+    } while (0)
+
+int dispatch_fwd(int din, int dout, bool prior, int lpc, const FwdParams &prm, cudaStream_t st) {
+    KLA_DISPATCH(launch_fwd, din, dout, prior, lpc, prm, st);
+}
+int dispatch_bwd(int din, int dout, bool prior, int lpc, const BwdParams &prm, cudaStream_t st) {
+    KLA_DISPATCH(launch_bwd, din, dout, prior, lpc, prm, st);
+}
+int dispatch_step(int din, int dout, bool prior, int lpc, const StepParams &prm, cudaStream_t st) {
+    KLA_DISPATCH(launch_step, din, dout, prior, lpc, prm, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t kla_b200_ckpt_interval(void) { return kCkptInterval; }
+
+size_t kla_b200_ckpt_bytes(int64_t B, int64_t L, int64_t M, int64_t S) {
+    if (B <= 0 || L <= 0 || M <= 0 || S <= 0) return 0;
+    const int64_t nt = (L + kCkptInterval - 1) / kCkptInterval;
+    return (size_t)B * (size_t)nt * (size_t)M * (size_t)S * sizeof(float2);
+}
+
+int kla_b200_scan_fwd(const kla_b200_fwd_args *a, void *stream) {
+    if (a == nullptr) return KLA_B200_EINVAL;
+    int rc = check_common(a->B, a->L, a->M, a->S, a->in_dtype, a->out_dtype);
+    if (rc) return rc;
+    const size_t esz = a->in_dtype == KLA_B200_F32 ? 4 : 2, osz = a->out_dtype == KLA_B200_F32 ? 4 : 2;
+    const bool empty = a->B == 0 || a->M == 0 || a->S == 0;
+    if (empty) return KLA_B200_OK;
+    if (!a->a || !a->p || !a->lam_fin || !a->eta_fin) return KLA_B200_EINVAL;
+    if ((a->lam0 == nullptr) != (a->eta0 == nullptr)) return KLA_B200_EINVAL;
+    if (a->L > 0) {
+        const kla_b200_tensor3 *ts[] = {&a->v, &a->lambda_v, &a->k, &a->q};
+        for (const kla_b200_tensor3 *t : ts)
+            if ((rc = check_t3(*t, esz, true))) return rc;
+        if ((rc = check_t3(a->y, osz, true))) return rc;
+        if ((rc = check_t3(a->y_var, osz, true))) return rc;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    FwdParams prm{};
+    prm.B = (int)a->B; prm.L = (int)a->L; prm.M = (int)a->M; prm.S = (int)a->S;
+    prm.NT = (int)((a->L + kTT - 1) / kTT);
+    prm.v = t3(a->v); prm.lv = t3(a->lambda_v); prm.k = t3(a->k); prm.q = t3(a->q);
+    prm.y = t3(a->y); prm.yv = t3(a->y_var);
+    prm.a = a->a; prm.p = a->p; prm.lam0 = a->lam0; prm.eta0 = a->eta0;
+    prm.lam_fin = a->lam_fin; prm.eta_fin = a->eta_fin;
+    prm.ckpt = static_cast<float2 *>(a->ckpt);
+    if (a->in_dtype == KLA_B200_F32) {
+        prm.vec_v = vec_ok<float>(a->v, a->M); prm.vec_lv = vec_ok<float>(a->lambda_v, a->M);
+    } else {
+        prm.vec_v = vec_ok<__nv_bfloat16>(a->v, a->M); prm.vec_lv = vec_ok<__nv_bfloat16>(a->lambda_v, a->M);
+    }
+    return dispatch_fwd(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc_for(a->S), prm, st);
+}
+
+int kla_b200_scan_bwd(const kla_b200_bwd_args *a, void *stream) {
+    if (a == nullptr) return KLA_B200_EINVAL;
+    int rc = check_common(a->B, a->L, a->M, a->S, a->in_dtype, a->out_dtype);
+    if (rc) return rc;
+    const size_t esz = a->in_dtype == KLA_B200_F32 ? 4 : 2, osz = a->out_dtype == KLA_B200_F32 ? 4 : 2;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t n_bls = (size_t)a->B * a->L * a->S, n_ms = (size_t)a->M * a->S, n_bms = (size_t)a->B * a->M * a->S;
+    if (n_bls && (!a->dk || !a->dq)) return KLA_B200_EINVAL;
+    if (n_ms && (!a->da || !a->dp)) return KLA_B200_EINVAL;
+    if (n_bms && (!a->dlam0 || !a->deta0)) return KLA_B200_EINVAL;
+    if ((a->lam0 == nullptr) != (a->eta0 == nullptr)) return KLA_B200_EINVAL;
+    if ((a->dlam_fin == nullptr) != (a->deta_fin == nullptr)) return KLA_B200_EINVAL;
+    cudaError_t e;
+    if (n_bls) {
+        if ((e = cudaMemsetAsync(a->dk, 0, n_bls * 4, st)) != cudaSuccess) return cuda_fail(e);
+        if ((e = cudaMemsetAsync(a->dq, 0, n_bls * 4, st)) != cudaSuccess) return cuda_fail(e);
+    }
+    if (n_ms) {
+        if ((e = cudaMemsetAsync(a->da, 0, n_ms * 4, st)) != cudaSuccess) return cuda_fail(e);
+        if ((e = cudaMemsetAsync(a->dp, 0, n_ms * 4, st)) != cudaSuccess) return cuda_fail(e);
+    }
+    if (n_bms == 0) return KLA_B200_OK;
+    if (a->L == 0) {  // nothing to scan: the state gradient passes straight through
+        if (a->dlam_fin) {
+            if ((e = cudaMemcpyAsync(a->dlam0, a->dlam_fin, n_bms * 4, cudaMemcpyDeviceToDevice, st)) != cudaSuccess) return cuda_fail(e);
+            if ((e = cudaMemcpyAsync(a->deta0, a->deta_fin, n_bms * 4, cudaMemcpyDeviceToDevice, st)) != cudaSuccess) return cuda_fail(e);
+        } else {
+            if ((e = cudaMemsetAsync(a->dlam0, 0, n_bms * 4, st)) != cudaSuccess) return cuda_fail(e);
+            if ((e = cudaMemsetAsync(a->deta0, 0, n_bms * 4, st)) != cudaSuccess) return cuda_fail(e);
+        }
+        return KLA_B200_OK;
+    }
+    if (!a->a || !a->p || !a->ckpt) return KLA_B200_EINVAL;
+    const kla_b200_tensor3 *ts[] = {&a->v, &a->lambda_v, &a->k, &a->q, &a->dv, &a->dlambda_v};
+    for (const kla_b200_tensor3 *t : ts)
+        if ((rc = check_t3(*t, esz, true))) return rc;
+    if ((rc = check_t3(a->dy, osz, true))) return rc;
+    if ((rc = check_t3(a->dy_var, osz, false))) return rc;
+
+    BwdParams prm{};
+    prm.B = (int)a->B; prm.L = (int)a->L; prm.M = (int)a->M; prm.S = (int)a->S;
+    prm.NT = (int)((a->L + kTT - 1) / kTT);
+    prm.v = t3(a->v); prm.lv = t3(a->lambda_v); prm.k = t3(a->k); prm.q = t3(a->q);
+    prm.dy = t3(a->dy); prm.dyv = t3(a->dy_var); prm.dv = t3(a->dv); prm.dlv = t3(a->dlambda_v);
+    prm.a = a->a; prm.p = a->p; prm.lam0 = a->lam0; prm.eta0 = a->eta0;
+    prm.ckpt = static_cast<const float2 *>(a->ckpt);
+    prm.dlam_fin = a->dlam_fin; prm.deta_fin = a->deta_fin;
+    prm.dk = a->dk; prm.dq = a->dq; prm.da = a->da; prm.dp = a->dp;
+    prm.dlam0 = a->dlam0; prm.deta0 = a->deta0;
+    if (a->in_dtype == KLA_B200_F32) {
+        prm.vec_v = vec_ok<float>(a->v, a->M); prm.vec_lv = vec_ok<float>(a->lambda_v, a->M);
+    } else {
+        prm.vec_v = vec_ok<__nv_bfloat16>(a->v, a->M); prm.vec_lv = vec_ok<__nv_bfloat16>(a->lambda_v, a->M);
+    }
+    if (a->out_dtype == KLA_B200_F32) {
+        prm.vec_dy = vec_ok<float>(a->dy, a->M); prm.vec_dyv = vec_ok<float>(a->dy_var, a->M);
+    } else {
+        prm.vec_dy = vec_ok<__nv_bfloat16>(a->dy, a->M); prm.vec_dyv = vec_ok<__nv_bfloat16>(a->dy_var, a->M);
+    }
+    return dispatch_bwd(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc_for(a->S), prm, st);
+}
+
+int kla_b200_step(const kla_b200_step_args *a, void *stream) {
+    if (a == nullptr) return KLA_B200_EINVAL;
+    int rc = check_common(a->B, 1, a->M, a->S, a->in_dtype, a->out_dtype);
+    if (rc) return rc;
+    if (a->B == 0 || a->M == 0) return KLA_B200_OK;
+    if (!a->v || !a->lambda_v || !a->y || !a->y_var || !a->a || !a->p) return KLA_B200_EINVAL;
+    if (a->S > 0 && (!a->k || !a->q || !a->lam || !a->eta || !a->lam_out || !a->eta_out)) return KLA_B200_EINVAL;
+    const size_t esz = a->in_dtype == KLA_B200_F32 ? 4 : 2, osz = a->out_dtype == KLA_B200_F32 ? 4 : 2;
+    const void *ps[] = {a->v, a->lambda_v, a->k, a->q};
+    for (const void *p : ps)
+        if (p && !aligned(p, esz)) return KLA_B200_EALIGN;
+    if (!aligned(a->y, osz) || !aligned(a->y_var, osz)) return KLA_B200_EALIGN;
+    StepParams prm{};
+    prm.B = (int)a->B; prm.M = (int)a->M; prm.S = (int)a->S;
+    prm.v = a->v; prm.lv = a->lambda_v; prm.k = a->k; prm.q = a->q;
+    prm.v_sb = a->v_stride_b; prm.lv_sb = a->lambda_v_stride_b; prm.k_sb = a->k_stride_b; prm.q_sb = a->q_stride_b;
+    prm.a = a->a; prm.p = a->p; prm.lam = a->lam; prm.eta = a->eta;
+    prm.y = a->y; prm.yv = a->y_var; prm.lam_out = a->lam_out; prm.eta_out = a->eta_out;
+    int lpc = 1;
+    while (lpc * 4 < a->S) lpc *= 2;
+    return dispatch_step(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc, prm, static_cast<cudaStream_t>(stream));
+}
+
+const char *kla_b200_strerror(int code) {
+    switch (code) {
+        case KLA_B200_OK: return "ok";
+        case KLA_B200_EINVAL: return "invalid argument (NULL pointer, negative size or stride, or half of a pointer pair missing)";
+        case KLA_B200_EUNSUPPORTED: return "unsupported configuration (d_state above 128, unsupported dtype pair, or a dimension too large)";
+        case KLA_B200_EALIGN: return "pointer not aligned to its element size";
+        case KLA_B200_ECUDA:
+            snprintf(g_errbuf, sizeof(g_errbuf), "CUDA error: %s", cudaGetErrorString(g_last_cuda));
+            return g_errbuf;
+        default: return "unknown error code";
+    }
+}
+
+int kla_b200_version(void) { return 100; }
+
+int64_t kla_b200_launch_count(void) { return g_launches.load(); }
+
+}  // extern "C"

@@ -1,0 +1,325 @@
+"""Host side of the ``b200`` backend: the reference's backend-callable contract
+over the C-ABI library.
+
+The reference dispatches ``kla_scan(..., backend=name)`` to a callable
+
+    fn(v, lambda_v, k, q, a, p, initial_state=None, decode_from_prior=False)
+        -> (y [B,L,M], y_var [B,L,M], KLAState(lam, eta) [B,M,S])
+
+looked up in ``kla.ops.kla_ops._BACKENDS`` (src/kla/ops/kla_ops.py:430-442,
+486-541). :func:`kla_scan_b200` is such a callable; :func:`kla_step_b200`
+mirrors ``kla_step`` (src/kla/ops/kla_ops.py:293-331). Error behaviour follows
+the reference's GPU backends (src/kla/ops/cuda_backend.py:239-275): a request
+the kernels cannot serve raises ``NotImplementedError`` naming a backend that
+can; nothing falls back silently, and there is no CPU or Triton path.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import sys
+from typing import NamedTuple, Optional
+
+import torch
+
+from . import _lib
+from ._lib import BF16, F32, MAX_DSTATE, BwdArgs, FwdArgs, StepArgs, Tensor3
+
+
+class KLAState(NamedTuple):
+    """Filter state: posterior precision and information vector, each [B, M, S]
+    (same fields as the reference's ``KLAState``, src/kla/ops/kla_ops.py:47-51)."""
+
+    lam: torch.Tensor
+    eta: torch.Tensor
+
+
+def init_state(batch: int, d_model: int, d_state: int, device=None, dtype=torch.float32) -> KLAState:
+    """Unit prior: precision 1, zero mean (src/kla/ops/kla_ops.py:54-61)."""
+    return KLAState(
+        lam=torch.ones(batch, d_model, d_state, device=device, dtype=dtype),
+        eta=torch.zeros(batch, d_model, d_state, device=device, dtype=dtype),
+    )
+
+
+def _state_cls():
+    """The reference's own KLAState when the reference package is loaded, so
+    that callers doing isinstance checks or tuple unpacking see what they expect."""
+    mod = sys.modules.get("kla.ops.kla_ops")
+    return getattr(mod, "KLAState", KLAState) if mod is not None else KLAState
+
+
+def _unsupported(msg: str) -> NotImplementedError:
+    return NotImplementedError(
+        f"The b200 KLA backend {msg}. Use backend='torch' (any device) or 'triton' for this case."
+    )
+
+
+_SM100_CACHE: dict = {}
+
+
+def _require_sm100(device: torch.device) -> None:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ok = _SM100_CACHE.get(idx)
+    if ok is None:
+        ok = torch.cuda.get_device_capability(idx)[0] == 10
+        _SM100_CACHE[idx] = ok
+    if not ok:
+        raise _unsupported("is compiled for sm_100a (B200) only and this device is not one")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _t3(t: Optional[torch.Tensor]) -> Tensor3:
+    if t is None:
+        return Tensor3(None, 0, 0)
+    return Tensor3(t.data_ptr(), t.stride(0), t.stride(1))
+
+
+def _rowmajor_last(t: torch.Tensor) -> torch.Tensor:
+    """The kernels take a batch and a time stride per tensor but need unit stride
+    on the last dimension; anything else is copied once."""
+    if t.dim() == 3 and (t.shape[-1] <= 1 or t.stride(-1) == 1):
+        return t
+    return t.contiguous()
+
+
+def _stream(device: torch.device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _dt(t: torch.dtype) -> int:
+    return BF16 if t == torch.bfloat16 else F32
+
+
+class _KLAScanB200(torch.autograd.Function):
+    """Forward and exact backward of the fused scan, both as single kernels.
+
+    Inputs are already canonical: v, lambda_v, k, q share one dtype (float32 or
+    bfloat16) with unit last stride; a, p float32 contiguous [M, S]; lam0/eta0
+    float32 contiguous [B, M, S] or None."""
+
+    @staticmethod
+    def forward(ctx, v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype: torch.dtype):
+        lib = _lib.load()
+        B, L, M = v.shape
+        S = k.shape[2]
+        dev = v.device
+        need_grad = any(ctx.needs_input_grad[:8])
+        y = torch.empty((B, L, M), device=dev, dtype=out_dtype)
+        y_var = torch.empty((B, L, M), device=dev, dtype=out_dtype)
+        lam_fin = torch.empty((B, M, S), device=dev, dtype=torch.float32)
+        eta_fin = torch.empty((B, M, S), device=dev, dtype=torch.float32)
+        ckpt = None
+        if need_grad and L > 0:
+            ckpt = torch.empty(lib.kla_b200_ckpt_bytes(B, L, M, S), device=dev, dtype=torch.uint8)
+        args = FwdArgs(
+            B=B, L=L, M=M, S=S, in_dtype=_dt(v.dtype), out_dtype=_dt(out_dtype),
+            decode_from_prior=int(prior),
+            v=_t3(v), lambda_v=_t3(lambda_v), k=_t3(k), q=_t3(q),
+            a=_ptr(a), p=_ptr(p), lam0=_ptr(lam0), eta0=_ptr(eta0),
+            y=_t3(y), y_var=_t3(y_var), lam_fin=_ptr(lam_fin), eta_fin=_ptr(eta_fin),
+            ckpt=_ptr(ckpt),
+        )
+        with torch.cuda.device(dev):
+            _lib.check(lib.kla_b200_scan_fwd(ctypes.byref(args), _stream(dev)))
+        ctx.save_for_backward(v, lambda_v, k, q, a, p, lam0, eta0, ckpt)
+        ctx.prior = prior
+        ctx.out_dtype = out_dtype
+        return y, y_var, lam_fin, eta_fin
+
+    @staticmethod
+    def backward(ctx, dy, dy_var, dlam_fin, deta_fin):
+        lib = _lib.load()
+        v, lambda_v, k, q, a, p, lam0, eta0, ckpt = ctx.saved_tensors
+        B, L, M = v.shape
+        S = k.shape[2]
+        dev = v.device
+        od = ctx.out_dtype
+
+        def grad_in(g):
+            if g is None:
+                return None
+            if g.dtype != od:
+                g = g.to(od)
+            return _rowmajor_last(g)
+
+        dy = grad_in(dy)
+        dy_var = grad_in(dy_var)
+        if dy is None:
+            dy = torch.zeros((B, L, M), device=dev, dtype=od)
+        if (dlam_fin is None) != (deta_fin is None):
+            z = torch.zeros((B, M, S), device=dev, dtype=torch.float32)
+            dlam_fin = z if dlam_fin is None else dlam_fin
+            deta_fin = z if deta_fin is None else deta_fin
+        if dlam_fin is not None:
+            dlam_fin = dlam_fin.float().contiguous()
+            deta_fin = deta_fin.float().contiguous()
+
+        dv = torch.empty((B, L, M), device=dev, dtype=v.dtype)
+        dlv = torch.empty((B, L, M), device=dev, dtype=v.dtype)
+        dk = torch.empty((B, L, S), device=dev, dtype=torch.float32)
+        dq = torch.empty((B, L, S), device=dev, dtype=torch.float32)
+        da = torch.empty((M, S), device=dev, dtype=torch.float32)
+        dp = torch.empty((M, S), device=dev, dtype=torch.float32)
+        dlam0 = torch.empty((B, M, S), device=dev, dtype=torch.float32)
+        deta0 = torch.empty((B, M, S), device=dev, dtype=torch.float32)
+        args = BwdArgs(
+            B=B, L=L, M=M, S=S, in_dtype=_dt(v.dtype), out_dtype=_dt(od),
+            decode_from_prior=int(ctx.prior),
+            v=_t3(v), lambda_v=_t3(lambda_v), k=_t3(k), q=_t3(q),
+            a=_ptr(a), p=_ptr(p), lam0=_ptr(lam0), eta0=_ptr(eta0), ckpt=_ptr(ckpt),
+            dy=_t3(dy), dy_var=_t3(dy_var), dlam_fin=_ptr(dlam_fin), deta_fin=_ptr(deta_fin),
+            dv=_t3(dv), dlambda_v=_t3(dlv), dk=_ptr(dk), dq=_ptr(dq), da=_ptr(da), dp=_ptr(dp),
+            dlam0=_ptr(dlam0), deta0=_ptr(deta0),
+        )
+        with torch.cuda.device(dev):
+            _lib.check(lib.kla_b200_scan_bwd(ctypes.byref(args), _stream(dev)))
+        if k.dtype != torch.float32:
+            dk, dq = dk.to(k.dtype), dq.to(k.dtype)
+        has_state = lam0 is not None
+        return (dv, dlv, dk, dq, da, dp,
+                dlam0 if has_state else None, deta0 if has_state else None, None, None)
+
+
+def kla_scan_b200(
+    v: torch.Tensor,
+    lambda_v: torch.Tensor,
+    k: torch.Tensor,
+    q: torch.Tensor,
+    a: torch.Tensor,
+    p: torch.Tensor,
+    initial_state=None,
+    decode_from_prior: bool = False,
+    *,
+    out_dtype: Optional[torch.dtype] = None,
+):
+    """B200 KLA scan. Same call and return contract as the reference's
+    ``kla_scan_torch`` (src/kla/ops/kla_ops.py:188-290): returns
+    ``(y, y_var, KLAState)``, float32 unless ``out_dtype`` says otherwise.
+
+    float32 inputs are read in place through their strides (the layer hands the
+    scan ``torch.split`` views, src/kla/layers/kla_layer.py:205-207); bfloat16
+    inputs are read as bfloat16 and widened in registers, where the reference
+    widens them with a copy (kla_ops.py:126-137). ``out_dtype=torch.bfloat16``
+    (bfloat16 inputs only) also writes y, y_var as bfloat16 -- what the layer
+    would cast them to anyway (kla_layer.py:329-330).
+    """
+    if not v.is_cuda:
+        raise _unsupported("requires CUDA tensors")
+    if a.dim() != 2:
+        raise _unsupported("expects a/p of shape [M, S]")
+    if v.dim() != 3 or k.dim() != 3:
+        raise ValueError("v, lambda_v must be [B, L, M] and k, q [B, L, S]")
+    B, L, M = v.shape
+    S = k.shape[2]
+    if lambda_v.shape != v.shape or q.shape != k.shape or k.shape[:2] != (B, L):
+        raise ValueError("shape mismatch between v, lambda_v [B,L,M] and k, q [B,L,S]")
+    if tuple(a.shape) != (M, S) or tuple(p.shape) != (M, S):
+        raise ValueError(f"a and p must be [M, S] = [{M}, {S}]")
+    if S > MAX_DSTATE:
+        raise _unsupported(f"supports d_state <= {MAX_DSTATE} (got {S})")
+    tensors = (v, lambda_v, k, q, a, p)
+    if any(t.dtype == torch.float64 for t in tensors):
+        raise _unsupported("runs in float32 only (float64 inputs are for gradcheck on the torch backend)")
+    if any(t.device != v.device for t in tensors):
+        raise ValueError("all inputs must be on the same device")
+    _require_sm100(v.device)
+
+    if all(t.dtype == torch.bfloat16 for t in (v, lambda_v, k, q)):
+        act = torch.bfloat16
+    else:
+        act = torch.float32
+    if out_dtype is None:
+        out_dtype = torch.float32
+    if out_dtype not in (torch.float32, torch.bfloat16) or (out_dtype == torch.bfloat16 and act != torch.bfloat16):
+        raise _unsupported("writes float32 outputs, or bfloat16 outputs for bfloat16 inputs")
+    v, lambda_v, k, q = (_rowmajor_last(t if t.dtype == act else t.to(act)) for t in (v, lambda_v, k, q))
+    a = a.float().contiguous()
+    p = p.float().contiguous()
+    lam0 = eta0 = None
+    if initial_state is not None:
+        lam0, eta0 = initial_state
+        if tuple(lam0.shape) != (B, M, S) or tuple(eta0.shape) != (B, M, S):
+            raise ValueError(f"initial_state must hold [B, M, S] = [{B}, {M}, {S}] tensors")
+        lam0 = lam0.float().contiguous()
+        eta0 = eta0.float().contiguous()
+
+    y, y_var, lam_fin, eta_fin = _KLAScanB200.apply(
+        v, lambda_v, k, q, a, p, lam0, eta0, bool(decode_from_prior), out_dtype)
+    return y, y_var, _state_cls()(lam=lam_fin, eta=eta_fin)
+
+
+def kla_step_b200(
+    v: torch.Tensor,
+    lambda_v: torch.Tensor,
+    k: torch.Tensor,
+    q: torch.Tensor,
+    a: torch.Tensor,
+    p: torch.Tensor,
+    state,
+    decode_from_prior: bool = False,
+    *,
+    inplace: bool = False,
+):
+    """One decode step on the B200: ``kla_step`` of the reference
+    (src/kla/ops/kla_ops.py:293-331). v, lambda_v: [B, M]; k, q: [B, S];
+    state: (lam, eta) [B, M, S]. Returns ``(y [B,M], y_var [B,M], new_state)``.
+
+    ``inplace=True`` updates the state tensors where they are (they must be
+    float32 and contiguous) instead of allocating new ones. When a gradient is
+    required the step is run as a length-1 scan, which has a backward.
+    """
+    if not v.is_cuda:
+        raise _unsupported("requires CUDA tensors")
+    if v.dim() != 2 or k.dim() != 2:
+        raise ValueError("v, lambda_v must be [B, M] and k, q [B, S]")
+    lam, eta = state
+    if torch.is_grad_enabled() and any(
+        t.requires_grad for t in (v, lambda_v, k, q, a, p, lam, eta)
+    ):
+        y, y_var, st = kla_scan_b200(
+            v.unsqueeze(1), lambda_v.unsqueeze(1), k.unsqueeze(1), q.unsqueeze(1), a, p,
+            initial_state=(lam, eta), decode_from_prior=decode_from_prior)
+        return y[:, 0], y_var[:, 0], st
+    B, M = v.shape
+    S = k.shape[1]
+    if tuple(a.shape) != (M, S) or tuple(p.shape) != (M, S) or tuple(lam.shape) != (B, M, S):
+        raise ValueError("shape mismatch between v [B,M], k [B,S], a/p [M,S] and the state [B,M,S]")
+    if S > MAX_DSTATE:
+        raise _unsupported(f"supports d_state <= {MAX_DSTATE} (got {S})")
+    if any(t.dtype == torch.float64 for t in (v, lambda_v, k, q, a, p, lam, eta)):
+        raise _unsupported("runs in float32 only")
+    _require_sm100(v.device)
+    lib = _lib.load()
+    act = torch.bfloat16 if all(t.dtype == torch.bfloat16 for t in (v, lambda_v, k, q)) else torch.float32
+
+    def row(t):
+        t = t if t.dtype == act else t.to(act)
+        return t if (t.shape[-1] <= 1 or t.stride(-1) == 1) else t.contiguous()
+
+    v, lambda_v, k, q = row(v), row(lambda_v), row(k), row(q)
+    a = a.float().contiguous()
+    p = p.float().contiguous()
+    if inplace:
+        if lam.dtype != torch.float32 or not lam.is_contiguous() or eta.dtype != torch.float32 or not eta.is_contiguous():
+            raise ValueError("inplace=True needs float32 contiguous state tensors")
+        lam_out, eta_out = lam, eta
+    else:
+        lam, eta = lam.float().contiguous(), eta.float().contiguous()
+        lam_out, eta_out = torch.empty_like(lam), torch.empty_like(eta)
+    dev = v.device
+    y = torch.empty((B, M), device=dev, dtype=torch.float32)
+    y_var = torch.empty((B, M), device=dev, dtype=torch.float32)
+    args = StepArgs(
+        B=B, M=M, S=S, in_dtype=_dt(act), out_dtype=F32, decode_from_prior=int(decode_from_prior),
+        v=_ptr(v), lambda_v=_ptr(lambda_v), v_stride_b=v.stride(0), lambda_v_stride_b=lambda_v.stride(0),
+        k=_ptr(k), q=_ptr(q), k_stride_b=k.stride(0), q_stride_b=q.stride(0),
+        a=_ptr(a), p=_ptr(p), lam=_ptr(lam), eta=_ptr(eta),
+        y=_ptr(y), y_var=_ptr(y_var), lam_out=_ptr(lam_out), eta_out=_ptr(eta_out),
+    )
+    with torch.cuda.device(dev):
+        _lib.check(lib.kla_b200_step(ctypes.byref(args), _stream(dev)))
+    return y, y_var, _state_cls()(lam=lam_out, eta=eta_out)
