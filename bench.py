@@ -217,7 +217,9 @@ def run_b200(args):
         dist.init_process_group("nccl", device_id=dev)
 
     B, T, M, S = WORK["B"], WORK["L"], WORK["M"], WORK["S"]
-    host = make_inputs(seed=rank, **WORK)
+    if args.profile_batch:
+        B = args.profile_batch
+    host = make_inputs(seed=rank, **{**WORK, "B": B})
     d = {n: t.to(dev) for n, t in host.items()}
     # preallocated outputs and scratch: the C-ABI allocates nothing
     f32 = dict(device=dev, dtype=torch.float32)
@@ -254,6 +256,14 @@ def run_b200(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.profile_batch:
+        step()
+        barrier()
+        print(json.dumps({"profile_only": True, "B": B, "L": T, "M": M, "S": S}))
+        return
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()  # nvidia-smi needs a moment to start: begin before the warm-up
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
@@ -261,9 +271,6 @@ def run_b200(args):
     # ---- device-resident timing: K steps, CUDA events on the launching stream.
     # Inputs and gradients (4 x 134 MB read per step, 4 x 134 MB written) exceed
     # the 126 MB L2, so no explicit flush is needed between iterations.
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
     launches0 = L.kla_b200_launch_count()
     barrier()
@@ -350,12 +357,14 @@ def run_b200(args):
         if world == 1 and not args.no_cpu:
             sample = dict(B=1, L=T, M=128, S=S)
             rate, dt, cores = cpu_oracle_run(sample)
-            if dt < 3.0:  # grow the sample towards ~10 s of CPU work
-                sample["M"] = int(min(M, 128 * max(1, round(8.0 / max(dt, 1e-3)))))
-                rate, dt, cores = cpu_oracle_run(sample)
+            # grow the sample towards ~10 s of CPU work: channels first, then batch
+            units = max(1.0, 10.0 / max(dt, 1e-3))
+            sample["M"] = int(min(M, 128 * round(units)))
+            sample["B"] = int(min(WORK["B"], max(1, round(units * 128 / M))))
+            rate, dt, cores = cpu_oracle_run(sample)
             line["cpu_baseline"] = {
                 "value": rate, "unit": UNIT, "cores": cores, "kind": "port",
-                "sample": f"B=1 x T={T} x M={sample['M']} of {M} channels x S={S}, float32 oracle fwd+bwd, "
+                "sample": f"B={sample['B']} x T={T} x M={sample['M']} of {M} channels x S={S}, float32 oracle fwd+bwd, "
                           f"{dt:.1f} s; rate scaled by M/{M} (lanes independent over channels)"}
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -365,10 +374,13 @@ def run_b200(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--profile-batch", type=int, default=0,
+                    help="profiling aid: run exactly one forward and one backward launch at this batch size "
+                         "(same T, M, S) and exit without timing; for captures under ncu")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -9,7 +9,7 @@ import os
 from ctypes import POINTER, Structure, c_char_p, c_int, c_int32, c_int64, c_size_t, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libkla_b200.so")
+LIB_PATH = os.environ.get("KLA_B200_LIB") or os.path.join(HERE, "libkla_b200.so")
 
 F32, BF16 = 0, 1
 MAX_DSTATE = 128

@@ -34,20 +34,21 @@ struct BwdParams {
     const float2 *ckpt;
     const float *dlam_fin, *deta_fin;
     float *dk, *dq, *da, *dp, *dlam0, *deta0;
-    int vec_v, vec_lv, vec_dy, vec_dyv;
+    int vec_v, vec_lv, vec_dy, vec_dyv, vec_dv, vec_dlv;
 };
 
 template <typename T, typename TO, int SPT, int LPC, int CH, int NW, int TT, bool PRIOR>
 __global__ void __launch_bounds__(NW * 32) kla_bwd_kernel(const BwdParams prm) {
     using Sh = ScanShape<SPT, LPC, CH, NW, TT>;
-    constexpr int SPAD = Sh::kSPad, MC = Sh::kMC, NTHR = Sh::kThreads, KQ = Sh::kKqPer;
-    constexpr int CLS = 32 / LPC;  // channel groups per warp
+    constexpr int SPAD = Sh::kSPad, MC = Sh::kMC, MCP = Sh::kMCP, NTHR = Sh::kThreads, KQ = Sh::kKqPer;
+    constexpr int CLS = Sh::kCLS;  // channel groups per warp
     static_assert(TT == kCkptInterval, "one checkpoint per tile");
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float4 *kq4 = reinterpret_cast<float4 *>(smem_raw);                        // [2][TT][SPAD]
     float2 *traj = reinterpret_cast<float2 *>(kq4 + 2 * TT * SPAD);            // [TT*CH*SPT][NTHR]
-    T *vbuf = reinterpret_cast<T *>(traj + TT * CH * SPT * NTHR);              // [2][TT][MC] each
+    float2 *dpart = traj + TT * CH * SPT * NTHR;                               // [TT][LPC][MCP]
+    T *vbuf = reinterpret_cast<T *>(dpart + TT * LPC * MCP);                   // [2][TT][MC] each
     T *lbuf = vbuf + 2 * TT * MC;
     TO *dybuf = reinterpret_cast<TO *>(lbuf + 2 * TT * MC);
     TO *dyvbuf = dybuf + 2 * TT * MC;
@@ -172,16 +173,22 @@ __global__ void __launch_bounds__(NW * 32) kla_bwd_kernel(const BwdParams prm) {
             load_kq(t0 - TT);
             load_ck(tile - 1);
         }
+        const T *lrow = lbuf + cur * TT * MC + cw;
+        const T *vrow = vbuf + cur * TT * MC + cw;
+        const TO *dyrow = dybuf + cur * TT * MC + cw;
+        const TO *dyvrow = dyvbuf + cur * TT * MC + cw;
+        const float4 *kqrow = kq4 + cur * TT * SPAD + j;
+        float2 *drow = dpart + j * MCP + cw;
         auto replay_step = [&](int tt) {
             float lv[CH], vl[CH];
 #pragma unroll
             for (int ci = 0; ci < CH; ++ci) {
-                lv[ci] = to_f32<T>(lbuf[(cur * TT + tt) * MC + cw + ci]);
-                vl[ci] = to_f32<T>(vbuf[(cur * TT + tt) * MC + cw + ci]) * lv[ci];
+                lv[ci] = to_f32<T>(lrow[tt * MC + ci]);
+                vl[ci] = to_f32<T>(vrow[tt * MC + ci]) * lv[ci];
             }
 #pragma unroll
             for (int i = 0; i < SPT; ++i) {
-                const float4 c = kq4[(cur * TT + tt) * SPAD + i * LPC + j];
+                const float4 c = kqrow[tt * SPAD + i * LPC];
 #pragma unroll
                 for (int ci = 0; ci < CH; ++ci) {
                     traj[slot(tt, ci, i, warp, lane)] = make_float2(P[ci][i], mean[ci][i]);
@@ -225,10 +232,10 @@ __global__ void __launch_bounds__(NW * 32) kla_bwd_kernel(const BwdParams prm) {
             float lv[CH], lv2[CH], vv[CH], vl[CH], dy[CH], dyv[CH], dyv2[CH], dvl[CH], dlphi[CH];
 #pragma unroll
             for (int ci = 0; ci < CH; ++ci) {
-                lv[ci] = to_f32<T>(lbuf[(cur * TT + tt) * MC + cw + ci]);
-                vv[ci] = to_f32<T>(vbuf[(cur * TT + tt) * MC + cw + ci]);
-                dy[ci] = to_f32<TO>(dybuf[(cur * TT + tt) * MC + cw + ci]);
-                dyv[ci] = to_f32<TO>(dyvbuf[(cur * TT + tt) * MC + cw + ci]);
+                lv[ci] = to_f32<T>(lrow[tt * MC + ci]);
+                vv[ci] = to_f32<T>(vrow[tt * MC + ci]);
+                dy[ci] = to_f32<TO>(dyrow[tt * MC + ci]);
+                dyv[ci] = to_f32<TO>(dyvrow[tt * MC + ci]);
                 vl[ci] = vv[ci] * lv[ci];
                 lv2[ci] = lv[ci] + lv[ci];
                 dyv2[ci] = dyv[ci] + dyv[ci];
@@ -237,7 +244,7 @@ __global__ void __launch_bounds__(NW * 32) kla_bwd_kernel(const BwdParams prm) {
             }
 #pragma unroll
             for (int i = 0; i < SPT; ++i) {
-                const float4 c = kq4[(cur * TT + tt) * SPAD + i * LPC + j];  // k^2, k, q, q^2
+                const float4 c = kqrow[tt * SPAD + i * LPC];  // k^2, k, q, q^2
                 float X2 = 0.0f, Y = 0.0f, A_ = 0.0f, B2 = 0.0f;
 #pragma unroll
                 for (int ci = 0; ci < CH; ++ci) {
@@ -284,20 +291,9 @@ __global__ void __launch_bounds__(NW * 32) kla_bwd_kernel(const BwdParams prm) {
                 // this thread's share of dk, dq for (t, s): parked where (P', mean') was
                 traj[slot(tt, 0, i, warp, lane)] = make_float2(fmaf(c.y, X2, Y), fmaf(c.z, B2, A_));
             }
+            // this thread's share of the sums over s; summed over lane groups per tile
 #pragma unroll
-            for (int ci = 0; ci < CH; ++ci) {
-#pragma unroll
-                for (int off = LPC / 2; off > 0; off >>= 1) {
-                    dvl[ci] += __shfl_xor_sync(0xffffffffu, dvl[ci], off);
-                    dlphi[ci] += __shfl_xor_sync(0xffffffffu, dlphi[ci], off);
-                }
-                const int m = m_cta + cw + ci;
-                if (j == 0 && m < M) {
-                    // v enters only through v*lambda_v (kla_ops.py:177)
-                    dvb[(long long)(t0 + tt) * prm.dv.st + m] = from_f32<T>(dvl[ci] * lv[ci]);
-                    dlvb[(long long)(t0 + tt) * prm.dlv.st + m] = from_f32<T>(fmaf(dvl[ci], vv[ci], dlphi[ci]));
-                }
-            }
+            for (int ci = 0; ci < CH; ++ci) drow[tt * LPC * MCP + ci] = make_float2(dvl[ci], dlphi[ci]);
         };
         if (n == TT) {
 #pragma unroll
@@ -306,6 +302,20 @@ __global__ void __launch_bounds__(NW * 32) kla_bwd_kernel(const BwdParams prm) {
             for (int tt = n - 1; tt >= 0; --tt) reverse_step(tt);
         }
         __syncthreads();
+
+        // ---- sum the (dv, dlambda_v) partials over lane groups and store them.
+        // v enters only through v*lambda_v (kla_ops.py:177): with D = sum_s rbar k,
+        // dv = D lambda_v and dlambda_v = sum_s phibar k^2 + D v.
+        {
+            const T *lt = lbuf + cur * TT * MC, *vt = vbuf + cur * TT * MC;
+            output_pass<T, LPC, MC, MCP, TT, NTHR>(
+                dpart, dvb + (long long)t0 * prm.dv.st, prm.dv.st, prm.vec_dv,
+                dlvb + (long long)t0 * prm.dlv.st, prm.dlv.st, prm.vec_dlv, n, m_cta, M, tid,
+                [&](float2 acc, int tt, int c, float &o0, float &o1) {
+                    o0 = acc.x * to_f32<T>(lt[tt * MC + c]);
+                    o1 = fmaf(acc.x, to_f32<T>(vt[tt * MC + c]), acc.y);
+                });
+        }
 
         // ---- sum dk, dq over the CTA's channels and add to global memory
         for (int pidx = tid; pidx < n * SPAD; pidx += NTHR) {

@@ -13,9 +13,15 @@ namespace {
 
 using namespace kla;
 
-constexpr int kNW = 4;                 // warps per CTA
+#ifndef KLA_NW
+#define KLA_NW 4
+#endif
+constexpr int kNW = KLA_NW;            // warps per CTA
 constexpr int kTT = kCkptInterval;     // steps per tile
-constexpr int kSPT = 4;                // states per thread
+#ifndef KLA_SPT
+#define KLA_SPT 4
+#endif
+constexpr int kSPT = KLA_SPT;          // states per thread
 constexpr int kCH = 1;                 // channels per thread
 
 std::atomic<long long> g_launches{0};
@@ -37,6 +43,12 @@ int vec_ok(const kla_b200_tensor3 &t, int64_t M) {
     constexpr int VEC = 16 / sizeof(T);
     return t.ptr != nullptr && aligned(t.ptr, 16) && (t.stride_b % VEC) == 0 && (t.stride_t % VEC) == 0 &&
            (M % VEC) == 0;
+}
+
+// Vector stores of 2 output elements are legal when every row start is aligned to them.
+template <typename T>
+int vec2_ok(const kla_b200_tensor3 &t) {
+    return t.ptr != nullptr && aligned(t.ptr, 2 * sizeof(T)) && (t.stride_b % 2) == 0 && (t.stride_t % 2) == 0;
 }
 
 int lpc_for(int64_t S) {
@@ -66,7 +78,8 @@ template <typename T, typename TO, int LPC, bool PRIOR>
 int launch_fwd(const FwdParams &prm, cudaStream_t st) {
     using Sh = ScanShape<kSPT, LPC, kCH, kNW, kTT>;
     auto kern = kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kTT, PRIOR>;
-    const size_t smem = sizeof(float4) * 2 * kTT * Sh::kSPad + sizeof(T) * 4 * kTT * Sh::kMC;
+    const size_t smem = sizeof(float4) * 2 * kTT * Sh::kSPad + sizeof(float2) * 2 * kTT * LPC * Sh::kMCP +
+                        sizeof(T) * 4 * kTT * Sh::kMC;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return cuda_fail(e);
     dim3 grid((unsigned)((prm.M + Sh::kMC - 1) / Sh::kMC), (unsigned)prm.B);
@@ -81,6 +94,7 @@ int launch_bwd(const BwdParams &prm, cudaStream_t st) {
     using Sh = ScanShape<kSPT, LPC, kCH, kNW, kTT>;
     auto kern = kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kTT, PRIOR>;
     const size_t smem = sizeof(float4) * 2 * kTT * Sh::kSPad + sizeof(float2) * kTT * kCH * kSPT * Sh::kThreads +
+                        sizeof(float2) * kTT * LPC * Sh::kMCP +
                         (sizeof(T) + sizeof(TO)) * 4 * kTT * Sh::kMC;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return cuda_fail(e);
@@ -180,6 +194,8 @@ int kla_b200_scan_fwd(const kla_b200_fwd_args *a, void *stream) {
     } else {
         prm.vec_v = vec_ok<__nv_bfloat16>(a->v, a->M); prm.vec_lv = vec_ok<__nv_bfloat16>(a->lambda_v, a->M);
     }
+    prm.vec_y = a->out_dtype == KLA_B200_F32 ? vec2_ok<float>(a->y) : vec2_ok<__nv_bfloat16>(a->y);
+    prm.vec_yv = a->out_dtype == KLA_B200_F32 ? vec2_ok<float>(a->y_var) : vec2_ok<__nv_bfloat16>(a->y_var);
     return dispatch_fwd(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc_for(a->S), prm, st);
 }
 
@@ -242,6 +258,8 @@ int kla_b200_scan_bwd(const kla_b200_bwd_args *a, void *stream) {
     } else {
         prm.vec_dy = vec_ok<__nv_bfloat16>(a->dy, a->M); prm.vec_dyv = vec_ok<__nv_bfloat16>(a->dy_var, a->M);
     }
+    prm.vec_dv = a->in_dtype == KLA_B200_F32 ? vec2_ok<float>(a->dv) : vec2_ok<__nv_bfloat16>(a->dv);
+    prm.vec_dlv = a->in_dtype == KLA_B200_F32 ? vec2_ok<float>(a->dlambda_v) : vec2_ok<__nv_bfloat16>(a->dlambda_v);
     return dispatch_bwd(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc_for(a->S), prm, st);
 }
 
