@@ -148,6 +148,15 @@ int kla_b200_version(void);
  * (memsets are not counted). Used by the benchmark to report its launch count. */
 int64_t kla_b200_launch_count(void);
 
+/*
+ * Device-side status of the kernels launched so far on the current device.
+ * Synchronises with the device. *status is 0 when every kernel ran to the end;
+ * 0x100 | site when a bounded wait inside a kernel (producer/consumer hand-off
+ * between its warps) ran out and the kernel gave up instead of hanging -- the
+ * outputs of that launch are then invalid. Reading a non-zero status clears it.
+ */
+int kla_b200_device_status(int *status);
+
 #ifdef __cplusplus
 }
 #endif

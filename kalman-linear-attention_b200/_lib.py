@@ -23,6 +23,7 @@ SYMBOLS = (
     "kla_b200_strerror",
     "kla_b200_version",
     "kla_b200_launch_count",
+    "kla_b200_device_status",
 )
 
 
@@ -101,8 +102,18 @@ def load() -> ctypes.CDLL:
     lib.kla_b200_strerror.argtypes = [c_int]
     lib.kla_b200_version.restype = c_int
     lib.kla_b200_launch_count.restype = c_int64
+    lib.kla_b200_device_status.restype = c_int
+    lib.kla_b200_device_status.argtypes = [POINTER(c_int)]
     _lib = lib
     return lib
+
+
+def device_status() -> int:
+    """Synchronise and return the device-side status word (0 = every kernel ran to
+    its end; see ``kla_b200_device_status`` in ``include/kla_b200.h``)."""
+    st = c_int(0)
+    check(load().kla_b200_device_status(ctypes.byref(st)))
+    return st.value
 
 
 def check(code: int) -> None:

@@ -2,6 +2,7 @@
 // selection and launches. No torch types, no allocation, no exceptions.
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "../../include/kla_b200.h"
@@ -16,17 +17,26 @@ using namespace kla;
 #ifndef KLA_NW
 #define KLA_NW 4
 #endif
-constexpr int kNW = KLA_NW;            // warps per CTA
+constexpr int kNW = KLA_NW;            // compute warps per CTA
+#ifndef KLA_NH
+#define KLA_NH 4
+#endif
+constexpr int kNH = KLA_NH;            // helper warps per CTA
 constexpr int kTT = kCkptInterval;     // steps per tile
 #ifndef KLA_SPT
 #define KLA_SPT 4
 #endif
 constexpr int kSPT = KLA_SPT;          // states per thread
-constexpr int kCH = 1;                 // channels per thread
+#ifndef KLA_CH
+#define KLA_CH 1
+#endif
+constexpr int kCH = KLA_CH;            // channels per thread
 
 std::atomic<long long> g_launches{0};
 thread_local cudaError_t g_last_cuda = cudaSuccess;
 thread_local char g_errbuf[256];
+// KLA_B200_NO_TMA=1 forces the plain-load staging path (used by the tests to cover it)
+const bool g_no_tma = [] { const char *e = getenv("KLA_B200_NO_TMA"); return e && e[0] == '1'; }();
 
 int cuda_fail(cudaError_t e) {
     g_last_cuda = e;
@@ -37,18 +47,50 @@ Tensor3 t3(const kla_b200_tensor3 &t) { return Tensor3{t.ptr, t.stride_b, t.stri
 
 bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
-// 16-byte staging is legal when every row start of the tensor is 16-byte aligned.
-template <typename T>
-int vec_ok(const kla_b200_tensor3 &t, int64_t M) {
-    constexpr int VEC = 16 / sizeof(T);
-    return t.ptr != nullptr && aligned(t.ptr, 16) && (t.stride_b % VEC) == 0 && (t.stride_t % VEC) == 0 &&
-           (M % VEC) == 0;
-}
-
 // Vector stores of 2 output elements are legal when every row start is aligned to them.
 template <typename T>
 int vec2_ok(const kla_b200_tensor3 &t) {
     return t.ptr != nullptr && aligned(t.ptr, 2 * sizeof(T)) && (t.stride_b % 2) == 0 && (t.stride_t % 2) == 0;
+}
+
+// cuTensorMapEncodeTiled is fetched from the driver at run time, so the library
+// links against the CUDA runtime only.
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// Rank-3 tensor map over a [B, L, M] activation tensor, dims (M, L, B), box
+// (box_m, box_t, 1). Returns false when the tensor does not meet the TMA rules
+// (16-byte aligned base and strides); the kernels then stage with plain loads.
+template <typename T>
+bool make_tile_map(CUtensorMap *tm, const kla_b200_tensor3 &t, int64_t B, int64_t L, int64_t M, int box_m, int box_t) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (enc == nullptr || t.ptr == nullptr || B <= 0 || L <= 0 || M <= 0) return false;
+    // size-1 dimensions may carry arbitrary strides; give them the dense value
+    const int64_t st = L > 1 ? t.stride_t : M;
+    const int64_t sb = B > 1 ? t.stride_b : L * st;
+    const uint64_t st_b = (uint64_t)st * sizeof(T), sb_b = (uint64_t)sb * sizeof(T);
+    if (!aligned(t.ptr, 16) || st_b % 16 || sb_b % 16 || st < M || st_b >= (1ull << 40) || sb_b >= (1ull << 40))
+        return false;
+    if ((box_m * sizeof(T)) % 16 || box_m > 256 || box_t > 256) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)M, (cuuint64_t)L, (cuuint64_t)B};
+    const cuuint64_t strides[2] = {st_b, sb_b};
+    const cuuint32_t box[3] = {(cuuint32_t)box_m, (cuuint32_t)box_t, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUtensorMapDataType dt = sizeof(T) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    return enc(tm, dt, 3, t.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 int lpc_for(int64_t S) {
@@ -75,31 +117,34 @@ int check_t3(const kla_b200_tensor3 &t, size_t esz, bool required) {
 }
 
 template <typename T, typename TO, int LPC, bool PRIOR>
-int launch_fwd(const FwdParams &prm, cudaStream_t st) {
-    using Sh = ScanShape<kSPT, LPC, kCH, kNW, kTT>;
-    auto kern = kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kTT, PRIOR>;
-    const size_t smem = sizeof(float4) * 2 * kTT * Sh::kSPad + sizeof(float2) * 2 * kTT * LPC * Sh::kMCP +
-                        sizeof(T) * 4 * kTT * Sh::kMC;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+int launch_fwd(FwdParams &prm, const kla_b200_fwd_args &a, cudaStream_t st) {
+    using Sh = ScanShape<kSPT, LPC, kCH, kNW, kNH, kTT>;
+    using Sm = FwdSmem<T, kSPT, LPC, kCH, kNW, kNH, kTT>;
+    auto kern = kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR>;
+    prm.use_tma = !g_no_tma && make_tile_map<T>(&prm.tm_v, a.v, a.B, a.L, a.M, Sh::kMC, kTT) &&
+                  make_tile_map<T>(&prm.tm_lv, a.lambda_v, a.B, a.L, a.M, Sh::kMC, kTT);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sm::kTotal);
     if (e != cudaSuccess) return cuda_fail(e);
     dim3 grid((unsigned)((prm.M + Sh::kMC - 1) / Sh::kMC), (unsigned)prm.B);
-    kern<<<grid, Sh::kThreads, smem, st>>>(prm);
+    kern<<<grid, Sh::kThreads, Sm::kTotal, st>>>(prm);
     g_launches++;
     e = cudaGetLastError();
     return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
 }
 
 template <typename T, typename TO, int LPC, bool PRIOR>
-int launch_bwd(const BwdParams &prm, cudaStream_t st) {
-    using Sh = ScanShape<kSPT, LPC, kCH, kNW, kTT>;
-    auto kern = kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kTT, PRIOR>;
-    const size_t smem = sizeof(float4) * 2 * kTT * Sh::kSPad + sizeof(float2) * kTT * kCH * kSPT * Sh::kThreads +
-                        sizeof(float2) * kTT * LPC * Sh::kMCP +
-                        (sizeof(T) + sizeof(TO)) * 4 * kTT * Sh::kMC;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+int launch_bwd(BwdParams &prm, const kla_b200_bwd_args &a, cudaStream_t st) {
+    using Sh = ScanShape<kSPT, LPC, kCH, kNW, kNH, kTT>;
+    using Sm = BwdSmem<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT>;
+    auto kern = kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR>;
+    prm.use_tma = !g_no_tma && make_tile_map<T>(&prm.tm_v, a.v, a.B, a.L, a.M, Sh::kMC, kTT) &&
+                  make_tile_map<T>(&prm.tm_lv, a.lambda_v, a.B, a.L, a.M, Sh::kMC, kTT) &&
+                  make_tile_map<TO>(&prm.tm_dy, a.dy, a.B, a.L, a.M, Sh::kMC, kTT) &&
+                  (a.dy_var.ptr == nullptr || make_tile_map<TO>(&prm.tm_dyv, a.dy_var, a.B, a.L, a.M, Sh::kMC, kTT));
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sm::kTotal);
     if (e != cudaSuccess) return cuda_fail(e);
     dim3 grid((unsigned)((prm.M + Sh::kMC - 1) / Sh::kMC), (unsigned)prm.B);
-    kern<<<grid, Sh::kThreads, smem, st>>>(prm);
+    kern<<<grid, Sh::kThreads, Sm::kTotal, st>>>(prm);
     g_launches++;
     e = cudaGetLastError();
     return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
@@ -142,11 +187,11 @@ int launch_step(const StepParams &prm, cudaStream_t st) {
         }                                                                                    \
     } while (0)
 
-int dispatch_fwd(int din, int dout, bool prior, int lpc, const FwdParams &prm, cudaStream_t st) {
-    KLA_DISPATCH(launch_fwd, din, dout, prior, lpc, prm, st);
+int dispatch_fwd(int din, int dout, bool prior, int lpc, FwdParams &prm, const kla_b200_fwd_args &a, cudaStream_t st) {
+    KLA_DISPATCH(launch_fwd, din, dout, prior, lpc, prm, a, st);
 }
-int dispatch_bwd(int din, int dout, bool prior, int lpc, const BwdParams &prm, cudaStream_t st) {
-    KLA_DISPATCH(launch_bwd, din, dout, prior, lpc, prm, st);
+int dispatch_bwd(int din, int dout, bool prior, int lpc, BwdParams &prm, const kla_b200_bwd_args &a, cudaStream_t st) {
+    KLA_DISPATCH(launch_bwd, din, dout, prior, lpc, prm, a, st);
 }
 int dispatch_step(int din, int dout, bool prior, int lpc, const StepParams &prm, cudaStream_t st) {
     KLA_DISPATCH(launch_step, din, dout, prior, lpc, prm, st);
@@ -189,14 +234,9 @@ int kla_b200_scan_fwd(const kla_b200_fwd_args *a, void *stream) {
     prm.a = a->a; prm.p = a->p; prm.lam0 = a->lam0; prm.eta0 = a->eta0;
     prm.lam_fin = a->lam_fin; prm.eta_fin = a->eta_fin;
     prm.ckpt = static_cast<float2 *>(a->ckpt);
-    if (a->in_dtype == KLA_B200_F32) {
-        prm.vec_v = vec_ok<float>(a->v, a->M); prm.vec_lv = vec_ok<float>(a->lambda_v, a->M);
-    } else {
-        prm.vec_v = vec_ok<__nv_bfloat16>(a->v, a->M); prm.vec_lv = vec_ok<__nv_bfloat16>(a->lambda_v, a->M);
-    }
     prm.vec_y = a->out_dtype == KLA_B200_F32 ? vec2_ok<float>(a->y) : vec2_ok<__nv_bfloat16>(a->y);
     prm.vec_yv = a->out_dtype == KLA_B200_F32 ? vec2_ok<float>(a->y_var) : vec2_ok<__nv_bfloat16>(a->y_var);
-    return dispatch_fwd(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc_for(a->S), prm, st);
+    return dispatch_fwd(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc_for(a->S), prm, *a, st);
 }
 
 int kla_b200_scan_bwd(const kla_b200_bwd_args *a, void *stream) {
@@ -248,19 +288,9 @@ int kla_b200_scan_bwd(const kla_b200_bwd_args *a, void *stream) {
     prm.dlam_fin = a->dlam_fin; prm.deta_fin = a->deta_fin;
     prm.dk = a->dk; prm.dq = a->dq; prm.da = a->da; prm.dp = a->dp;
     prm.dlam0 = a->dlam0; prm.deta0 = a->deta0;
-    if (a->in_dtype == KLA_B200_F32) {
-        prm.vec_v = vec_ok<float>(a->v, a->M); prm.vec_lv = vec_ok<float>(a->lambda_v, a->M);
-    } else {
-        prm.vec_v = vec_ok<__nv_bfloat16>(a->v, a->M); prm.vec_lv = vec_ok<__nv_bfloat16>(a->lambda_v, a->M);
-    }
-    if (a->out_dtype == KLA_B200_F32) {
-        prm.vec_dy = vec_ok<float>(a->dy, a->M); prm.vec_dyv = vec_ok<float>(a->dy_var, a->M);
-    } else {
-        prm.vec_dy = vec_ok<__nv_bfloat16>(a->dy, a->M); prm.vec_dyv = vec_ok<__nv_bfloat16>(a->dy_var, a->M);
-    }
     prm.vec_dv = a->in_dtype == KLA_B200_F32 ? vec2_ok<float>(a->dv) : vec2_ok<__nv_bfloat16>(a->dv);
     prm.vec_dlv = a->in_dtype == KLA_B200_F32 ? vec2_ok<float>(a->dlambda_v) : vec2_ok<__nv_bfloat16>(a->dlambda_v);
-    return dispatch_bwd(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc_for(a->S), prm, st);
+    return dispatch_bwd(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc_for(a->S), prm, *a, st);
 }
 
 int kla_b200_step(const kla_b200_step_args *a, void *stream) {
@@ -302,5 +332,17 @@ const char *kla_b200_strerror(int code) {
 int kla_b200_version(void) { return 100; }
 
 int64_t kla_b200_launch_count(void) { return g_launches.load(); }
+
+int kla_b200_device_status(int *status) {
+    if (status == nullptr) return KLA_B200_EINVAL;
+    int zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(status, g_kla_status, sizeof(int));
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (*status != 0) {
+        e = cudaMemcpyToSymbol(g_kla_status, &zero, sizeof(int));
+        if (e != cudaSuccess) return cuda_fail(e);
+    }
+    return KLA_B200_OK;
+}
 
 }  // extern "C"

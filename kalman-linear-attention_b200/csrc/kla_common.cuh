@@ -4,14 +4,16 @@
 // channel m, state s) lane of the filter; chains never interact except through
 // the read-out sum over s and the gradient sums over m, b and t.
 //
-//   * a thread owns CH consecutive channels x SPT states: CH*SPT chains whose
-//     state lives in registers for the whole sequence;
+//   * a compute thread owns CH consecutive channels x SPT states: CH*SPT chains
+//     whose state lives in registers for the whole sequence;
 //   * LPC consecutive lanes of a warp share a channel group; lane j of such a
 //     group owns states s = i*LPC + j, i = 0..SPT-1, so S is padded to
-//     SPAD = SPT*LPC and sums over s finish with log2(LPC) shuffle rounds;
-//   * a warp therefore covers (32/LPC)*CH channels and a CTA of NW warps covers
-//     MC = NW*(32/LPC)*CH channels of one batch element; time is the serial axis
-//     and is walked in tiles of TT steps staged through shared memory.
+//     SPAD = SPT*LPC and sums over s are LPC partial sums per channel;
+//   * a warp therefore covers (32/LPC)*CH channels and a CTA with NW compute
+//     warps covers MC = NW*(32/LPC)*CH channels of one batch element; time is
+//     the serial axis and is walked in tiles of TT steps staged through shared
+//     memory by a second group of NH helper warps (loads, sums of partials,
+//     stores), so the compute warps never wait on global memory.
 //
 // The recurrence is carried in variance form, which is the same filter as the
 // reference's information form (src/kla/ops/kla_ops.py:9-14) with P = 1/lambda
@@ -27,6 +29,7 @@
 // directly.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -38,32 +41,67 @@ constexpr float kPMin = 1e-12f;     // P_MIN, src/kla/ops/kla_ops.py:44
 constexpr float kLamMin = 1e-20f;   // floor on a carried-in precision before 1/lambda
 constexpr int kCkptInterval = 16;   // steps between checkpoints of the filter state
 
+// Device-side status word: 0 = ok, otherwise the code of the first bounded wait
+// that ran out (kStatusWait | site). Read back by kla_b200_device_status().
+constexpr int kStatusWait = 0x100;
+
 struct Tensor3 {
     void *ptr;
     long long sb, st;  // batch and time strides, in elements
 };
 
+template <int SPT, int LPC, int CH, int NW, int NH, int TT>
+struct ScanShape {
+    static constexpr int kSPad = SPT * LPC;
+    static constexpr int kCLS = 32 / LPC;         // channel groups per warp
+    static constexpr int kCPW = kCLS * CH;        // channels per warp
+    static constexpr int kMC = NW * kCPW;         // channels per CTA
+    static constexpr int kCompute = NW * 32;      // compute threads
+    static constexpr int kHelpers = NH * 32;      // helper threads
+    static constexpr int kThreads = kCompute + kHelpers;
+    // Row length of the [TT][LPC][MCP] float2 partial-sum buffers. 8-byte
+    // shared-memory accesses are served half a warp at a time; a half-warp
+    // writes LPC rows of kCPW/2 channels each, so rows are offset by kCPW/2
+    // channels modulo the 16 channels (32 banks) a wavefront covers.
+    static constexpr int kHalf = kCPW / 2 > 0 ? kCPW / 2 : 1;
+    static constexpr int kPadRaw = ((kHalf - kMC) % 16 + 16) % 16;
+    static constexpr int kMCP = kMC + kPadRaw + (kPadRaw & 1);
+    static_assert(kMC % 2 == 0, "the output pass works on pairs of channels");
+};
+
 __device__ __forceinline__ float rcp_approx(float x) {
+#ifdef KLA_KO_RCP
+    return 2.0f - x;
+#else
     float y;
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+#endif
 }
 
-// One predict+update step of one chain. Explicit intrinsics pin the rounding so
-// that the backward's replay reproduces the forward bit for bit.
-struct StepOut {
-    float Pp, g;
-};
-__device__ __forceinline__ StepOut chain_step(float &P, float &mean, float phi, float r,
-                                              float a, float a2, float p) {
-    StepOut o;
-    o.Pp = __fmaf_rn(a2, P, p);
-    const float d = __fmaf_rn(phi, o.Pp, 1.0f);
-    o.g = rcp_approx(d);
-    P = __fmul_rn(o.Pp, o.g);
-    const float u = __fmaf_rn(o.Pp, r, __fmul_rn(a, mean));
-    mean = __fmul_rn(o.g, u);
-    return o;
+// One predict+update step of one chain, in pieces so that callers can put the
+// reciprocals of several independent chains in flight together. Explicit
+// intrinsics pin the rounding so that the backward's replay reproduces the
+// forward bit for bit.
+//
+// chain_inputs: phi = lambda_v k^2 and r = (v lambda_v) k from one product
+// lambda_v k, so that only k itself has to come from shared memory.
+__device__ __forceinline__ void chain_inputs(float lv, float v, float k, float &phi, float &r) {
+    const float lk = __fmul_rn(lv, k);
+    phi = __fmul_rn(lk, k);
+    r = __fmul_rn(v, lk);
+}
+// chain_denominator: Pp = a2 P + p and d = 1 + phi Pp. d is evaluated as
+// (a2 phi) P + (phi p + 1): the same value with one FMA, not two, between the
+// carried P and the reciprocal, which is what bounds the serial chain.
+__device__ __forceinline__ float chain_denominator(float P, float phi, float a2, float p, float &Pp) {
+    Pp = __fmaf_rn(a2, P, p);
+    return __fmaf_rn(__fmul_rn(a2, phi), P, __fmaf_rn(phi, p, 1.0f));
+}
+// chain_update: P = Pp g, mean = g (a mean' + Pp r), with g = 1/d.
+__device__ __forceinline__ void chain_update(float &P, float &mean, float Pp, float g, float r, float a) {
+    P = __fmul_rn(Pp, g);
+    mean = __fmul_rn(g, __fmaf_rn(Pp, r, __fmul_rn(a, mean)));
 }
 
 template <typename T>
@@ -80,43 +118,141 @@ __device__ __forceinline__ float from_f32<float>(float x) { return x; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
-__device__ __forceinline__ void cp_async_16(void *smem, const void *gmem) {
-    const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+// ---------------------------------------------------------------- mbarrier + TMA
+//
+// Producer/consumer hand-off between helper and compute warps uses mbarrier
+// objects in shared memory; tile loads use the tensor-map form of the bulk
+// async copy (TMA), which signals the same mbarrier with its byte count.
+
+__device__ int g_kla_status = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
-__device__ __forceinline__ void cp_async_4(void *smem, const void *gmem) {
-    const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gmem) : "memory");
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
-__device__ __forceinline__ void cp_async_wait_all() {
-    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait. A waiting warp sleeps between polls so that it does not take
+// issue slots from the warps that are computing on the same scheduler. After
+// about a second of polling it gives up, records where in g_kla_status and
+// returns false; the caller then leaves its loop so that the CTA ends instead
+// of hanging the device.
+constexpr uint32_t kSpinLimit = 1u << 22;
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int site) {
+    if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        __nanosleep(200);
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    atomicCAS(&g_kla_status, 0, kStatusWait | site);
+    return false;
+}
+// generic-proxy writes to shared memory -> visible to the async proxy (TMA)
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// TMA: tile (x: channel, y: time, z: batch) of a rank-3 tensor map -> shared memory
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *tm, int x, int y, int z, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
+// untiled bulk copy global -> shared (16-byte aligned, size a multiple of 16)
+__device__ __forceinline__ void bulk_load_1d(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
 }
 
-// Stage a [TT x MC] tile of a [B, L, M] tensor (rows t0.., columns m0..) into
-// shared memory as T, zero-filling rows past L and columns past M. `vec` says
-// that 16-byte copies are legal for this tensor (base and strides aligned, M a
-// multiple of the vector width).
+// Named barrier over a subset of the CTA's warps (id 1..15).
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Cooperative fallback staging of a [TT x MC] tile (rows t0.., columns m0..) by
+// NTHR threads with plain loads, zero-filling rows past L and columns past M;
+// used when a tensor does not meet the tensor-map alignment rules.
 template <typename T, int TT, int MC, int NTHR>
-__device__ __forceinline__ void stage_tile(T *smem, const T *base, long long st, int t0, int L,
-                                           int m0, int M, bool vec, int tid) {
-    constexpr int VEC = 16 / sizeof(T);
-    if (vec && (MC % VEC) == 0) {
-        constexpr int CPR = (MC / VEC) > 0 ? (MC / VEC) : 1;  // chunks per row
-        for (int idx = tid; idx < TT * CPR; idx += NTHR) {
-            const int row = idx / CPR, c = (idx % CPR) * VEC;
-            T *dst = smem + row * MC + c;
-            if (t0 + row < L && m0 + c < M) {
-                cp_async_16(dst, base + (long long)(t0 + row) * st + m0 + c);
-            } else {
-                *reinterpret_cast<uint4 *>(dst) = make_uint4(0, 0, 0, 0);
-            }
+__device__ __forceinline__ void stage_tile_plain(T *smem, const T *base, long long st, int t0, int L, int m0, int M,
+                                                 int tid) {
+    for (int idx = tid; idx < TT * MC; idx += NTHR) {
+        const int row = idx / MC, c = idx % MC;
+        T v = from_f32<T>(0.0f);
+        if (t0 + row < L && m0 + c < M) v = base[(long long)(t0 + row) * st + m0 + c];
+        smem[row * MC + c] = v;
+    }
+}
+
+// Sum the per-lane-group partials of one tile over the LPC lane groups and
+// write two [rows x MC] output tiles. part: [TT][LPC][MCP] float2 in shared
+// memory. Each thread handles pairs of channels, so consecutive lanes read
+// consecutive 16-byte words. FIN maps (sum.x, sum.y, tt, channel) to the two
+// output values. vec0/vec1: 2-element vector stores are legal for that output.
+template <typename TO, int LPC, int MC, int MCP, int TT, int NTHR, typename Fin>
+__device__ __forceinline__ void output_pass(const float2 *part, TO *o0, long long st0, int vec0, TO *o1,
+                                            long long st1, int vec1, int nrows, int m0, int M, int tid, Fin fin) {
+#pragma unroll
+    for (int u0 = 0; u0 < TT * (MC / 2); u0 += NTHR) {
+        const int u = u0 + tid;
+        const int tt = u / (MC / 2), c = (u % (MC / 2)) * 2;
+        if (u >= TT * (MC / 2) || tt >= nrows || m0 + c >= M) continue;
+        float ax = 0.0f, ay = 0.0f, bx = 0.0f, by = 0.0f;
+#pragma unroll
+        for (int jj = 0; jj < LPC; ++jj) {
+            const float4 x = *reinterpret_cast<const float4 *>(part + (tt * LPC + jj) * MCP + c);
+            ax += x.x; ay += x.y; bx += x.z; by += x.w;
         }
-    } else {
-        for (int idx = tid; idx < TT * MC; idx += NTHR) {
-            const int row = idx / MC, c = idx % MC;
-            T v = from_f32<T>(0.0f);
-            if (t0 + row < L && m0 + c < M) v = base[(long long)(t0 + row) * st + m0 + c];
-            smem[row * MC + c] = v;
+        float r0[2], r1[2];
+        fin(make_float2(ax, ay), tt, c, r0[0], r1[0]);
+        fin(make_float2(bx, by), tt, c + 1, r0[1], r1[1]);
+        TO *p0 = o0 + (long long)tt * st0 + m0 + c;
+        TO *p1 = o1 + (long long)tt * st1 + m0 + c;
+        const bool full = m0 + c + 1 < M;
+        if (full && vec0) {
+            if constexpr (sizeof(TO) == 4) {
+                *reinterpret_cast<float2 *>(p0) = make_float2(r0[0], r0[1]);
+            } else {
+                *reinterpret_cast<__nv_bfloat162 *>(p0) = __floats2bfloat162_rn(r0[0], r0[1]);
+            }
+        } else {
+            p0[0] = from_f32<TO>(r0[0]);
+            if (full) p0[1] = from_f32<TO>(r0[1]);
+        }
+        if (full && vec1) {
+            if constexpr (sizeof(TO) == 4) {
+                *reinterpret_cast<float2 *>(p1) = make_float2(r1[0], r1[1]);
+            } else {
+                *reinterpret_cast<__nv_bfloat162 *>(p1) = __floats2bfloat162_rn(r1[0], r1[1]);
+            }
+        } else {
+            p1[0] = from_f32<TO>(r1[0]);
+            if (full) p1[1] = from_f32<TO>(r1[1]);
         }
     }
 }

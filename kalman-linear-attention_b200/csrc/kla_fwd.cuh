@@ -5,255 +5,317 @@
 // posterior and the read-out all live in registers. Per token the kernel reads
 // v, lambda_v (2M) and k, q (2S, once per CTA of MC channels) and writes y,
 // y_var (2M).
+//
+// The CTA is split into NW compute warps and NH helper warps.
+//   compute warps  run the recurrence only: per step they read their inputs
+//                  from a shared-memory stage and leave their share of the
+//                  read-out sums (over their SPT states) in shared memory;
+//   helper warps   feed them: TMA tile loads of v and lambda_v (one elected
+//                  thread), (k, q) interleaving, and per finished tile the sum
+//                  of the LPC partial read-outs and the stores of y, y_var.
+// Stages are handed over with mbarriers, so the compute warps see neither
+// global-memory latency nor a CTA-wide barrier inside the time loop.
 #pragma once
 
 #include "kla_common.cuh"
 
 namespace kla {
 
-struct FwdParams {
+constexpr int kInStages = 3;   // input stages in flight
+constexpr int kOutStages = 2;  // read-out partial buffers
+
+struct alignas(64) FwdParams {
+    CUtensorMap tm_v, tm_lv;  // rank-3 (M, L, B) maps with box (MC, TT, 1); valid when use_tma
     int B, L, M, S, NT;
+    int use_tma;
     Tensor3 v, lv, k, q, y, yv;
     const float *a, *p, *lam0, *eta0;
     float *lam_fin, *eta_fin;
     float2 *ckpt;  // [B, NT, M, S] (P, mean) at the start of each tile, or nullptr
-    int vec_v, vec_lv, vec_y, vec_yv;
+    int vec_y, vec_yv;
 };
 
-template <int SPT, int LPC, int CH, int NW, int TT>
-struct ScanShape {
-    static constexpr int kSPad = SPT * LPC;
-    static constexpr int kCLS = 32 / LPC;         // channel groups per warp
-    static constexpr int kCPW = kCLS * CH;        // channels per warp
-    static constexpr int kMC = NW * kCPW;         // channels per CTA
-    static constexpr int kThreads = NW * 32;
-    static constexpr int kKqPer = (TT * kSPad + kThreads - 1) / kThreads;
-    // Row length of the [TT][LPC][MCP] float2 partial-sum buffers. 8-byte
-    // shared-memory accesses are served half a warp at a time; a half-warp
-    // writes LPC rows of kCPW/2 channels each, so rows are offset by kCPW/2
-    // channels modulo the 16 channels (32 banks) a wavefront covers.
-    static constexpr int kHalf = kCPW / 2 > 0 ? kCPW / 2 : 1;
-    static constexpr int kPadRaw = ((kHalf - kMC) % 16 + 16) % 16;
-    static constexpr int kMCP = kMC + kPadRaw + (kPadRaw & 1);
-    static_assert(kMC % 2 == 0, "the output pass works on pairs of channels");
+// Shared-memory carve-up, shared by the kernel and the launcher.
+template <typename T, int SPT, int LPC, int CH, int NW, int NH, int TT>
+struct FwdSmem {
+    using Sh = ScanShape<SPT, LPC, CH, NW, NH, TT>;
+    static constexpr size_t kBars = 128;
+    static constexpr size_t kTile = ((sizeof(T) * TT * Sh::kMC + 127) / 128) * 128;   // one of v / lambda_v
+    static constexpr size_t kKq = ((sizeof(float2) * TT * Sh::kSPad + 127) / 128) * 128;
+    static constexpr size_t kIn = 2 * kTile + kKq;
+    static constexpr size_t kOut = ((sizeof(float2) * TT * LPC * Sh::kMCP + 127) / 128) * 128;
+    static constexpr size_t kTotal = kBars + kInStages * kIn + kOutStages * kOut;
 };
 
-// Sum the per-lane-group partials of one tile over the LPC lane groups and
-// write two [rows x MC] output tiles. part: [TT][LPC][MCP] float2 in shared
-// memory. Each thread handles pairs of channels, so consecutive lanes read
-// consecutive 16-byte words. FIN maps (sum.x, sum.y, tt, channel) to the two
-// output values. vec0/vec1: 2-element vector stores are legal for that output.
-template <typename TO, int LPC, int MC, int MCP, int TT, int NTHR, typename Fin>
-__device__ __forceinline__ void output_pass(const float2 *part, TO *o0, long long st0, int vec0, TO *o1,
-                                            long long st1, int vec1, int nrows, int m0, int M, int tid, Fin fin) {
-#pragma unroll
-    for (int u0 = 0; u0 < TT * (MC / 2); u0 += NTHR) {
-        const int u = u0 + tid;
-        const int tt = u / (MC / 2), c = (u % (MC / 2)) * 2;
-        if (u >= TT * (MC / 2) || tt >= nrows || m0 + c >= M) continue;
-        float ax = 0.0f, ay = 0.0f, bx = 0.0f, by = 0.0f;
-#pragma unroll
-        for (int jj = 0; jj < LPC; ++jj) {
-            const float4 x = *reinterpret_cast<const float4 *>(part + (tt * LPC + jj) * MCP + c);
-            ax += x.x; ay += x.y; bx += x.z; by += x.w;
-        }
-        float r0[2], r1[2];
-        fin(make_float2(ax, ay), tt, c, r0[0], r1[0]);
-        fin(make_float2(bx, by), tt, c + 1, r0[1], r1[1]);
-        TO *p0 = o0 + (long long)tt * st0 + m0 + c;
-        TO *p1 = o1 + (long long)tt * st1 + m0 + c;
-        const bool full = m0 + c + 1 < M;
-        if (full && vec0) {
-            if constexpr (sizeof(TO) == 4) {
-                *reinterpret_cast<float2 *>(p0) = make_float2(r0[0], r0[1]);
-            } else {
-                *reinterpret_cast<__nv_bfloat162 *>(p0) = __floats2bfloat162_rn(r0[0], r0[1]);
-            }
-        } else {
-            p0[0] = from_f32<TO>(r0[0]);
-            if (full) p0[1] = from_f32<TO>(r0[1]);
-        }
-        if (full && vec1) {
-            if constexpr (sizeof(TO) == 4) {
-                *reinterpret_cast<float2 *>(p1) = make_float2(r1[0], r1[1]);
-            } else {
-                *reinterpret_cast<__nv_bfloat162 *>(p1) = __floats2bfloat162_rn(r1[0], r1[1]);
-            }
-        } else {
-            p1[0] = from_f32<TO>(r1[0]);
-            if (full) p1[1] = from_f32<TO>(r1[1]);
-        }
-    }
-}
-
-template <typename T, typename TO, int SPT, int LPC, int CH, int NW, int TT, bool PRIOR>
-__global__ void __launch_bounds__(NW * 32) kla_fwd_kernel(const FwdParams prm) {
-    using Sh = ScanShape<SPT, LPC, CH, NW, TT>;
-    constexpr int SPAD = Sh::kSPad, MC = Sh::kMC, MCP = Sh::kMCP, NTHR = Sh::kThreads, KQ = Sh::kKqPer;
+template <typename T, typename TO, int SPT, int LPC, int CH, int NW, int NH, int TT, bool PRIOR>
+__global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_constant__ FwdParams prm) {
+    using Sh = ScanShape<SPT, LPC, CH, NW, NH, TT>;
+    using Sm = FwdSmem<T, SPT, LPC, CH, NW, NH, TT>;
+    constexpr int SPAD = Sh::kSPad, MC = Sh::kMC, MCP = Sh::kMCP;
+    constexpr int NS = kInStages, NO = kOutStages;
     static_assert(TT == kCkptInterval, "one checkpoint per tile");
 
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    float4 *kq4 = reinterpret_cast<float4 *>(smem_raw);                 // [2][TT][SPAD]
-    float2 *ypart = reinterpret_cast<float2 *>(kq4 + 2 * TT * SPAD);    // [2][TT][LPC][MCP]
-    T *vbuf = reinterpret_cast<T *>(ypart + 2 * TT * LPC * MCP);        // [2][TT][MC]
-    T *lbuf = vbuf + 2 * TT * MC;                                       // [2][TT][MC]
+    // Declared with its alignment (no run-time rounding of the pointer) so that
+    // the compiler keeps every access below in the shared address space.
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t *full_in = reinterpret_cast<uint64_t *>(smem);  // [NS]
+    uint64_t *empty_in = full_in + NS;                       // [NS]
+    uint64_t *full_out = empty_in + NS;                      // [NO]
+    uint64_t *empty_out = full_out + NO;                     // [NO]
+    unsigned char *in_base = smem + Sm::kBars;
+    unsigned char *out_base = in_base + NS * Sm::kIn;
+    auto vstage = [&](int s) { return reinterpret_cast<T *>(in_base + s * Sm::kIn); };
+    auto lstage = [&](int s) { return reinterpret_cast<T *>(in_base + s * Sm::kIn + Sm::kTile); };
+    auto kqstage = [&](int s) { return reinterpret_cast<float2 *>(in_base + s * Sm::kIn + 2 * Sm::kTile); };
+    auto ystage = [&](int o) { return reinterpret_cast<float2 *>(out_base + o * Sm::kOut); };
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int j = lane % LPC, cl = lane / LPC;
     const int b = blockIdx.y;
     const int m_cta = blockIdx.x * MC;
-    const int cw = warp * Sh::kCPW + cl * CH;  // first channel of this thread, CTA-relative
-    const int L = prm.L, M = prm.M, S = prm.S;
+    const int L = prm.L, M = prm.M, S = prm.S, NT = prm.NT;
 
-    const T *vb = static_cast<const T *>(prm.v.ptr) + (long long)b * prm.v.sb;
-    const T *lb = static_cast<const T *>(prm.lv.ptr) + (long long)b * prm.lv.sb;
-    const T *kb = static_cast<const T *>(prm.k.ptr) + (long long)b * prm.k.sb;
-    const T *qb = static_cast<const T *>(prm.q.ptr) + (long long)b * prm.q.sb;
-    TO *yb = static_cast<TO *>(prm.y.ptr) + (long long)b * prm.y.sb;
-    TO *yvb = static_cast<TO *>(prm.yv.ptr) + (long long)b * prm.yv.sb;
-
-    // Per-chain constants and state. Padding chains (s >= S or m >= M) get
-    // a = 0, p = 1, so their variance sits at 1 and their mean at 0.
-    float ca[CH][SPT], ca2[CH][SPT], cp[CH][SPT], P[CH][SPT], mean[CH][SPT];
-#pragma unroll
-    for (int ci = 0; ci < CH; ++ci) {
-        const int m = m_cta + cw + ci;
-#pragma unroll
-        for (int i = 0; i < SPT; ++i) {
-            const int s = i * LPC + j;
-            const bool live = (m < M) && (s < S);
-            const float av = live ? prm.a[(long long)m * S + s] : 0.0f;
-            const float pv = live ? prm.p[(long long)m * S + s] : 1.0f;
-            ca[ci][i] = av;
-            ca2[ci][i] = live ? fmaxf(av * av, kEps) : 0.0f;
-            cp[ci][i] = fmaxf(pv, kPMin);
-            float lam = 1.0f, eta = 0.0f;
-            if (live && prm.lam0 != nullptr) {
-                lam = prm.lam0[((long long)b * M + m) * S + s];
-                eta = prm.eta0[((long long)b * M + m) * S + s];
-            }
-            const float P0 = 1.0f / fmaxf(lam, kLamMin);
-            P[ci][i] = P0;
-            mean[ci][i] = eta * P0;
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(&full_in[s], Sh::kHelpers);
+            mbar_init(&empty_in[s], NW);
         }
+        for (int o = 0; o < NO; ++o) {
+            mbar_init(&full_out[o], NW);
+            mbar_init(&empty_out[o], NH);
+        }
+        mbar_fence_init();
     }
-
-    float kreg[KQ], qreg[KQ];
-    auto load_kq = [&](int t0) {
-#pragma unroll
-        for (int e = 0; e < KQ; ++e) {
-            const int idx = tid + e * NTHR;
-            const int row = idx / SPAD, s = idx % SPAD;
-            float kv = 0.0f, qv = 0.0f;
-            if (idx < TT * SPAD && s < S && t0 + row < L) {
-                kv = to_f32<T>(kb[(long long)(t0 + row) * prm.k.st + s]);
-                qv = to_f32<T>(qb[(long long)(t0 + row) * prm.q.st + s]);
-            }
-            kreg[e] = kv;
-            qreg[e] = qv;
-        }
-    };
-    auto store_kq = [&](int buf) {
-#pragma unroll
-        for (int e = 0; e < KQ; ++e) {
-            const int idx = tid + e * NTHR;
-            if (idx < TT * SPAD)
-                kq4[buf * TT * SPAD + idx] = make_float4(kreg[e] * kreg[e], kreg[e], qreg[e], qreg[e] * qreg[e]);
-        }
-    };
-
-    // One time step for every chain of this thread; the per-thread share of the
-    // read-out goes to shared memory and is summed over lane groups per tile.
-    auto step = [&](const T *lrow, const T *vrow, const float4 *kqrow, float2 *yrow, int tt) {
-        float lv[CH], vl[CH], ys[CH], yvs[CH];
-#pragma unroll
-        for (int ci = 0; ci < CH; ++ci) {
-            lv[ci] = to_f32<T>(lrow[tt * MC + ci]);
-            vl[ci] = to_f32<T>(vrow[tt * MC + ci]) * lv[ci];
-            ys[ci] = 0.0f;
-            yvs[ci] = 0.0f;
-        }
-#pragma unroll
-        for (int i = 0; i < SPT; ++i) {
-            const float4 c = kqrow[tt * SPAD + i * LPC];  // k^2, k, q, q^2
-#pragma unroll
-            for (int ci = 0; ci < CH; ++ci) {
-                const float phi = __fmul_rn(lv[ci], c.x);
-                const float r = __fmul_rn(vl[ci], c.y);
-                chain_step(P[ci][i], mean[ci][i], phi, r, ca[ci][i], ca2[ci][i], cp[ci][i]);
-                if (PRIOR) {  // read out the one-step-ahead prior, kla_ops.py:284-286
-                    ys[ci] = fmaf(c.z, ca[ci][i] * mean[ci][i], ys[ci]);
-                    yvs[ci] = fmaf(c.w, fmaf(ca2[ci][i], P[ci][i], cp[ci][i]), yvs[ci]);
-                } else {
-                    ys[ci] = fmaf(c.z, mean[ci][i], ys[ci]);
-                    yvs[ci] = fmaf(c.w, P[ci][i], yvs[ci]);
-                }
-            }
-        }
-#pragma unroll
-        for (int ci = 0; ci < CH; ++ci) yrow[tt * LPC * MCP + ci] = make_float2(ys[ci], yvs[ci]);
-    };
-
-    // prologue: tile 0
-    stage_tile<T, TT, MC, NTHR>(vbuf, vb, prm.v.st, 0, L, m_cta, M, prm.vec_v, tid);
-    stage_tile<T, TT, MC, NTHR>(lbuf, lb, prm.lv.st, 0, L, m_cta, M, prm.vec_lv, tid);
-    load_kq(0);
-    store_kq(0);
-    cp_async_wait_all();
     __syncthreads();
 
-    for (int tile = 0; tile < prm.NT; ++tile) {
-        const int cur = tile & 1, nxt = cur ^ 1;
-        const int t0 = tile * TT;
-        const bool more = tile + 1 < prm.NT;
-        if (more) {
-            stage_tile<T, TT, MC, NTHR>(vbuf + nxt * TT * MC, vb, prm.v.st, t0 + TT, L, m_cta, M, prm.vec_v, tid);
-            stage_tile<T, TT, MC, NTHR>(lbuf + nxt * TT * MC, lb, prm.lv.st, t0 + TT, L, m_cta, M, prm.vec_lv, tid);
-            load_kq(t0 + TT);
+    if (warp < NW) {
+        // =============================================================== compute
+        const int j = lane % LPC, cl = lane / LPC;
+        const int cw = warp * Sh::kCPW + cl * CH;  // first channel of this thread, CTA-relative
+
+        // Per-chain constants and state. Padding chains (s >= S or m >= M) get
+        // a = 0, p = 1, so their variance sits at 1 and their mean at 0.
+        float ca[CH][SPT], ca2[CH][SPT], cp[CH][SPT], P[CH][SPT], mean[CH][SPT];
+#pragma unroll
+        for (int ci = 0; ci < CH; ++ci) {
+            const int m = m_cta + cw + ci;
+#pragma unroll
+            for (int i = 0; i < SPT; ++i) {
+                const int s = i * LPC + j;
+                const bool live = (m < M) && (s < S);
+                const float av = live ? prm.a[(long long)m * S + s] : 0.0f;
+                const float pv = live ? prm.p[(long long)m * S + s] : 1.0f;
+                ca[ci][i] = av;
+                ca2[ci][i] = live ? fmaxf(av * av, kEps) : 0.0f;
+                cp[ci][i] = fmaxf(pv, kPMin);
+                float lam = 1.0f, eta = 0.0f;
+                if (live && prm.lam0 != nullptr) {
+                    lam = prm.lam0[((long long)b * M + m) * S + s];
+                    eta = prm.eta0[((long long)b * M + m) * S + s];
+                }
+                const float P0 = 1.0f / fmaxf(lam, kLamMin);
+                P[ci][i] = P0;
+                mean[ci][i] = eta * P0;
+            }
         }
-        if (prm.ckpt != nullptr) {
+        // checkpoint pointer of chain (ci = 0, i = 0); advanced by one tile per tile
+        float2 *ck = prm.ckpt;
+        if (ck != nullptr) ck += ((long long)b * NT * M + (m_cta + cw)) * S + j;
+        const long long ck_tile = (long long)M * S;
+
+        // Inputs of one time step, fetched from shared memory one step ahead of use.
+        struct StepIn {
+            float lv[CH], vv[CH];
+            float2 c[SPT];  // (k, q) for this thread's states
+        };
+        auto fetch = [&](StepIn &in, const T *lrow, const T *vrow, const float2 *kqrow, int tt) {
+#ifdef KLA_KO_LDS
+#pragma unroll
+            for (int ci = 0; ci < CH; ++ci) { in.lv[ci] = 0.5f + 0.001f * tt; in.vv[ci] = 0.25f; }
+#pragma unroll
+            for (int i = 0; i < SPT; ++i) in.c[i] = make_float2(0.25f + 0.01f * i, 0.1f * tt);
+#else
 #pragma unroll
             for (int ci = 0; ci < CH; ++ci) {
-                const int m = m_cta + cw + ci;
+                in.lv[ci] = to_f32<T>(lrow[tt * MC + ci]);
+                in.vv[ci] = to_f32<T>(vrow[tt * MC + ci]);
+            }
 #pragma unroll
-                for (int i = 0; i < SPT; ++i) {
-                    const int s = i * LPC + j;
-                    if (m < M && s < S)
-                        prm.ckpt[(((long long)b * prm.NT + tile) * M + m) * S + s] = make_float2(P[ci][i], mean[ci][i]);
+            for (int i = 0; i < SPT; ++i) in.c[i] = kqrow[tt * SPAD + i * LPC];
+#endif
+        };
+        // One time step for every chain of this thread. The chains are advanced
+        // phase by phase (all denominators, all reciprocals, all updates) so that
+        // the independent reciprocals are in flight together. The thread's share
+        // of the read-out goes to shared memory.
+        auto step = [&](const StepIn &in, float2 *yrow, int tt) {
+            float Pp[CH][SPT], g[CH][SPT], r[CH][SPT], ys[CH], yvs[CH];
+#pragma unroll
+            for (int i = 0; i < SPT; ++i)
+#pragma unroll
+                for (int ci = 0; ci < CH; ++ci) {
+                    float phi;
+                    chain_inputs(in.lv[ci], in.vv[ci], in.c[i].x, phi, r[ci][i]);
+                    g[ci][i] = chain_denominator(P[ci][i], phi, ca2[ci][i], cp[ci][i], Pp[ci][i]);
+                }
+#pragma unroll
+            for (int i = 0; i < SPT; ++i)
+#pragma unroll
+                for (int ci = 0; ci < CH; ++ci) g[ci][i] = rcp_approx(g[ci][i]);
+#pragma unroll
+            for (int ci = 0; ci < CH; ++ci) ys[ci] = yvs[ci] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < SPT; ++i)
+#pragma unroll
+                for (int ci = 0; ci < CH; ++ci) {
+                    chain_update(P[ci][i], mean[ci][i], Pp[ci][i], g[ci][i], r[ci][i], ca[ci][i]);
+                    const float q = in.c[i].y;
+                    if (PRIOR) {  // read out the one-step-ahead prior, kla_ops.py:284-286
+                        ys[ci] = fmaf(q, ca[ci][i] * mean[ci][i], ys[ci]);
+                        yvs[ci] = fmaf(q, q * fmaf(ca2[ci][i], P[ci][i], cp[ci][i]), yvs[ci]);
+                    } else {
+                        ys[ci] = fmaf(q, mean[ci][i], ys[ci]);
+                        yvs[ci] = fmaf(q, q * P[ci][i], yvs[ci]);
+                    }
+                }
+#ifdef KLA_KO_OUT
+#pragma unroll
+            for (int ci = 0; ci < CH; ++ci) if (ys[ci] == 123.456f) yrow[ci] = make_float2(ys[ci], yvs[ci]);
+#else
+#pragma unroll
+            for (int ci = 0; ci < CH; ++ci) yrow[tt * LPC * MCP + ci] = make_float2(ys[ci], yvs[ci]);
+#endif
+        };
+
+        for (int tile = 0; tile < NT; ++tile) {
+            const int s = tile % NS, o = tile % NO;
+            const int t0 = tile * TT;
+#ifndef KLA_KO_HELP
+            if (!mbar_wait(&full_in[s], (tile / NS) & 1, 1)) break;
+            if (tile >= NO && !mbar_wait(&empty_out[o], (tile / NO - 1) & 1, 2)) break;
+#endif
+#ifdef KLA_KO_CK
+            if (false) {
+#else
+            if (ck != nullptr) {
+#endif
+#pragma unroll
+                for (int ci = 0; ci < CH; ++ci)
+#pragma unroll
+                    for (int i = 0; i < SPT; ++i)
+                        if (m_cta + cw + ci < M && i * LPC + j < S)
+                            ck[ci * S + i * LPC] = make_float2(P[ci][i], mean[ci][i]);
+                ck += ck_tile;
+            }
+            const T *lrow = lstage(s) + cw;
+            const T *vrow = vstage(s) + cw;
+            const float2 *kqrow = kqstage(s) + j;
+            float2 *yrow = ystage(o) + j * MCP + cw;
+            StepIn in0, in1;
+            fetch(in0, lrow, vrow, kqrow, 0);
+            if (t0 + TT <= L) {
+                // four steps per trip keeps the loop body inside the instruction cache
+#ifdef KLA_FWD_UNROLL16
+#pragma unroll
+#else
+#pragma unroll 1
+#endif
+                for (int t4 = 0; t4 < TT; t4 += 4) {
+#pragma unroll
+                    for (int u = 0; u < 4; u += 2) {
+                        const int tt = t4 + u;
+                        fetch(in1, lrow, vrow, kqrow, tt + 1);
+                        step(in0, yrow, tt);
+                        fetch(in0, lrow, vrow, kqrow, (tt + 2) % TT);
+                        step(in1, yrow, tt + 1);
+                    }
+                }
+            } else {
+                for (int tt = 0; t0 + tt < L; ++tt) {
+                    fetch(in0, lrow, vrow, kqrow, tt);
+                    step(in0, yrow, tt);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&empty_in[s]);
+                mbar_arrive(&full_out[o]);
+            }
+        }
+
+        // final state back in information form: lambda = 1/P, eta = mean * lambda
+#pragma unroll
+        for (int ci = 0; ci < CH; ++ci) {
+            const int m = m_cta + cw + ci;
+#pragma unroll
+            for (int i = 0; i < SPT; ++i) {
+                const int s = i * LPC + j;
+                if (m < M && s < S) {
+                    const float lam = 1.0f / P[ci][i];
+                    prm.lam_fin[((long long)b * M + m) * S + s] = lam;
+                    prm.eta_fin[((long long)b * M + m) * S + s] = mean[ci][i] * lam;
                 }
             }
         }
-        const T *lrow = lbuf + cur * TT * MC + cw;
-        const T *vrow = vbuf + cur * TT * MC + cw;
-        const float4 *kqrow = kq4 + cur * TT * SPAD + j;
-        float2 *yrow = ypart + cur * TT * LPC * MCP + j * MCP + cw;
-        if (t0 + TT <= L) {
-#pragma unroll
-            for (int tt = 0; tt < TT; ++tt) step(lrow, vrow, kqrow, yrow, tt);
-        } else {
-            for (int tt = 0; t0 + tt < L; ++tt) step(lrow, vrow, kqrow, yrow, tt);
-        }
-        if (more) store_kq(nxt);
-        cp_async_wait_all();
-        __syncthreads();
-        output_pass<TO, LPC, MC, MCP, TT, NTHR>(
-            ypart + cur * TT * LPC * MCP, yb + (long long)t0 * prm.y.st, prm.y.st, prm.vec_y,
-            yvb + (long long)t0 * prm.yv.st, prm.yv.st, prm.vec_yv, min(TT, L - t0), m_cta, M, tid,
-            [](float2 acc, int, int, float &o0, float &o1) { o0 = acc.x; o1 = acc.y; });
-    }
+    } else {
+        // ================================================================ helpers
+#ifdef KLA_KO_HELP
+        return;
+#endif
+        const int htid = tid - Sh::kCompute;
+        const int hlane = htid & 31;
+        const T *vb = static_cast<const T *>(prm.v.ptr) + (long long)b * prm.v.sb;
+        const T *lb = static_cast<const T *>(prm.lv.ptr) + (long long)b * prm.lv.sb;
+        const T *kb = static_cast<const T *>(prm.k.ptr) + (long long)b * prm.k.sb;
+        const T *qb = static_cast<const T *>(prm.q.ptr) + (long long)b * prm.q.sb;
+        TO *yb = static_cast<TO *>(prm.y.ptr) + (long long)b * prm.y.sb;
+        TO *yvb = static_cast<TO *>(prm.yv.ptr) + (long long)b * prm.yv.sb;
+        constexpr uint32_t kTileBytes = sizeof(T) * TT * MC;
+        int produced = 0;
+        bool ok = true;
 
-    // final state back in information form: lambda = 1/P, eta = mean * lambda
-#pragma unroll
-    for (int ci = 0; ci < CH; ++ci) {
-        const int m = m_cta + cw + ci;
-#pragma unroll
-        for (int i = 0; i < SPT; ++i) {
-            const int s = i * LPC + j;
-            if (m < M && s < S) {
-                const float lam = 1.0f / P[ci][i];
-                prm.lam_fin[((long long)b * M + m) * S + s] = lam;
-                prm.eta_fin[((long long)b * M + m) * S + s] = mean[ci][i] * lam;
+        for (int it = 0; it < NT + NO && ok; ++it) {
+            if (it < NT) {  // ---- produce tile `it`
+                const int s = it % NS, t0 = it * TT;
+                if (it >= NS && !mbar_wait(&empty_in[s], (it / NS - 1) & 1, 3)) { ok = false; break; }
+                if (prm.use_tma) {
+                    if (htid == 0) {
+                        mbar_arrive_expect_tx(&full_in[s], 2 * kTileBytes);
+                        tma_load_3d(vstage(s), &prm.tm_v, m_cta, t0, b, &full_in[s]);
+                        tma_load_3d(lstage(s), &prm.tm_lv, m_cta, t0, b, &full_in[s]);
+                    }
+                } else {
+                    stage_tile_plain<T, TT, MC, Sh::kHelpers>(vstage(s), vb, prm.v.st, t0, L, m_cta, M, htid);
+                    stage_tile_plain<T, TT, MC, Sh::kHelpers>(lstage(s), lb, prm.lv.st, t0, L, m_cta, M, htid);
+                }
+                float2 *kq = kqstage(s);
+                for (int idx = htid; idx < TT * SPAD; idx += Sh::kHelpers) {
+                    const int row = idx / SPAD, sidx = idx % SPAD;
+                    float kv = 0.0f, qv = 0.0f;
+                    if (sidx < S && t0 + row < L) {
+                        kv = to_f32<T>(kb[(long long)(t0 + row) * prm.k.st + sidx]);
+                        qv = to_f32<T>(qb[(long long)(t0 + row) * prm.q.st + sidx]);
+                    }
+                    kq[idx] = make_float2(kv, qv);
+                }
+                if (!(prm.use_tma && htid == 0)) mbar_arrive(&full_in[s]);
+                produced = it + 1;
             }
+            const int jt = it - NO;  // ---- drain the read-out of tile `jt`
+            if (jt >= 0) {
+                const int o = jt % NO, t0 = jt * TT;
+                if (!mbar_wait(&full_out[o], (jt / NO) & 1, 4)) { ok = false; break; }
+                output_pass<TO, LPC, MC, MCP, TT, Sh::kHelpers>(
+                    ystage(o), yb + (long long)t0 * prm.y.st, prm.y.st, prm.vec_y,
+                    yvb + (long long)t0 * prm.yv.st, prm.yv.st, prm.vec_yv, min(TT, L - t0), m_cta, M, htid,
+                    [](float2 acc, int, int, float &o0, float &o1) { o0 = acc.x; o1 = acc.y; });
+                __syncwarp();
+                if (hlane == 0) mbar_arrive(&empty_out[o]);
+            }
+        }
+        // Leaving early (a wait ran out): do not end the CTA with bulk copies
+        // still in flight into its shared memory.
+        if (!ok && prm.use_tma && htid == 0) {
+            for (int t = max(0, produced - NS); t < produced; ++t) mbar_wait(&full_in[t % NS], (t / NS) & 1, 5);
         }
     }
 }
