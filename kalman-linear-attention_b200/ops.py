@@ -58,6 +58,13 @@ def _unsupported(msg: str) -> NotImplementedError:
 _SM100_CACHE: dict = {}
 
 
+def _require_device(t: torch.Tensor) -> None:
+    """The kernels exist for CUDA tensors on an sm_100 device only."""
+    if not t.is_cuda:
+        raise _unsupported("requires CUDA tensors")
+    _require_sm100(t.device)
+
+
 def _require_sm100(device: torch.device) -> None:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     ok = _SM100_CACHE.get(idx)
@@ -94,6 +101,62 @@ def _dt(t: torch.dtype) -> int:
     return BF16 if t == torch.bfloat16 else F32
 
 
+def _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype, need_ckpt: bool):
+    """Allocate outputs (and the checkpoint scratch when a backward will follow)
+    and enqueue ``kla_b200_scan_fwd`` on the current stream of the inputs' device."""
+    lib = _lib.load()
+    B, L, M = v.shape
+    S = k.shape[2]
+    dev = v.device
+    y = torch.empty((B, L, M), device=dev, dtype=out_dtype)
+    y_var = torch.empty((B, L, M), device=dev, dtype=out_dtype)
+    lam_fin = torch.empty((B, M, S), device=dev, dtype=torch.float32)
+    eta_fin = torch.empty((B, M, S), device=dev, dtype=torch.float32)
+    ckpt = None
+    if need_ckpt and L > 0:
+        ckpt = torch.empty(lib.kla_b200_ckpt_bytes(B, L, M, S), device=dev, dtype=torch.uint8)
+    args = FwdArgs(
+        B=B, L=L, M=M, S=S, in_dtype=_dt(v.dtype), out_dtype=_dt(out_dtype),
+        decode_from_prior=int(prior),
+        v=_t3(v), lambda_v=_t3(lambda_v), k=_t3(k), q=_t3(q),
+        a=_ptr(a), p=_ptr(p), lam0=_ptr(lam0), eta0=_ptr(eta0),
+        y=_t3(y), y_var=_t3(y_var), lam_fin=_ptr(lam_fin), eta_fin=_ptr(eta_fin),
+        ckpt=_ptr(ckpt),
+    )
+    with torch.cuda.device(dev):
+        _lib.check(lib.kla_b200_scan_fwd(ctypes.byref(args), _stream(dev)))
+    return y, y_var, lam_fin, eta_fin, ckpt
+
+
+def _launch_bwd(v, lambda_v, k, q, a, p, lam0, eta0, ckpt, dy, dy_var, dlam_fin, deta_fin,
+                prior: bool, out_dtype):
+    """Allocate the gradients and enqueue ``kla_b200_scan_bwd``."""
+    lib = _lib.load()
+    B, L, M = v.shape
+    S = k.shape[2]
+    dev = v.device
+    dv = torch.empty((B, L, M), device=dev, dtype=v.dtype)
+    dlv = torch.empty((B, L, M), device=dev, dtype=v.dtype)
+    dk = torch.empty((B, L, S), device=dev, dtype=torch.float32)
+    dq = torch.empty((B, L, S), device=dev, dtype=torch.float32)
+    da = torch.empty((M, S), device=dev, dtype=torch.float32)
+    dp = torch.empty((M, S), device=dev, dtype=torch.float32)
+    dlam0 = torch.empty((B, M, S), device=dev, dtype=torch.float32)
+    deta0 = torch.empty((B, M, S), device=dev, dtype=torch.float32)
+    args = BwdArgs(
+        B=B, L=L, M=M, S=S, in_dtype=_dt(v.dtype), out_dtype=_dt(out_dtype),
+        decode_from_prior=int(prior),
+        v=_t3(v), lambda_v=_t3(lambda_v), k=_t3(k), q=_t3(q),
+        a=_ptr(a), p=_ptr(p), lam0=_ptr(lam0), eta0=_ptr(eta0), ckpt=_ptr(ckpt),
+        dy=_t3(dy), dy_var=_t3(dy_var), dlam_fin=_ptr(dlam_fin), deta_fin=_ptr(deta_fin),
+        dv=_t3(dv), dlambda_v=_t3(dlv), dk=_ptr(dk), dq=_ptr(dq), da=_ptr(da), dp=_ptr(dp),
+        dlam0=_ptr(dlam0), deta0=_ptr(deta0),
+    )
+    with torch.cuda.device(dev):
+        _lib.check(lib.kla_b200_scan_bwd(ctypes.byref(args), _stream(dev)))
+    return dv, dlv, dk, dq, da, dp, dlam0, deta0
+
+
 class _KLAScanB200(torch.autograd.Function):
     """Forward and exact backward of the fused scan, both as single kernels.
 
@@ -103,28 +166,9 @@ class _KLAScanB200(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype: torch.dtype):
-        lib = _lib.load()
-        B, L, M = v.shape
-        S = k.shape[2]
-        dev = v.device
         need_grad = any(ctx.needs_input_grad[:8])
-        y = torch.empty((B, L, M), device=dev, dtype=out_dtype)
-        y_var = torch.empty((B, L, M), device=dev, dtype=out_dtype)
-        lam_fin = torch.empty((B, M, S), device=dev, dtype=torch.float32)
-        eta_fin = torch.empty((B, M, S), device=dev, dtype=torch.float32)
-        ckpt = None
-        if need_grad and L > 0:
-            ckpt = torch.empty(lib.kla_b200_ckpt_bytes(B, L, M, S), device=dev, dtype=torch.uint8)
-        args = FwdArgs(
-            B=B, L=L, M=M, S=S, in_dtype=_dt(v.dtype), out_dtype=_dt(out_dtype),
-            decode_from_prior=int(prior),
-            v=_t3(v), lambda_v=_t3(lambda_v), k=_t3(k), q=_t3(q),
-            a=_ptr(a), p=_ptr(p), lam0=_ptr(lam0), eta0=_ptr(eta0),
-            y=_t3(y), y_var=_t3(y_var), lam_fin=_ptr(lam_fin), eta_fin=_ptr(eta_fin),
-            ckpt=_ptr(ckpt),
-        )
-        with torch.cuda.device(dev):
-            _lib.check(lib.kla_b200_scan_fwd(ctypes.byref(args), _stream(dev)))
+        y, y_var, lam_fin, eta_fin, ckpt = _launch_fwd(
+            v, lambda_v, k, q, a, p, lam0, eta0, prior, out_dtype, need_grad)
         ctx.save_for_backward(v, lambda_v, k, q, a, p, lam0, eta0, ckpt)
         ctx.prior = prior
         ctx.out_dtype = out_dtype
@@ -132,7 +176,6 @@ class _KLAScanB200(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy, dy_var, dlam_fin, deta_fin):
-        lib = _lib.load()
         v, lambda_v, k, q, a, p, lam0, eta0, ckpt = ctx.saved_tensors
         B, L, M = v.shape
         S = k.shape[2]
@@ -157,26 +200,8 @@ class _KLAScanB200(torch.autograd.Function):
         if dlam_fin is not None:
             dlam_fin = dlam_fin.float().contiguous()
             deta_fin = deta_fin.float().contiguous()
-
-        dv = torch.empty((B, L, M), device=dev, dtype=v.dtype)
-        dlv = torch.empty((B, L, M), device=dev, dtype=v.dtype)
-        dk = torch.empty((B, L, S), device=dev, dtype=torch.float32)
-        dq = torch.empty((B, L, S), device=dev, dtype=torch.float32)
-        da = torch.empty((M, S), device=dev, dtype=torch.float32)
-        dp = torch.empty((M, S), device=dev, dtype=torch.float32)
-        dlam0 = torch.empty((B, M, S), device=dev, dtype=torch.float32)
-        deta0 = torch.empty((B, M, S), device=dev, dtype=torch.float32)
-        args = BwdArgs(
-            B=B, L=L, M=M, S=S, in_dtype=_dt(v.dtype), out_dtype=_dt(od),
-            decode_from_prior=int(ctx.prior),
-            v=_t3(v), lambda_v=_t3(lambda_v), k=_t3(k), q=_t3(q),
-            a=_ptr(a), p=_ptr(p), lam0=_ptr(lam0), eta0=_ptr(eta0), ckpt=_ptr(ckpt),
-            dy=_t3(dy), dy_var=_t3(dy_var), dlam_fin=_ptr(dlam_fin), deta_fin=_ptr(deta_fin),
-            dv=_t3(dv), dlambda_v=_t3(dlv), dk=_ptr(dk), dq=_ptr(dq), da=_ptr(da), dp=_ptr(dp),
-            dlam0=_ptr(dlam0), deta0=_ptr(deta0),
-        )
-        with torch.cuda.device(dev):
-            _lib.check(lib.kla_b200_scan_bwd(ctypes.byref(args), _stream(dev)))
+        dv, dlv, dk, dq, da, dp, dlam0, deta0 = _launch_bwd(
+            v, lambda_v, k, q, a, p, lam0, eta0, ckpt, dy, dy_var, dlam_fin, deta_fin, ctx.prior, od)
         if k.dtype != torch.float32:
             dk, dq = dk.to(k.dtype), dq.to(k.dtype)
         has_state = lam0 is not None
@@ -207,8 +232,7 @@ def kla_scan_b200(
     (bfloat16 inputs only) also writes y, y_var as bfloat16 -- what the layer
     would cast them to anyway (kla_layer.py:329-330).
     """
-    if not v.is_cuda:
-        raise _unsupported("requires CUDA tensors")
+    _require_device(v)
     if a.dim() != 2:
         raise _unsupported("expects a/p of shape [M, S]")
     if v.dim() != 3 or k.dim() != 3:
@@ -226,7 +250,6 @@ def kla_scan_b200(
         raise _unsupported("runs in float32 only (float64 inputs are for gradcheck on the torch backend)")
     if any(t.device != v.device for t in tensors):
         raise ValueError("all inputs must be on the same device")
-    _require_sm100(v.device)
 
     if all(t.dtype == torch.bfloat16 for t in (v, lambda_v, k, q)):
         act = torch.bfloat16
@@ -272,8 +295,7 @@ def kla_step_b200(
     float32 and contiguous) instead of allocating new ones. When a gradient is
     required the step is run as a length-1 scan, which has a backward.
     """
-    if not v.is_cuda:
-        raise _unsupported("requires CUDA tensors")
+    _require_device(v)
     if v.dim() != 2 or k.dim() != 2:
         raise ValueError("v, lambda_v must be [B, M] and k, q [B, S]")
     lam, eta = state
@@ -292,7 +314,6 @@ def kla_step_b200(
         raise _unsupported(f"supports d_state <= {MAX_DSTATE} (got {S})")
     if any(t.dtype == torch.float64 for t in (v, lambda_v, k, q, a, p, lam, eta)):
         raise _unsupported("runs in float32 only")
-    _require_sm100(v.device)
     lib = _lib.load()
     act = torch.bfloat16 if all(t.dtype == torch.bfloat16 for t in (v, lambda_v, k, q)) else torch.float32
 

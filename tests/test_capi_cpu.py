@@ -1,0 +1,86 @@
+"""The C-ABI library without a GPU: it loads, exports every symbol the header
+declares, and rejects bad arguments before touching CUDA."""
+
+import ctypes
+import importlib
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "kla_b200.h")
+
+
+@pytest.fixture(scope="module")
+def L():
+    import kla_b200
+
+    kla_b200.build()
+    return importlib.import_module("kalman-linear-attention_b200._lib")
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(kla_b200_\w+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(L):
+    lib = L.load()
+    names = declared_functions()
+    assert len(names) >= 8
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/kla_b200.h but not exported"
+    assert set(L.SYMBOLS) <= set(names)
+
+
+def test_version_and_checkpoint_size(L):
+    lib = L.load()
+    assert lib.kla_b200_version() >= 100
+    iv = lib.kla_b200_ckpt_interval()
+    assert iv == 16
+    # one (P, mean) float2 per lane per started interval
+    assert lib.kla_b200_ckpt_bytes(8, 4096, 1024, 16) == 8 * (4096 // iv) * 1024 * 16 * 8
+    assert lib.kla_b200_ckpt_bytes(2, 17, 3, 5) == 2 * 2 * 3 * 5 * 8
+    assert lib.kla_b200_ckpt_bytes(0, 17, 3, 5) == 0
+
+
+def test_bad_arguments_are_rejected_without_cuda(L):
+    lib = L.load()
+    assert lib.kla_b200_scan_fwd(None, None) == 1
+    assert lib.kla_b200_scan_bwd(None, None) == 1
+    assert lib.kla_b200_step(None, None) == 1
+    a = L.FwdArgs(B=1, L=4, M=2, S=200, in_dtype=0, out_dtype=0)
+    assert lib.kla_b200_scan_fwd(ctypes.byref(a), None) == 2  # d_state above the cap
+    a = L.FwdArgs(B=1, L=4, M=2, S=4, in_dtype=7, out_dtype=0)
+    assert lib.kla_b200_scan_fwd(ctypes.byref(a), None) == 2  # unknown dtype
+    a = L.FwdArgs(B=1, L=4, M=2, S=4, in_dtype=0, out_dtype=1)
+    assert lib.kla_b200_scan_fwd(ctypes.byref(a), None) == 2  # f32 in, bf16 out is not a pair
+    a = L.FwdArgs(B=-1, L=4, M=2, S=4)
+    assert lib.kla_b200_scan_fwd(ctypes.byref(a), None) == 1
+    a = L.FwdArgs(B=1, L=4, M=2, S=4)  # all pointers NULL
+    assert lib.kla_b200_scan_fwd(ctypes.byref(a), None) == 1
+    # empty problems are fine and launch nothing
+    a = L.FwdArgs(B=0, L=4, M=2, S=4)
+    assert lib.kla_b200_scan_fwd(ctypes.byref(a), None) == 0
+    assert lib.kla_b200_launch_count() == 0
+
+
+def test_error_text_and_exception_mapping(L):
+    lib = L.load()
+    assert lib.kla_b200_strerror(0) == b"ok"
+    assert b"invalid" in lib.kla_b200_strerror(1)
+    with pytest.raises(NotImplementedError, match="backend='torch'"):
+        L.check(2)
+    with pytest.raises(ValueError):
+        L.check(1)
+    with pytest.raises(ValueError):
+        L.check(4)
+
+
+def test_missing_library_fails_loudly(L, monkeypatch):
+    monkeypatch.setattr(L, "_lib", None)
+    monkeypatch.setattr(L, "LIB_PATH", "/nonexistent/libkla_b200.so")
+    with pytest.raises(L.LibraryMissing, match="no CPU or Triton fallback"):
+        L.load()

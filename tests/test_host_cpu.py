@@ -1,0 +1,253 @@
+"""Host-side logic on the CPU: error behaviour of the backend callable, the
+wrapper's plumbing with the kernel launches replaced by the oracle, plugging
+into the reference package, and the batch x channel sharding under gloo."""
+
+import importlib
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden
+from oracle import kla_oracle as O
+
+import kla_b200
+
+ops = importlib.import_module("kalman-linear-attention_b200.ops")
+REF_SRC = "/root/reference/src"
+INPUTS = ("v", "lambda_v", "k", "q", "a", "p")
+
+
+def _t(g, names=INPUTS, dtype=torch.float32):
+    return [torch.tensor(g[n], dtype=dtype) for n in names]
+
+
+# ------------------------------------------------------------ error behaviour
+
+def test_cpu_tensors_are_refused_not_served():
+    ins = _t(load_golden("backends"))
+    with pytest.raises(NotImplementedError, match="backend='torch'"):
+        kla_b200.kla_scan_b200(*ins)
+    with pytest.raises(NotImplementedError, match="CUDA"):
+        kla_b200.kla_step_b200(ins[0][:, 0], ins[1][:, 0], ins[2][:, 0], ins[3][:, 0], ins[4], ins[5],
+                               kla_b200.init_state(2, 16, 8))
+
+
+# ----------------------------------- wrapper plumbing with oracle-backed launches
+
+@pytest.fixture
+def oracle_launches(monkeypatch):
+    """Replace the two kernel launches by the CPU oracle and let CPU tensors
+    through, so that everything above the C-ABI call runs here."""
+    monkeypatch.setattr(ops, "_require_device", lambda t: None)
+
+    def fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior, out_dtype, need_ckpt):
+        n = lambda t: None if t is None else t.detach().double().numpy()
+        f = O.scan_fwd(n(v), n(lambda_v), n(k), n(q), n(a), n(p), n(lam0), n(eta0), prior=prior)
+        return (torch.tensor(f.y, dtype=out_dtype), torch.tensor(f.y_var, dtype=out_dtype),
+                torch.tensor(f.lam, dtype=torch.float32), torch.tensor(f.eta, dtype=torch.float32),
+                torch.zeros(1, dtype=torch.uint8) if need_ckpt else None)
+
+    def bwd(v, lambda_v, k, q, a, p, lam0, eta0, ckpt, dy, dy_var, dlam_fin, deta_fin, prior, out_dtype):
+        n = lambda t: None if t is None else t.detach().double().numpy()
+        g = O.scan_bwd(n(v), n(lambda_v), n(k), n(q), n(a), n(p), n(dy), n(dy_var), n(lam0), n(eta0),
+                       n(dlam_fin), n(deta_fin), prior=prior)
+        f32 = lambda x, dt=torch.float32: torch.tensor(x, dtype=dt)
+        return (f32(g.dv, v.dtype), f32(g.dlambda_v, v.dtype), f32(g.dk), f32(g.dq), f32(g.da), f32(g.dp),
+                f32(g.dlam0), f32(g.deta0))
+
+    monkeypatch.setattr(ops, "_launch_fwd", fwd)
+    monkeypatch.setattr(ops, "_launch_bwd", bwd)
+
+
+def test_wrapper_contract(oracle_launches):
+    g = load_golden("backends_state_prior")
+    ins = [t.requires_grad_(True) for t in _t(g)]
+    lam0 = torch.tensor(g["lam0"], dtype=torch.float32, requires_grad=True)
+    eta0 = torch.tensor(g["eta0"], dtype=torch.float32, requires_grad=True)
+    y, y_var, st = kla_b200.kla_scan_b200(*ins, initial_state=(lam0, eta0), decode_from_prior=True)
+    assert y.dtype == torch.float32 and y.shape == ins[0].shape
+    assert hasattr(st, "lam") and hasattr(st, "eta")
+    loss = ((y * torch.tensor(g["dy"], dtype=torch.float32)).sum()
+            + (y_var * torch.tensor(g["dyvar"], dtype=torch.float32)).sum()
+            + (st.lam * torch.tensor(g["dlam_fin"], dtype=torch.float32)).sum()
+            + (st.eta * torch.tensor(g["deta_fin"], dtype=torch.float32)).sum())
+    grads = torch.autograd.grad(loss, ins + [lam0, eta0])
+    for n, gr in zip(["dv", "dlambda_v", "dk", "dq", "da", "dp", "dlam0", "deta0"], grads):
+        np.testing.assert_allclose(gr.numpy(), g[n], rtol=2e-4, atol=2e-5, err_msg=n)
+
+
+def test_wrapper_widens_and_validates(oracle_launches):
+    g = load_golden("backends")
+    ins = _t(g)
+    # half precision is widened to float32 like the reference (kla_ops.py:126-137)
+    y, _, _ = kla_b200.kla_scan_b200(*[t.half() if i < 4 else t for i, t in enumerate(ins)])
+    assert y.dtype == torch.float32
+    # bfloat16 activations stay bfloat16 into the kernel; outputs are float32 unless asked
+    y, _, _ = kla_b200.kla_scan_b200(*[t.bfloat16() if i < 4 else t for i, t in enumerate(ins)])
+    assert y.dtype == torch.float32
+    y, _, _ = kla_b200.kla_scan_b200(*[t.bfloat16() if i < 4 else t for i, t in enumerate(ins)],
+                                      out_dtype=torch.bfloat16)
+    assert y.dtype == torch.bfloat16
+    with pytest.raises(NotImplementedError, match="float32 only"):
+        kla_b200.kla_scan_b200(*[t.double() for t in ins])
+    with pytest.raises(NotImplementedError, match=r"\[M, S\]"):
+        kla_b200.kla_scan_b200(*ins[:4], ins[4][None], ins[5][None])
+    with pytest.raises(NotImplementedError, match="d_state <= 128"):
+        B, L = 1, 2
+        kla_b200.kla_scan_b200(torch.zeros(B, L, 2), torch.ones(B, L, 2), torch.zeros(B, L, 129),
+                               torch.zeros(B, L, 129), torch.ones(2, 129), torch.ones(2, 129))
+    with pytest.raises(ValueError):
+        kla_b200.kla_scan_b200(ins[0], ins[1][:, :-1], *ins[2:])
+    # a non-unit last stride is copied, a row-strided view is passed through
+    wide = torch.zeros(2, 64, 40)
+    wide[..., 3:19] = ins[0]
+    y2, _, _ = kla_b200.kla_scan_b200(wide[..., 3:19], *ins[1:])
+    y1, _, _ = kla_b200.kla_scan_b200(*ins)
+    torch.testing.assert_close(y1, y2)
+
+
+# ------------------------------------------------ plugging into the reference
+
+needs_ref = pytest.mark.skipif(not os.path.isdir(REF_SRC), reason="reference package not present")
+
+
+@needs_ref
+def test_register_into_reference_dispatch(oracle_launches):
+    sys.path.insert(0, REF_SRC)
+    try:
+        import kla
+        from kla.ops import kla_ops
+
+        before_auto = kla_ops._resolve_auto(torch.zeros(1))
+        kla_b200.register()
+        try:
+            assert "b200" in kla.ops.backend_names()
+            assert kla_ops._resolve_auto(torch.zeros(1)) == before_auto  # "auto" untouched
+            g = load_golden("backends")
+            ins = _t(g)
+            y, y_var, st = kla.ops.kla_scan(*ins, backend="b200")
+            assert isinstance(st, kla_ops.KLAState)
+            y_ref, _, _ = kla.ops.kla_scan_reference(*ins)
+            torch.testing.assert_close(y, y_ref, atol=2e-4, rtol=1e-4)
+            # through the layer: KLAConfig(backend="b200") reaches the callable
+            torch.manual_seed(0)
+            layer = kla.KLALayer(32, kla.KLAConfig(d_state=8, backend="b200"))
+            ref = kla.KLALayer(32, kla.KLAConfig(d_state=8, backend="torch"))
+            ref.load_state_dict(layer.state_dict())
+            x = torch.randn(2, 24, 32)
+            torch.testing.assert_close(layer(x), ref(x), atol=5e-4, rtol=5e-4)
+            # the decode hook leaves CPU tensors to the original kla_step
+            import kla.layers.kla_layer as kl
+
+            assert kl.kla_step is not kla_ops.kla_step
+            out = kl.kla_step(ins[0][:, 0], ins[1][:, 0], ins[2][:, 0], ins[3][:, 0], ins[4], ins[5],
+                              kla_ops.init_state(2, 16, 8))
+            ref_out = kla_ops.kla_step(ins[0][:, 0], ins[1][:, 0], ins[2][:, 0], ins[3][:, 0], ins[4], ins[5],
+                                       kla_ops.init_state(2, 16, 8))
+            torch.testing.assert_close(out[0], ref_out[0])
+        finally:
+            kla_b200.unregister()
+        assert "b200" not in kla.ops.backend_names()
+        with pytest.raises(ValueError):
+            kla.ops.kla_scan(*_t(load_golden("backends")), backend="b200")
+    finally:
+        sys.path.remove(REF_SRC)
+
+
+# ------------------------------------------------------------------- sharding
+
+def test_blocks_tile_the_lane_grid():
+    sh = kla_b200.shard
+    for B, M, world in ((8, 1024, 1), (8, 1024, 2), (8, 1024, 8), (2, 4096, 8), (3, 100, 4), (16, 1536, 8)):
+        seen = np.zeros((B, M), int)
+        for r in range(world):
+            blk = sh.block_of(B, M, world, r)
+            seen[blk.b0:blk.b1, blk.m0:blk.m1] += 1
+            assert blk.batch_parts * blk.channel_parts == world
+        assert (seen == 1).all(), (B, M, world)
+    assert sh.grid_for(8, 1024, 8) == (8, 1)   # batch first
+    assert sh.grid_for(2, 4096, 8) == (2, 4)   # then channels
+    blk = sh.block_of(2, 4096, 8, 5)
+    assert (blk.m1 - blk.m0) % 32 == 0
+
+
+def _worker(rank, world, port, case, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        opsm = importlib.import_module("kalman-linear-attention_b200.ops")
+        sh = kla_b200.shard
+
+        class CpuScan(torch.autograd.Function):  # oracle-backed stand-in for the kernels
+            @staticmethod
+            def forward(ctx, v, lv, k, qq, a, p):
+                n = lambda t: t.detach().double().numpy()
+                f = O.scan_fwd(n(v), n(lv), n(k), n(qq), n(a), n(p))
+                ctx.save_for_backward(v, lv, k, qq, a, p)
+                return torch.tensor(f.y), torch.tensor(f.y_var)
+
+            @staticmethod
+            def backward(ctx, dy, dyv):
+                n = lambda t: t.detach().double().numpy()
+                g = O.scan_bwd(*[n(t) for t in ctx.saved_tensors], n(dy), n(dyv))
+                return tuple(torch.tensor(x) for x in (g.dv, g.dlambda_v, g.dk, g.dq, g.da, g.dp))
+
+        def scan_fn(v, lv, k, qq, a, p, initial_state=None, decode_from_prior=False):
+            y, yv = CpuScan.apply(v, lv, k, qq, a, p)
+            return y, yv, None
+
+        g = load_golden("cfg2small")
+        full = [torch.tensor(g[n]).requires_grad_(True) for n in INPUTS]
+        B, M = (2, 24) if case == "batch" else (1, 24)
+        if case == "channel":
+            full = [t[:1].detach().requires_grad_(True) if t.dim() == 3 else t for t in full]
+        blk = sh.block_of(B, M, world, rank, align=4)
+        groups = sh.make_groups(world, blk.batch_parts, blk.channel_parts)
+        v, lv, k, qq, a, p, _ = sh.take_block(blk, *full)
+        y, yv, _ = sh.scan_block(scan_fn, groups, v, lv, k, qq, a, p)
+        dy = torch.tensor(g["dy"])[blk.b0:blk.b1, :, blk.m0:blk.m1]
+        dyv = torch.tensor(g["dyvar"])[blk.b0:blk.b1, :, blk.m0:blk.m1]
+        grads = torch.autograd.grad((y * dy).sum() + (yv * dyv).sum(), full)
+        q.put((rank, tuple(blk), y.detach().numpy(), [t.numpy() for t in grads]))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("case", ["batch", "channel"])
+def test_sharded_scan_matches_full_under_gloo(case):
+    """world_size 2 on CPU: the blocks' outputs tile the full output, and after
+    the backward's all-reduces every rank holds the full-problem da, dp (batch
+    split) or dk, dq (channel split)."""
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() % 2000) + (0 if case == "batch" else 1)
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, case, q)) for r in range(2)]
+    [p.start() for p in procs]
+    res = sorted([q.get(timeout=120) for _ in procs], key=lambda t: t[0])
+    [p.join(timeout=60) for p in procs]
+    assert all(p.exitcode == 0 for p in procs)
+
+    g = load_golden("cfg2small")
+    ins = [g[n] for n in INPUTS]
+    dy, dyv = g["dy"], g["dyvar"]
+    if case == "channel":
+        ins = [x[:1] if x.ndim == 3 else x for x in ins]
+        dy, dyv = dy[:1], dyv[:1]
+    f = O.scan_fwd(*ins)
+    b = O.scan_bwd(*ins, dy, dyv)
+    for rank, blk, y, grads in res:
+        b0, b1, m0, m1 = blk[:4]
+        np.testing.assert_allclose(y, f.y[b0:b1, :, m0:m1], rtol=1e-10, atol=1e-12)
+        dv, dlv, dk, dq, da, dp = grads
+        # autograd wrote each rank's slice of the full-shaped gradient
+        np.testing.assert_allclose(dv[b0:b1, :, m0:m1], b.dv[b0:b1, :, m0:m1], rtol=1e-9, atol=1e-12)
+        np.testing.assert_allclose(dk[b0:b1], b.dk[b0:b1], rtol=1e-9, atol=1e-11)   # summed over channels
+        np.testing.assert_allclose(da[m0:m1], b.da[m0:m1], rtol=1e-9, atol=1e-11)   # summed over batch
+        np.testing.assert_allclose(dp[m0:m1], b.dp[m0:m1], rtol=1e-9, atol=1e-11)
