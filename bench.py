@@ -47,9 +47,9 @@ def algorithmic_bytes_per_token(M, S, esz=4):
     return fwd, bwd
 
 
-# ncu-measured DRAM traffic per launch at the bench workload (bytes), copied
-# from the summaries under profiles/; None until a capture exists.
-NCU_TRAFFIC = {"kla_bwd_kernel": None, "kla_fwd_kernel": None}
+# ncu-measured DRAM traffic per launch at the bench workload (bytes, read + write), copied
+# from profiles/kla_scan_fwd_bwd_B8_T4096_M1024_S16_f32.md.
+NCU_TRAFFIC = {"kla_bwd_kernel": 1074.9e6, "kla_fwd_kernel": 759.5e6}
 
 
 def make_inputs(seed=0, **w):

@@ -22,8 +22,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",
-    "--split-compile", "0",
-]
+]  # no --split-compile: with it the optimiser's result (and the kernels' speed) varied from build to build
 
 
 def _nvcc() -> str:

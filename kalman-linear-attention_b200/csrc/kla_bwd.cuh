@@ -53,7 +53,8 @@ struct BwdSmem {
     static constexpr size_t kTileO = ((sizeof(TO) * TT * Sh::kMC + 127) / 128) * 128;  // dy or dyvar
     static constexpr size_t kKq = ((sizeof(float4) * TT * Sh::kSPad + 127) / 128) * 128;
     static constexpr size_t kIn = 2 * kTileI + 2 * kTileO + kKq;
-    static constexpr size_t kTraj = sizeof(float2) * TT * CH * SPT * Sh::kCompute;
+    static constexpr int kRowPad = 4;  // slots; 8 words = the span of LPC lanes' float2 reads
+    static constexpr size_t kTraj = ((sizeof(float2) * TT * CH * SPT * (Sh::kCompute + kRowPad) + 127) / 128) * 128;
     static constexpr size_t kDpart = ((sizeof(float2) * TT * LPC * Sh::kMCP + 127) / 128) * 128;
     static constexpr size_t kTotal = kBars + kBwdStages * kIn + kTraj + kDpart;
 };
@@ -63,7 +64,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
     using Sh = ScanShape<SPT, LPC, CH, NW, NH, TT>;
     using Sm = BwdSmem<T, TO, SPT, LPC, CH, NW, NH, TT>;
     constexpr int SPAD = Sh::kSPad, MC = Sh::kMC, MCP = Sh::kMCP, NTC = Sh::kCompute;
-    constexpr int CLS = Sh::kCLS, NS = kBwdStages, NQ = TT / kQuarter;
+    constexpr int NS = kBwdStages, NQ = TT / kQuarter;
     static_assert(TT == kCkptInterval && TT % kQuarter == 0, "one checkpoint per tile, whole quarters");
 
     // Declared with its alignment (no run-time rounding of the pointer) so that
@@ -103,17 +104,16 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
     }
     __syncthreads();
 
-    // Slot of (physical quarter pq, step u in the quarter, channel ci, state i)
-    // for compute thread (w, ln) inside traj. Rows are rotated inside each warp's
-    // 32 slots so that the reduction over channels reads shared memory without
-    // bank conflicts. The quarter a time step lands in alternates direction from
-    // one processed tile to the next (pq = qd or NQ-1-qd), so that the replay of
-    // a tile writes quarters in the order in which the previous tile's partials
-    // were consumed; u is a compile-time constant wherever this is called.
-    auto slot = [&](int pq, int u, int ci, int i, int w, int ln) {
-        const int rot = LPC * ((u * SPT + i) % CLS);
-        return (((pq * kQuarter + u) * CH + ci) * SPT + i) * NTC + w * 32 + ((ln + rot) & 31);
-    };
+    // traj holds one float2 per compute thread for every (step, channel ci,
+    // state i): row = ((pq*kQuarter + u)*CH + ci)*SPT + i, rows of NTC slots padded
+    // by kRowPad so that the helpers, whose lanes read different rows at the same
+    // column, do not collide on shared-memory banks. The quarter a time step
+    // lands in alternates direction from one processed tile to the next (pq = qd
+    // or NQ-1-qd), so that the replay of a tile writes quarters in the order in
+    // which the previous tile's partials were consumed; u is a compile-time
+    // constant wherever a row is formed.
+    constexpr int ROW = NTC + Sm::kRowPad;
+    auto trow = [&](int pq, int u, int ci, int i) { return (((pq * kQuarter + u) * CH + ci) * SPT + i) * ROW; };
 
     if (warp < NW) {
         // =============================================================== compute
@@ -189,7 +189,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                     const float kk = kqrow[tt * SPAD + i * LPC].y;
 #pragma unroll
                     for (int ci = 0; ci < CH; ++ci) {
-                        traj[slot(pq, u, ci, i, warp, lane)] = make_float2(P[ci][i], mean[ci][i]);
+                        traj[trow(pq, u, ci, i) + tid] = make_float2(P[ci][i], mean[ci][i]);
                         float phi;
                         chain_inputs(lv[ci], vv[ci], kk, phi, r[ci][i]);
                         g[ci][i] = chain_denominator(P[ci][i], phi, ca2[ci][i], cp[ci][i], Pp[ci][i]);
@@ -266,7 +266,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                     c[i] = kqrow[tt * SPAD + i * LPC];  // k^2, k, q, q^2
 #pragma unroll
                     for (int ci = 0; ci < CH; ++ci) {
-                        prev[ci][i] = traj[slot(pq, u, ci, i, warp, lane)];  // P', mean'
+                        prev[ci][i] = traj[trow(pq, u, ci, i) + tid];  // P', mean'
                         chain_inputs(lv[ci], vv[ci], c[i].y, phi[ci][i], r[ci][i]);
                         g[ci][i] = chain_denominator(prev[ci][i].x, phi[ci][i], ca2[ci][i], cp[ci][i], Pp[ci][i]);
                     }
@@ -317,7 +317,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                         mn[ci][i] = prev[ci][i].y;
                     }
                     // this thread's share of dk, dq for (t, s): parked where (P', mean') was
-                    traj[slot(pq, u, 0, i, warp, lane)] = make_float2(fmaf(c[i].y, X2, Y), fmaf(c[i].z, B2, A_));
+                    traj[trow(pq, u, 0, i) + tid] = make_float2(fmaf(c[i].y, X2, Y), fmaf(c[i].z, B2, A_));
                 }
                 // this thread's share of the sums over s
 #pragma unroll
@@ -388,7 +388,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
         for (int it = 0; it <= NT && ok; ++it) {
             if (it < NT) {  // ---- produce the it-th tile from the end
                 const int tile = NT - 1 - it, s = it % NS, t0 = tile * TT;
-                if (it >= NS && !mbar_wait(&empty_in[s], (it / NS - 1) & 1, 13)) { ok = false; break; }
+                if (it >= NS && !mbar_wait(&empty_in[s], (it / NS - 1) & 1, 13, 200)) { ok = false; break; }
                 // every helper warp has finished reading this stage's v / lambda_v tiles
                 __syncwarp();
                 if (hlane == 0) mbar_arrive(helper_sync);
@@ -431,25 +431,26 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                     // the compute warps finish the quarters of a tile from its last steps to its first
                     const int qd = NQ - 1 - step;                 // quarter in time order
                     const int prq = flip ? NQ - 1 - qd : qd;      // its physical rows
-                    if (!mbar_wait(&part_full[prq], jt & 1, 14)) { ok = false; break; }
-                    // dk, dq: add the CTA's channels
+                    if (!mbar_wait(&part_full[prq], jt & 1, 14, 200)) { ok = false; break; }
+                    // dk, dq: add the CTA's channels. Compute thread t holds lane
+                    // group j = t % LPC, so the partials of state s = i*LPC + jj
+                    // sit at columns jj, jj + LPC, ... of row (u, i).
                     for (int pidx = htid; pidx < kQuarter * SPAD; pidx += Sh::kHelpers) {
                         const int jj = pidx % LPC, row = pidx / LPC;  // row = (step in quarter, i)
                         const int u = row / SPT, i = row % SPT;
                         const int tt = qd * kQuarter + u;
                         const int st = i * LPC + jj;
-                        float sk = 0.0f, sq = 0.0f;
+                        const float2 *src = traj + trow(prq, u, 0, i) + jj;
+                        float sk0 = 0.0f, sq0 = 0.0f, sk1 = 0.0f, sq1 = 0.0f;
 #pragma unroll
-                        for (int w = 0; w < NW; ++w)
-#pragma unroll
-                            for (int c = 0; c < CLS; ++c) {
-                                const float2 x = traj[slot(prq, u, 0, i, w, c * LPC + jj)];
-                                sk += x.x;
-                                sq += x.y;
-                            }
+                        for (int c = 0; c < NTC / LPC; c += 2) {
+                            const float2 x0 = src[c * LPC], x1 = src[(c + 1) * LPC];
+                            sk0 += x0.x; sq0 += x0.y;
+                            sk1 += x1.x; sq1 += x1.y;
+                        }
                         if (st < S && tt < n) {
-                            atomicAdd(prm.dk + ((long long)b * L + t0 + tt) * S + st, sk);
-                            atomicAdd(prm.dq + ((long long)b * L + t0 + tt) * S + st, sq);
+                            atomicAdd(prm.dk + ((long long)b * L + t0 + tt) * S + st, sk0 + sk1);
+                            atomicAdd(prm.dq + ((long long)b * L + t0 + tt) * S + st, sq0 + sq1);
                         }
                     }
                     // dv, dlambda_v: add the lane groups. v enters only through

@@ -70,13 +70,9 @@ struct ScanShape {
 };
 
 __device__ __forceinline__ float rcp_approx(float x) {
-#ifdef KLA_KO_RCP
-    return 2.0f - x;
-#else
     float y;
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-#endif
 }
 
 // One predict+update step of one chain, in pieces so that callers can put the
@@ -155,16 +151,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait. A waiting warp sleeps between polls so that it does not take
-// issue slots from the warps that are computing on the same scheduler. After
-// about a second of polling it gives up, records where in g_kla_status and
-// returns false; the caller then leaves its loop so that the CTA ends instead
-// of hanging the device.
-constexpr uint32_t kSpinLimit = 1u << 22;
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int site) {
+// Bounded wait. A waiting warp sleeps between polls (sleep_ns each) so that it
+// does not take issue slots from the warps that are computing on the same
+// scheduler. After about a second of polling it gives up, records where in
+// g_kla_status and returns false; the caller then leaves its loop so that the
+// CTA ends instead of hanging the device.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int site, unsigned sleep_ns = 100) {
     if (mbar_try_wait(bar, parity)) return true;
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        __nanosleep(200);
+    const uint32_t limit = 1000000000u / (sleep_ns + 100);
+    for (uint32_t i = 0; i < limit; ++i) {
+        __nanosleep(sleep_ns);
         if (mbar_try_wait(bar, parity)) return true;
     }
     atomicCAS(&g_kla_status, 0, kStatusWait | site);

@@ -128,12 +128,6 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             float2 c[SPT];  // (k, q) for this thread's states
         };
         auto fetch = [&](StepIn &in, const T *lrow, const T *vrow, const float2 *kqrow, int tt) {
-#ifdef KLA_KO_LDS
-#pragma unroll
-            for (int ci = 0; ci < CH; ++ci) { in.lv[ci] = 0.5f + 0.001f * tt; in.vv[ci] = 0.25f; }
-#pragma unroll
-            for (int i = 0; i < SPT; ++i) in.c[i] = make_float2(0.25f + 0.01f * i, 0.1f * tt);
-#else
 #pragma unroll
             for (int ci = 0; ci < CH; ++ci) {
                 in.lv[ci] = to_f32<T>(lrow[tt * MC + ci]);
@@ -141,7 +135,6 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             }
 #pragma unroll
             for (int i = 0; i < SPT; ++i) in.c[i] = kqrow[tt * SPAD + i * LPC];
-#endif
         };
         // One time step for every chain of this thread. The chains are advanced
         // phase by phase (all denominators, all reciprocals, all updates) so that
@@ -177,27 +170,16 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                         yvs[ci] = fmaf(q, q * P[ci][i], yvs[ci]);
                     }
                 }
-#ifdef KLA_KO_OUT
-#pragma unroll
-            for (int ci = 0; ci < CH; ++ci) if (ys[ci] == 123.456f) yrow[ci] = make_float2(ys[ci], yvs[ci]);
-#else
 #pragma unroll
             for (int ci = 0; ci < CH; ++ci) yrow[tt * LPC * MCP + ci] = make_float2(ys[ci], yvs[ci]);
-#endif
         };
 
         for (int tile = 0; tile < NT; ++tile) {
             const int s = tile % NS, o = tile % NO;
             const int t0 = tile * TT;
-#ifndef KLA_KO_HELP
             if (!mbar_wait(&full_in[s], (tile / NS) & 1, 1)) break;
             if (tile >= NO && !mbar_wait(&empty_out[o], (tile / NO - 1) & 1, 2)) break;
-#endif
-#ifdef KLA_KO_CK
-            if (false) {
-#else
             if (ck != nullptr) {
-#endif
 #pragma unroll
                 for (int ci = 0; ci < CH; ++ci)
 #pragma unroll
@@ -214,11 +196,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             fetch(in0, lrow, vrow, kqrow, 0);
             if (t0 + TT <= L) {
                 // four steps per trip keeps the loop body inside the instruction cache
-#ifdef KLA_FWD_UNROLL16
-#pragma unroll
-#else
 #pragma unroll 1
-#endif
                 for (int t4 = 0; t4 < TT; t4 += 4) {
 #pragma unroll
                     for (int u = 0; u < 4; u += 2) {
@@ -258,9 +236,6 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         }
     } else {
         // ================================================================ helpers
-#ifdef KLA_KO_HELP
-        return;
-#endif
         const int htid = tid - Sh::kCompute;
         const int hlane = htid & 31;
         const T *vb = static_cast<const T *>(prm.v.ptr) + (long long)b * prm.v.sb;
@@ -276,7 +251,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         for (int it = 0; it < NT + NO && ok; ++it) {
             if (it < NT) {  // ---- produce tile `it`
                 const int s = it % NS, t0 = it * TT;
-                if (it >= NS && !mbar_wait(&empty_in[s], (it / NS - 1) & 1, 3)) { ok = false; break; }
+                if (it >= NS && !mbar_wait(&empty_in[s], (it / NS - 1) & 1, 3, 1000)) { ok = false; break; }
                 if (prm.use_tma) {
                     if (htid == 0) {
                         mbar_arrive_expect_tx(&full_in[s], 2 * kTileBytes);
@@ -303,7 +278,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             const int jt = it - NO;  // ---- drain the read-out of tile `jt`
             if (jt >= 0) {
                 const int o = jt % NO, t0 = jt * TT;
-                if (!mbar_wait(&full_out[o], (jt / NO) & 1, 4)) { ok = false; break; }
+                if (!mbar_wait(&full_out[o], (jt / NO) & 1, 4, 1000)) { ok = false; break; }
                 output_pass<TO, LPC, MC, MCP, TT, Sh::kHelpers>(
                     ystage(o), yb + (long long)t0 * prm.y.st, prm.y.st, prm.vec_y,
                     yvb + (long long)t0 * prm.yv.st, prm.yv.st, prm.vec_yv, min(TT, L - t0), m_cta, M, htid,
