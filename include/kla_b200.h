@@ -34,6 +34,7 @@ extern "C" {
 #define KLA_B200_EUNSUPPORTED 2 /* S above KLA_B200_MAX_DSTATE, unknown dtype */
 #define KLA_B200_ECUDA 3       /* a CUDA runtime call failed (cudaGetLastError text via strerror) */
 #define KLA_B200_EALIGN 4      /* pointer not aligned to its element size */
+#define KLA_B200_ETOOBIG 5     /* kla_b200_scan_fwd_static: checkpoints would not fit the built-in scratch */
 
 /* Largest d_state the kernels are instantiated for. The reference's fused
  * kernels have the same kind of cap (src/kla/ops/cuda_backend.py:134,274-275). */
@@ -82,6 +83,34 @@ size_t kla_b200_ckpt_bytes(int64_t B, int64_t L, int64_t M, int64_t S);
 int64_t kla_b200_ckpt_interval(void);
 
 int kla_b200_scan_fwd(const kla_b200_fwd_args *args, void *stream);
+
+/*
+ * Forward scan for callers that cannot allocate device memory. It has no
+ * counterpart in the reference; it exists for hosts that are handed their
+ * tensors by someone else and have no allocator of their own to ask for the
+ * checkpoint scratch: a plugin running inside another runtime's memory arena,
+ * a step that must not touch the allocator because an allocation there would
+ * synchronise or fail, a real-time loop with a fixed memory budget.
+ *
+ * Same computation as kla_b200_scan_fwd in training mode, but the checkpoints
+ * go to a fixed buffer of KLA_B200_STATIC_CKPT_BYTES that lives inside the
+ * library (every GPU that loads the library holds it until the process exits).
+ * args->ckpt is ignored; on success *ckpt receives the device address of the
+ * built-in buffer, to be passed as kla_b200_bwd_args.ckpt to the backward of
+ * the same step. Problems whose checkpoints (kla_b200_ckpt_bytes) exceed the
+ * buffer are refused with KLA_B200_ETOOBIG and nothing is launched. The call
+ * itself allocates nothing, on the host or on the device.
+ *
+ * The first call on each device looks up the buffer's address (the device must
+ * be current); make that first call outside any stream capture. All calls on a
+ * device share the one buffer and it keeps what the last call wrote: a forward
+ * overwrites exactly the part its own backward will read, so nothing has to be
+ * cleared, but a second forward issued before the first step's backward has
+ * finished (other stream, other thread) overwrites that step's checkpoints --
+ * calls that can overlap on the GPU race, so keep one step in flight per device.
+ */
+#define KLA_B200_STATIC_CKPT_BYTES (32u << 20)
+int kla_b200_scan_fwd_static(const kla_b200_fwd_args *args, void *stream, const void **ckpt);
 
 /*
  * Backward scan: exact adjoint of kla_b200_scan_fwd. Replaces what torch

@@ -13,11 +13,13 @@ LIB_PATH = os.environ.get("KLA_B200_LIB") or os.path.join(HERE, "libkla_b200.so"
 
 F32, BF16 = 0, 1
 MAX_DSTATE = 128
+STATIC_CKPT_BYTES = 32 << 20
 
 SYMBOLS = (
     "kla_b200_ckpt_bytes",
     "kla_b200_ckpt_interval",
     "kla_b200_scan_fwd",
+    "kla_b200_scan_fwd_static",
     "kla_b200_scan_bwd",
     "kla_b200_step",
     "kla_b200_strerror",
@@ -94,6 +96,8 @@ def load() -> ctypes.CDLL:
     lib.kla_b200_ckpt_interval.restype = c_int64
     lib.kla_b200_scan_fwd.restype = c_int
     lib.kla_b200_scan_fwd.argtypes = [POINTER(FwdArgs), c_void_p]
+    lib.kla_b200_scan_fwd_static.restype = c_int
+    lib.kla_b200_scan_fwd_static.argtypes = [POINTER(FwdArgs), c_void_p, POINTER(c_void_p)]
     lib.kla_b200_scan_bwd.restype = c_int
     lib.kla_b200_scan_bwd.argtypes = [POINTER(BwdArgs), c_void_p]
     lib.kla_b200_step.restype = c_int
@@ -125,6 +129,6 @@ def check(code: int) -> None:
     msg = load().kla_b200_strerror(code).decode()
     if code == 2:
         raise NotImplementedError(f"The b200 KLA backend: {msg}. Use backend='torch' for this case.")
-    if code in (1, 4):
+    if code in (1, 4, 5):
         raise ValueError(f"kla_b200: {msg}")
     raise RuntimeError(f"kla_b200: {msg}")

@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "../../include/kla_b200.h"
 #include "kla_bwd.cuh"
@@ -322,6 +323,7 @@ const char *kla_b200_strerror(int code) {
         case KLA_B200_EINVAL: return "invalid argument (NULL pointer, negative size or stride, or half of a pointer pair missing)";
         case KLA_B200_EUNSUPPORTED: return "unsupported configuration (d_state above 128, unsupported dtype pair, or a dimension too large)";
         case KLA_B200_EALIGN: return "pointer not aligned to its element size";
+        case KLA_B200_ETOOBIG: return "problem too large for the library's built-in checkpoint scratch (KLA_B200_STATIC_CKPT_BYTES); use kla_b200_scan_fwd with caller-provided scratch";
         case KLA_B200_ECUDA:
             snprintf(g_errbuf, sizeof(g_errbuf), "CUDA error: %s", cudaGetErrorString(g_last_cuda));
             return g_errbuf;
@@ -332,6 +334,55 @@ const char *kla_b200_strerror(int code) {
 int kla_b200_version(void) { return 100; }
 
 int64_t kla_b200_launch_count(void) { return g_launches.load(); }
+
+// ---------------------------------------------------------------------------
+// Forward scan with its checkpoint scratch inside the library.
+//
+// The scratch is a fixed array in device memory that every GPU loading this
+// library carries until the process exits. In host code the name of a
+// __device__ array is only a handle, not an address a kernel can use, so the
+// device address is looked up once per device with cudaGetSymbolAddress and
+// cached here.
+static __device__ __align__(256) unsigned char g_static_ckpt[KLA_B200_STATIC_CKPT_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void *g_static_ckpt_ptr[kMaxDevices] = {};
+
+// Device address of g_static_ckpt on the current device (set up on first use).
+int static_ckpt_address(void **out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (dev < 0 || dev >= kMaxDevices) return KLA_B200_EUNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (g_static_ckpt_ptr[dev] == nullptr) {
+        void *ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_ckpt);
+        if (e != cudaSuccess) return cuda_fail(e);
+        g_static_ckpt_ptr[dev] = ptr;
+    }
+    *out = g_static_ckpt_ptr[dev];
+    return KLA_B200_OK;
+}
+}  // namespace
+
+int kla_b200_scan_fwd_static(const kla_b200_fwd_args *args, void *stream, const void **ckpt) {
+    if (args == nullptr || ckpt == nullptr) return KLA_B200_EINVAL;
+    *ckpt = nullptr;
+    int rc = check_common(args->B, args->L, args->M, args->S, args->in_dtype, args->out_dtype);
+    if (rc) return rc;
+    if (kla_b200_ckpt_bytes(args->B, args->L, args->M, args->S) > (size_t)KLA_B200_STATIC_CKPT_BYTES)
+        return KLA_B200_ETOOBIG;
+    void *scratch = nullptr;
+    if ((rc = static_ckpt_address(&scratch))) return rc;
+    kla_b200_fwd_args a = *args;
+    a.ckpt = scratch;  // whatever the caller put there is ignored
+    rc = kla_b200_scan_fwd(&a, stream);
+    if (rc == KLA_B200_OK) *ckpt = scratch;
+    return rc;
+}
 
 int kla_b200_device_status(int *status) {
     if (status == nullptr) return KLA_B200_EINVAL;
