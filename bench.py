@@ -148,6 +148,9 @@ def cpu_oracle_run(sample, threads=None):
     channels, so cost is linear in M and the rate is scaled by M_sample/M."""
     import numpy as np
 
+    # launchers such as torchrun export OMP_NUM_THREADS=1; the CPU legs use every host core
+    if "kla_oracle" not in "".join(sys.modules):
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     from oracle import kla_oracle as O
 
     ins = make_inputs(**sample)
