@@ -144,6 +144,37 @@ typedef struct kla_b200_bwd_args {
 int kla_b200_scan_bwd(const kla_b200_bwd_args *args, void *stream);
 
 /*
+ * Slab aggregate for the sequence-sharded scan. The reference has no
+ * multi-device path; what it does have is the algebra this rests on: Moebius
+ * maps compose associatively under a common rescaling
+ * (src/kla/ops/kla_ops.py:76-116) and a carried state folds onto a scanned
+ * chunk (src/kla/ops/kernels/triton/tiled_mobius_scan.py:91-102, 194-196).
+ *
+ * One 32-byte record per lane, out[B, M, S, 8]:
+ *  adjoint == 0: the slab's state map in homogeneous coordinates (x, w, z),
+ *    P = w/x, mean = z/x: (m00 m01 m10 m11 m20 m21 m22 0) with
+ *    x' = m00 x + m01 w, w' = m10 x + m11 w, z' = m20 x + m21 w + m22 z, up to a
+ *    common factor. Needs v, lambda_v, k, a, p only.
+ *  adjoint != 0: with the slab's true initial state (lam0, eta0; NULL = unit
+ *    prior) and the upstream dy, dy_var: (K00 K01 K11 b0 b1 P_end mean_end 0),
+ *    where the backward carry (dL/dP, dL/dmean) leaving the slab's first step
+ *    is [[K00 K01][0 K11]] c_in + (b0 b1) for a carry c_in entering at its end.
+ */
+typedef struct kla_b200_slab_args {
+    int64_t B, L, M, S;
+    int32_t in_dtype, out_dtype;
+    int32_t decode_from_prior;
+    int32_t adjoint;
+    kla_b200_tensor3 v, lambda_v, k, q; /* q: adjoint only */
+    const float *a, *p;
+    const float *lam0, *eta0;           /* adjoint only; both NULL = unit prior */
+    kla_b200_tensor3 dy, dy_var;        /* adjoint only; dy_var.ptr may be NULL */
+    float *out;                         /* [B, M, S, 8] float32 */
+} kla_b200_slab_args;
+
+int kla_b200_slab_aggregate(const kla_b200_slab_args *args, void *stream);
+
+/*
  * One decode step. Replaces kla_step (src/kla/ops/kla_ops.py:293-331), which
  * the reference layer calls directly for single-token decode
  * (src/kla/layers/kla_layer.py:277-293). phi is floored at 1e-12 as there

@@ -12,6 +12,8 @@ a C-ABI shared library, wrapped in the reference's backend-callable contract.
 from .ops import KLAState, init_state, kla_scan_b200, kla_step_b200  # noqa: F401
 from .register import register, unregister  # noqa: F401
 from . import shard  # noqa: F401
+from . import seqshard  # noqa: F401
+from .seqshard import kla_scan_seq_sharded  # noqa: F401
 from ._lib import LIB_PATH, LibraryMissing, SYMBOLS  # noqa: F401
 from .build import build  # noqa: F401
 

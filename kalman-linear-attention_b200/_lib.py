@@ -22,6 +22,7 @@ SYMBOLS = (
     "kla_b200_scan_fwd_static",
     "kla_b200_scan_bwd",
     "kla_b200_step",
+    "kla_b200_slab_aggregate",
     "kla_b200_strerror",
     "kla_b200_version",
     "kla_b200_launch_count",
@@ -56,6 +57,16 @@ class BwdArgs(Structure):
         ("dv", Tensor3), ("dlambda_v", Tensor3),
         ("dk", c_void_p), ("dq", c_void_p), ("da", c_void_p), ("dp", c_void_p),
         ("dlam0", c_void_p), ("deta0", c_void_p),
+    ]
+
+
+class SlabArgs(Structure):
+    _fields_ = [
+        ("B", c_int64), ("L", c_int64), ("M", c_int64), ("S", c_int64),
+        ("in_dtype", c_int32), ("out_dtype", c_int32), ("decode_from_prior", c_int32), ("adjoint", c_int32),
+        ("v", Tensor3), ("lambda_v", Tensor3), ("k", Tensor3), ("q", Tensor3),
+        ("a", c_void_p), ("p", c_void_p), ("lam0", c_void_p), ("eta0", c_void_p),
+        ("dy", Tensor3), ("dy_var", Tensor3), ("out", c_void_p),
     ]
 
 
@@ -100,6 +111,8 @@ def load() -> ctypes.CDLL:
     lib.kla_b200_scan_fwd_static.argtypes = [POINTER(FwdArgs), c_void_p, POINTER(c_void_p)]
     lib.kla_b200_scan_bwd.restype = c_int
     lib.kla_b200_scan_bwd.argtypes = [POINTER(BwdArgs), c_void_p]
+    lib.kla_b200_slab_aggregate.restype = c_int
+    lib.kla_b200_slab_aggregate.argtypes = [POINTER(SlabArgs), c_void_p]
     lib.kla_b200_step.restype = c_int
     lib.kla_b200_step.argtypes = [POINTER(StepArgs), c_void_p]
     lib.kla_b200_strerror.restype = c_char_p

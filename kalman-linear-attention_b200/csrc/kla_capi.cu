@@ -9,6 +9,7 @@
 #include "../../include/kla_b200.h"
 #include "kla_bwd.cuh"
 #include "kla_fwd.cuh"
+#include "kla_slab.cuh"
 #include "kla_step.cuh"
 
 namespace {
@@ -194,6 +195,19 @@ int dispatch_fwd(int din, int dout, bool prior, int lpc, FwdParams &prm, const k
 int dispatch_bwd(int din, int dout, bool prior, int lpc, BwdParams &prm, const kla_b200_bwd_args &a, cudaStream_t st) {
     KLA_DISPATCH(launch_bwd, din, dout, prior, lpc, prm, a, st);
 }
+template <typename T, typename TO, int LPC, bool PRIOR>
+int launch_slab(const SlabParams &prm, bool adjoint, cudaStream_t st) {
+    constexpr int MC = 4 * (32 / LPC);
+    dim3 grid((unsigned)((prm.M + MC - 1) / MC), (unsigned)prm.B);
+    if (adjoint) kla_slab_aggregate_kernel<T, TO, kSPT, LPC, true, PRIOR><<<grid, 128, 0, st>>>(prm);
+    else kla_slab_aggregate_kernel<T, TO, kSPT, LPC, false, false><<<grid, 128, 0, st>>>(prm);
+    g_launches++;
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
+}
+int dispatch_slab(int din, int dout, bool prior, int lpc, const SlabParams &prm, bool adjoint, cudaStream_t st) {
+    KLA_DISPATCH(launch_slab, din, dout, prior, lpc, prm, adjoint, st);
+}
 int dispatch_step(int din, int dout, bool prior, int lpc, const StepParams &prm, cudaStream_t st) {
     KLA_DISPATCH(launch_step, din, dout, prior, lpc, prm, st);
 }
@@ -292,6 +306,30 @@ int kla_b200_scan_bwd(const kla_b200_bwd_args *a, void *stream) {
     prm.vec_dv = a->in_dtype == KLA_B200_F32 ? vec2_ok<float>(a->dv) : vec2_ok<__nv_bfloat16>(a->dv);
     prm.vec_dlv = a->in_dtype == KLA_B200_F32 ? vec2_ok<float>(a->dlambda_v) : vec2_ok<__nv_bfloat16>(a->dlambda_v);
     return dispatch_bwd(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc_for(a->S), prm, *a, st);
+}
+
+int kla_b200_slab_aggregate(const kla_b200_slab_args *a, void *stream) {
+    if (a == nullptr) return KLA_B200_EINVAL;
+    int rc = check_common(a->B, a->L, a->M, a->S, a->in_dtype, a->out_dtype);
+    if (rc) return rc;
+    if (a->B == 0 || a->M == 0 || a->S == 0) return KLA_B200_OK;
+    if (!a->a || !a->p || !a->out) return KLA_B200_EINVAL;
+    if ((a->lam0 == nullptr) != (a->eta0 == nullptr)) return KLA_B200_EINVAL;
+    const size_t esz = a->in_dtype == KLA_B200_F32 ? 4 : 2, osz = a->out_dtype == KLA_B200_F32 ? 4 : 2;
+    if (a->L > 0) {
+        if ((rc = check_t3(a->v, esz, true)) || (rc = check_t3(a->lambda_v, esz, true)) || (rc = check_t3(a->k, esz, true)))
+            return rc;
+        if (a->adjoint && ((rc = check_t3(a->q, esz, true)) || (rc = check_t3(a->dy, osz, true)) ||
+                           (rc = check_t3(a->dy_var, osz, false))))
+            return rc;
+    }
+    SlabParams prm{};
+    prm.B = (int)a->B; prm.L = (int)a->L; prm.M = (int)a->M; prm.S = (int)a->S;
+    prm.v = t3(a->v); prm.lv = t3(a->lambda_v); prm.k = t3(a->k); prm.q = t3(a->q);
+    prm.dy = t3(a->dy); prm.dyv = t3(a->dy_var);
+    prm.a = a->a; prm.p = a->p; prm.lam0 = a->lam0; prm.eta0 = a->eta0; prm.out = a->out;
+    return dispatch_slab(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc_for(a->S), prm, a->adjoint != 0,
+                         static_cast<cudaStream_t>(stream));
 }
 
 int kla_b200_step(const kla_b200_step_args *a, void *stream) {

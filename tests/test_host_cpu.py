@@ -251,3 +251,126 @@ def test_sharded_scan_matches_full_under_gloo(case):
         np.testing.assert_allclose(dk[b0:b1], b.dk[b0:b1], rtol=1e-9, atol=1e-11)   # summed over channels
         np.testing.assert_allclose(da[m0:m1], b.da[m0:m1], rtol=1e-9, atol=1e-11)   # summed over batch
         np.testing.assert_allclose(dp[m0:m1], b.dp[m0:m1], rtol=1e-9, atol=1e-11)
+
+
+# --------------------------------------------------------- sequence sharding
+
+def test_slab_folds_reproduce_the_scan_on_cpu():
+    """The fold algebra alone, in numpy: slab aggregates folded onto the initial
+    state give the state the oracle reaches; adjoint aggregates folded onto the
+    final-state gradient give the carry the oracle's backward hands on."""
+    import slab_math
+
+    ss = kla_b200.seqshard
+    g = load_golden("cfg2small")
+    ins = [g[n] for n in INPUTS]
+    v, lv, k, q, a, p = ins
+    cuts = (0, 50, 111, 160)
+    slabs = [slice(cuts[i], cuts[i + 1]) for i in range(3)]
+    aggs = [torch.tensor(slab_math.forward_aggregate(v[:, s], lv[:, s], k[:, s], a, p)) for s in slabs]
+    lam0, eta0 = torch.tensor(g["lam0"]), torch.tensor(g["eta0"])
+    for r in range(1, 4):
+        lam, eta = ss.prefix_state(aggs[:r], lam0, eta0, lam0.shape, "cpu")
+        t1 = cuts[r]
+        f = O.scan_fwd(v[:, :t1], lv[:, :t1], k[:, :t1], q[:, :t1], a, p, g["lam0"], g["eta0"])
+        np.testing.assert_allclose(lam.numpy(), f.lam, rtol=2e-6)
+        np.testing.assert_allclose(eta.numpy(), f.eta, rtol=2e-5, atol=1e-6)
+    # carry handed from slab 1 to slab 0 == gradient of slab 1's initial state in the oracle
+    f0 = O.scan_fwd(v[:, slabs[0]], lv[:, slabs[0]], k[:, slabs[0]], q[:, slabs[0]], a, p, g["lam0"], g["eta0"])
+    tail = slice(cuts[1], cuts[3])
+    b_tail = O.scan_bwd(v[:, tail], lv[:, tail], k[:, tail], q[:, tail], a, p, g["dy"][:, tail], g["dyvar"][:, tail],
+                        f0.lam, f0.eta, g["dlam_fin"], g["deta_fin"])
+    states = [(f0.lam, f0.eta)]
+    f1 = O.scan_fwd(v[:, slabs[1]], lv[:, slabs[1]], k[:, slabs[1]], q[:, slabs[1]], a, p, f0.lam, f0.eta)
+    states.append((f1.lam, f1.eta))
+    f2 = O.scan_fwd(v[:, slabs[2]], lv[:, slabs[2]], k[:, slabs[2]], q[:, slabs[2]], a, p, f1.lam, f1.eta)
+    adjs = [torch.tensor(slab_math.adjoint_aggregate(v[:, s], lv[:, s], k[:, s], q[:, s], a, p, g["dy"][:, s],
+                                                     g["dyvar"][:, s], *st))
+            for s, st in zip(slabs[1:], states)]
+    P_end = torch.tensor(1.0 / f2.lam)
+    cP, cm = ss.carry_from_state_grad(torch.tensor(g["dlam_fin"]), torch.tensor(g["deta_fin"]), P_end,
+                                      torch.tensor(f2.eta) * P_end)
+    cP, cm = ss.suffix_carry(adjs, cP, cm)
+    # express the carry as a gradient of (lam, eta) at the end of slab 0 and compare
+    P0 = torch.tensor(1.0 / f0.lam)
+    dlam, deta = ss.state_grad_from_carry(cP, cm, P0, torch.tensor(f0.eta) * P0)
+    np.testing.assert_allclose(dlam.numpy(), b_tail.dlam0, rtol=1e-7, atol=1e-9)
+    np.testing.assert_allclose(deta.numpy(), b_tail.deta0, rtol=1e-7, atol=1e-9)
+
+
+def _seq_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+
+    import slab_math
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        opsm = importlib.import_module("kalman-linear-attention_b200.ops")
+        ss = kla_b200.seqshard
+        n = lambda t: None if t is None else t.detach().double().numpy()
+
+        def fwd(v, lv, k, qq, a, p, lam0, eta0, prior, out_dtype, need_ckpt):
+            f = O.scan_fwd(n(v), n(lv), n(k), n(qq), n(a), n(p), n(lam0), n(eta0), prior=prior)
+            return (torch.tensor(f.y), torch.tensor(f.y_var), torch.tensor(f.lam), torch.tensor(f.eta), None)
+
+        def bwd(v, lv, k, qq, a, p, lam0, eta0, ckpt, dy, dyv, dl, de, prior, out_dtype):
+            b = O.scan_bwd(n(v), n(lv), n(k), n(qq), n(a), n(p), n(dy), n(dyv), n(lam0), n(eta0), n(dl), n(de),
+                           prior=prior)
+            return tuple(torch.tensor(x) for x in b)
+
+        def agg(v, lv, k, a, p, *, q=None, dy=None, dy_var=None, lam0=None, eta0=None, prior=False):
+            if dy is None:
+                return torch.tensor(slab_math.forward_aggregate(n(v), n(lv), n(k), n(a), n(p)))
+            return torch.tensor(slab_math.adjoint_aggregate(n(v), n(lv), n(k), n(q), n(a), n(p), n(dy), n(dy_var),
+                                                            n(lam0), n(eta0), prior))
+
+        opsm._launch_fwd, opsm._launch_bwd, ss.slab_aggregate = fwd, bwd, agg
+        opsm._require_device = lambda t: None
+        g = load_golden("cfg2small")
+        cuts = (0, 70, 160)
+        sl = slice(cuts[rank], cuts[rank + 1])
+        full = [torch.tensor(g[k_]).requires_grad_(True) for k_ in INPUTS]
+        lam0 = torch.tensor(g["lam0"]).requires_grad_(True)
+        eta0 = torch.tensor(g["eta0"]).requires_grad_(True)
+        v, lv, k, qq, a, p = full
+        ins = (v[:, sl], lv[:, sl], k[:, sl], qq[:, sl], a, p)
+        y, yv, lam, eta = ss._SeqShardedScan.apply(*ins, lam0, eta0, False, torch.float64, None)
+        loss = (y * torch.tensor(g["dy"])[:, sl]).sum() + (yv * torch.tensor(g["dyvar"])[:, sl]).sum()
+        if rank == world - 1:  # the state's gradient enters on one rank only
+            loss = loss + (lam * torch.tensor(g["dlam_fin"])).sum() + (eta * torch.tensor(g["deta_fin"])).sum()
+        grads = torch.autograd.grad(loss, full + [lam0, eta0])
+        q.put((rank, (sl.start, sl.stop), y.detach().numpy(), lam.detach().numpy(), [t.numpy() for t in grads]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sequence_sharded_scan_under_gloo():
+    """world_size 2 on CPU with the kernels replaced by the oracle and the numpy
+    aggregates: checks the collectives and folds of the autograd function."""
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_seq_worker, args=(r, 2, port, q)) for r in range(2)]
+    [p.start() for p in procs]
+    res = sorted([q.get(timeout=180) for _ in procs], key=lambda t: t[0])
+    [p.join(timeout=60) for p in procs]
+    assert all(p.exitcode == 0 for p in procs)
+    g = load_golden("cfg2small")
+    ins = [g[n] for n in INPUTS]
+    f = O.scan_fwd(*ins, g["lam0"], g["eta0"])
+    b = O.scan_bwd(*ins, g["dy"], g["dyvar"], g["lam0"], g["eta0"], g["dlam_fin"], g["deta_fin"])
+    for rank, (t0, t1), y, lam, grads in res:
+        # the folded state crosses the slab boundary in float32, as on the GPU
+        np.testing.assert_allclose(y, f.y[:, t0:t1], rtol=1e-5, atol=1e-6)
+        np.testing.assert_allclose(lam, f.lam, rtol=1e-5)  # every rank returns the last slab's posterior
+        dv, dlv, dk, dq, da, dp, dlam0, deta0 = grads
+        tol = dict(rtol=2e-4, atol=2e-5)
+        np.testing.assert_allclose(dv[:, t0:t1], b.dv[:, t0:t1], **tol)
+        np.testing.assert_allclose(dk[:, t0:t1], b.dk[:, t0:t1], **tol)
+        np.testing.assert_allclose(da, b.da, **tol)       # all-reduced over the slabs
+        np.testing.assert_allclose(dp, b.dp, **tol)
+        np.testing.assert_allclose(dlam0, b.dlam0, **tol)  # broadcast from the first slab
+        np.testing.assert_allclose(deta0, b.deta0, **tol)

@@ -1,0 +1,114 @@
+"""Sequence-sharded scan on one GPU: the slabs of a sequence are processed as
+the ranks of a box would, with the all-gather replaced by a Python list. The
+result must equal the one-shot scan -- forward, returned state and every
+gradient -- and the kernels' aggregates must match their numpy restatement."""
+
+import importlib
+
+import numpy as np
+import pytest
+import torch
+
+import slab_math
+from oracle import kla_oracle as O
+from test_scan_gpu import INPUTS, REDUCED_SLACK, _seeded, ratio, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def mods():
+    import kla_b200
+
+    return kla_b200, importlib.import_module("kalman-linear-attention_b200.ops"), kla_b200.seqshard
+
+
+def _dev(g, names, dtype=torch.float32):
+    return [torch.tensor(g[n], dtype=dtype, device="cuda") for n in names]
+
+
+@pytest.mark.parametrize("prior", [False, True])
+def test_aggregates_match_numpy_restatement(mods, prior):
+    kb, ops, ss = mods
+    g = _seeded(2, 45, 12, 16, seed=21)
+    v, lv, k, q, a, p = _dev(g, INPUTS)
+    fa = ss.slab_aggregate(v, lv, k, a, p).double().cpu().numpy()
+    ref = slab_math.forward_aggregate(*[g[n] for n in ("v", "lambda_v", "k", "a", "p")])
+    # compare as maps: apply both to a few states
+    for P0, m0 in ((1.0, 0.0), (0.3, -0.7), (5.0, 2.0)):
+        def apply(A):
+            x = A[..., 0] + A[..., 1] * P0
+            return (A[..., 2] + A[..., 3] * P0) / x, (A[..., 4] + A[..., 5] * P0 + A[..., 6] * m0) / x
+        for got, want in zip(apply(fa), apply(ref)):
+            assert ratio(got, want, rtol=2e-5, atol=2e-6) <= 1
+    dy, dyv, lam0, eta0 = _dev(g, ("dy", "dyvar", "lam0", "eta0"))
+    aa = ss.slab_aggregate(v, lv, k, a, p, q=q, dy=dy, dy_var=dyv, lam0=lam0, eta0=eta0, prior=prior)
+    ref = slab_math.adjoint_aggregate(*[g[n] for n in INPUTS], g["dy"], g["dyvar"], g["lam0"], g["eta0"], prior)
+    for i, name in enumerate(("K00", "K01", "K11", "b0", "b1", "P_end", "mean_end")):
+        err = np.abs(aa[..., i].double().cpu().numpy() - ref[..., i]).max() / (np.abs(ref[..., i]).max() + 1e-6)
+        assert err < 2e-5, f"{name}: {err:.2e}"
+
+
+@pytest.mark.parametrize("cuts,prior", [((0, 40, 100), False), ((0, 16, 33, 64, 100), False), ((0, 7, 50, 100), True)])
+def test_slabs_equal_one_shot_scan(mods, cuts, prior):
+    kb, ops, ss = mods
+    B, L, M, S = 2, 100, 24, 16
+    g = _seeded(B, L, M, S, seed=31)
+    f = O.scan_fwd(*[g[n] for n in INPUTS], g["lam0"], g["eta0"], prior=prior)
+    bw = O.scan_bwd(*[g[n] for n in INPUTS], g["dy"], g["dyvar"], g["lam0"], g["eta0"],
+                    g["dlam_fin"], g["deta_fin"], prior=prior)
+    v, lv, k, q, a, p, lam0, eta0, dy, dyv, dlf, def_ = _dev(
+        g, INPUTS + ("lam0", "eta0", "dy", "dyvar", "dlam_fin", "deta_fin"))
+    slabs = [slice(cuts[i], cuts[i + 1]) for i in range(len(cuts) - 1)]
+    R = len(slabs)
+    # ---- forward, as R ranks would
+    aggs = [ss.slab_aggregate(v[:, s], lv[:, s], k[:, s], a, p) for s in slabs]
+    fwd = []
+    for r, s in enumerate(slabs):
+        lam_in, eta_in = ss.prefix_state(aggs[:r], lam0, eta0, (B, M, S), v.device)
+        fwd.append((lam_in, eta_in) + ops._launch_fwd(v[:, s], lv[:, s], k[:, s], q[:, s], a, p,
+                                                       lam_in.contiguous(), eta_in.contiguous(), prior,
+                                                       torch.float32, True))
+    y = torch.cat([x[2] for x in fwd], 1)
+    y_var = torch.cat([x[3] for x in fwd], 1)
+    lam_fin, eta_fin = fwd[-1][4], fwd[-1][5]
+    assert ratio(y, f.y) <= 1 and ratio(y_var, f.y_var) <= 1
+    assert ratio(lam_fin, f.lam) <= 1 and ratio(eta_fin, f.eta) <= 1
+    # ---- backward
+    adjs = [ss.slab_aggregate(v[:, s], lv[:, s], k[:, s], a, p, q=q[:, s], dy=dy[:, s].contiguous(),
+                              dy_var=dyv[:, s].contiguous(), lam0=fwd[r][0].contiguous(),
+                              eta0=fwd[r][1].contiguous(), prior=prior) for r, s in enumerate(slabs)]
+    P_last = 1.0 / lam_fin.double()
+    cP_end, cm_end = ss.carry_from_state_grad(dlf.double(), def_.double(), P_last, eta_fin.double() * P_last)
+    grads = []
+    for r, s in enumerate(slabs):
+        cP, cm = ss.suffix_carry(adjs[r + 1:], cP_end, cm_end)
+        mine = adjs[r].double()
+        dls, des = ss.state_grad_from_carry(cP, cm, mine[..., 5], mine[..., 6])
+        grads.append(ops._launch_bwd(v[:, s], lv[:, s], k[:, s], q[:, s], a, p, fwd[r][0].contiguous(),
+                                     fwd[r][1].contiguous(), fwd[r][6], dy[:, s].contiguous(),
+                                     dyv[:, s].contiguous(), dls.float().contiguous(), des.float().contiguous(),
+                                     prior, torch.float32))
+    got = dict(dv=torch.cat([x[0] for x in grads], 1), dlambda_v=torch.cat([x[1] for x in grads], 1),
+               dk=torch.cat([x[2] for x in grads], 1), dq=torch.cat([x[3] for x in grads], 1),
+               da=sum(x[4] for x in grads), dp=sum(x[5] for x in grads), dlam0=grads[0][6], deta0=grads[0][7])
+    for n, t in got.items():
+        lim = REDUCED_SLACK if n in ("dk", "dq", "da", "dp") else 2.0
+        assert ratio(t, getattr(bw, n)) <= lim, f"{n}: {ratio(t, getattr(bw, n)):.2f}"
+        assert rel_err(t, getattr(bw, n)) < 2e-3, n
+
+
+def test_public_function_without_process_group_is_the_plain_scan(mods):
+    kb, ops, ss = mods
+    g = _seeded(2, 70, 16, 16, seed=41)
+    ins = [t.requires_grad_(True) for t in _dev(g, INPUTS)]
+    ins2 = [t.detach().clone().requires_grad_(True) for t in ins]
+    lam0, eta0, dy, dyv = _dev(g, ("lam0", "eta0", "dy", "dyvar"))
+    y1, yv1, s1 = kb.kla_scan_seq_sharded(*ins, initial_state=(lam0, eta0))
+    y2, yv2, s2 = kb.kla_scan_b200(*ins2, initial_state=(lam0, eta0))
+    torch.testing.assert_close(y1, y2, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(s1.lam, s2.lam, rtol=1e-5, atol=1e-6)
+    g1 = torch.autograd.grad((y1 * dy).sum() + (yv1 * dyv).sum() + s1.eta.sum(), ins)
+    g2 = torch.autograd.grad((y2 * dy).sum() + (yv2 * dyv).sum() + s2.eta.sum(), ins2)
+    for n, x, z in zip(INPUTS, g1, g2):
+        assert ((x - z).abs().max() / (z.abs().max() + 1)).item() < 1e-4, n
