@@ -374,6 +374,82 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def run_seqshard(args):
+    """Secondary workload (not the default line): BASELINE config 5, the long
+    sequence split into time slabs over the ranks -- B=2, T=131072, M=4096, S=16,
+    bfloat16 I/O with float32 state, forward + backward through
+    ``kla_scan_seq_sharded`` (slab aggregates, NCCL all-gathers, fused scans).
+    Strong scaling: the sequence is fixed, each of N ranks holds T/N steps."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    import kla_b200
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    B, T, M, S = 2, 131072, 4096, 16
+    Ls = T // world
+    g = torch.Generator(device=dev).manual_seed(rank)
+    bf = torch.bfloat16
+    v = torch.randn(B, Ls, M, generator=g, device=dev).to(bf)
+    lv = (1.0 / F.softplus(torch.randn(B, Ls, M, generator=g, device=dev))).to(bf)
+    k = torch.randn(B, Ls, S, generator=g, device=dev)
+    q = torch.randn(B, Ls, S, generator=g, device=dev)
+    k, q = (k / k.norm(dim=-1, keepdim=True)).to(bf), (q / q.norm(dim=-1, keepdim=True)).to(bf)
+    g0 = torch.Generator(device=dev).manual_seed(1234)  # a, p are shared by all ranks
+    a = torch.sigmoid(torch.randn(M, S, generator=g0, device=dev))
+    p = F.softplus(torch.randn(M, S, generator=g0, device=dev))
+    dy = torch.randn(B, Ls, M, generator=g, device=dev).to(bf)
+    dyv = torch.randn(B, Ls, M, generator=g, device=dev).to(bf)
+    ins = [t.requires_grad_(True) for t in (v, lv, k, q, a, p)]
+
+    def step():
+        y, yv, st = kla_b200.kla_scan_seq_sharded(*ins, out_dtype=bf)
+        return torch.autograd.grad([y, yv], ins, [dy, dyv])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms = ms.item()
+        fb, bb = algorithmic_bytes_per_token(M, S, esz=2)
+        peak, src = peaks()
+        ach = (fb + bb) * B * T / world / (ms * 1e-3) / 1e9  # per GPU
+        print(json.dumps({
+            "metric": METRIC, "value": B * T / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "sequence-sharded KLA scan fwd+bwd, B=2 T=131072 M=4096 S=16, bf16 I/O, "
+                                   "float32 state, time split into N slabs", "B": B, "L": T, "M": M, "S": S,
+                       "slab": Ls},
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                         "traffic": None, "peak_source": src, "note": "per GPU, whole step, algorithmic bytes"},
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -384,7 +460,12 @@ def main():
     ap.add_argument("--profile-batch", type=int, default=0,
                     help="profiling aid: run exactly one forward and one backward launch at this batch size "
                          "(same T, M, S) and exit without timing; for captures under ncu")
+    ap.add_argument("--workload", default="raw", choices=["raw", "seqshard"],
+                    help="raw = the headline raw-op workload (default); seqshard = the long-sequence, "
+                         "time-sharded workload (secondary line)")
     args = ap.parse_args()
+    if args.workload == "seqshard" and args.impl != "reference":
+        return run_seqshard(args)
     if args.impl == "reference":
         run_reference(args)
     else:
