@@ -450,6 +450,70 @@ def run_seqshard(args):
         dist.destroy_process_group()
 
 
+def run_decode(args):
+    """Secondary workload: the single-token decode step of BASELINE config 3
+    (B=32, M=2048, S=16, float32 state updated in place), 256 steps per timed
+    pass through the C ABI. State-bound: per step every lane's (lam, eta) is read
+    and written (16 B) and a, p are read (8 B per (m, s), shared over the batch)."""
+    import torch
+
+    lib = __import__("importlib").import_module("kalman-linear-attention_b200._lib")
+    L = lib.load()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, M, S, NSTEP = 32, 2048, 16, 256
+    g = torch.Generator(device=dev).manual_seed(0)
+    f32 = dict(device=dev, dtype=torch.float32)
+    v = torch.randn(NSTEP, B, M, generator=g, **f32)
+    lv = 1.0 / torch.nn.functional.softplus(torch.randn(NSTEP, B, M, generator=g, **f32))
+    k = torch.nn.functional.normalize(torch.randn(NSTEP, B, S, generator=g, **f32), dim=-1)
+    q = torch.nn.functional.normalize(torch.randn(NSTEP, B, S, generator=g, **f32), dim=-1)
+    a = torch.sigmoid(torch.randn(M, S, generator=g, **f32))
+    p = torch.nn.functional.softplus(torch.randn(M, S, generator=g, **f32))
+    lam, eta = torch.ones(B, M, S, **f32), torch.zeros(B, M, S, **f32)
+    y, yv = torch.empty(NSTEP, B, M, **f32), torch.empty(NSTEP, B, M, **f32)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    sa = [lib.StepArgs(B=B, M=M, S=S, in_dtype=0, out_dtype=0, decode_from_prior=0, v=P(v[t]), lambda_v=P(lv[t]),
+                       v_stride_b=M, lambda_v_stride_b=M, k=P(k[t]), q=P(q[t]), k_stride_b=S, q_stride_b=S,
+                       a=P(a), p=P(p), lam=P(lam), eta=P(eta), y=P(y[t]), y_var=P(yv[t]),
+                       lam_out=P(lam), eta_out=P(eta)) for t in range(NSTEP)]
+
+    def one_pass(st):
+        for t in range(NSTEP):
+            lib.check(L.kla_b200_step(ctypes.byref(sa[t]), st))
+
+    for _ in range(max(args.warmup, 3)):
+        one_pass(stream)
+    torch.cuda.synchronize()
+    # The 256 launches of a pass are captured once into a CUDA graph and replayed:
+    # a decode step is a few microseconds of GPU work, less than a host-side launch.
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        one_pass(ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (args.steps * NSTEP)
+    bytes_step = B * M * S * 16 + M * S * 8 + B * (2 * M + 2 * S + 2 * M) * 4
+    peak, src = peaks()
+    ach = bytes_step / (us * 1e-6) / 1e9
+    print(json.dumps({
+        "metric": "KLA decode steps/s (tokens/s = steps/s x batch)", "value": B / (us * 1e-6), "unit": UNIT,
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": us * NSTEP * 1e-3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "single-token decode step, B=32 M=2048 S=16, 256 steps per pass (one CUDA graph), state in place",
+                   "us_per_decode_step": us, "note": "the 16 MB state stays in the 126 MB L2 between steps"},
+        "roofline": {"bound": "hbm", "kernel": "kla_step_kernel", "achieved": ach, "peak": peak, "unit": "GB/s",
+                     "frac": ach / peak, "traffic": None, "peak_source": src, "algorithmic_bytes": bytes_step},
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -460,12 +524,14 @@ def main():
     ap.add_argument("--profile-batch", type=int, default=0,
                     help="profiling aid: run exactly one forward and one backward launch at this batch size "
                          "(same T, M, S) and exit without timing; for captures under ncu")
-    ap.add_argument("--workload", default="raw", choices=["raw", "seqshard"],
+    ap.add_argument("--workload", default="raw", choices=["raw", "seqshard", "decode"],
                     help="raw = the headline raw-op workload (default); seqshard = the long-sequence, "
                          "time-sharded workload (secondary line)")
     args = ap.parse_args()
     if args.workload == "seqshard" and args.impl != "reference":
         return run_seqshard(args)
+    if args.workload == "decode" and args.impl != "reference":
+        return run_decode(args)
     if args.impl == "reference":
         run_reference(args)
     else:

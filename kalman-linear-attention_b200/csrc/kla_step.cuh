@@ -36,31 +36,64 @@ __global__ void __launch_bounds__(128) kla_step_kernel(const StepParams prm) {
         const float vl = to_f32<T>(static_cast<const T *>(prm.v)[(long long)b * prm.v_sb + m]) * lv;
         const T *kb = static_cast<const T *>(prm.k) + (long long)b * prm.k_sb;
         const T *qb = static_cast<const T *>(prm.q) + (long long)b * prm.q_sb;
+        const long long ms0 = (long long)m * S + j * 4, bms0 = ((long long)b * M + m) * S + j * 4;
+        // one lane's four states as 16-byte vectors when the row length allows it
+        const bool vec = (S % 4) == 0;
+        float lamv[4], etav[4], av[4], pv[4], lo[4], eo[4];
+        if (vec) {
+            const float4 l4 = *reinterpret_cast<const float4 *>(prm.lam + bms0);
+            const float4 e4 = *reinterpret_cast<const float4 *>(prm.eta + bms0);
+            const float4 a4 = *reinterpret_cast<const float4 *>(prm.a + ms0);
+            const float4 p4 = *reinterpret_cast<const float4 *>(prm.p + ms0);
+            lamv[0] = l4.x; lamv[1] = l4.y; lamv[2] = l4.z; lamv[3] = l4.w;
+            etav[0] = e4.x; etav[1] = e4.y; etav[2] = e4.z; etav[3] = e4.w;
+            av[0] = a4.x; av[1] = a4.y; av[2] = a4.z; av[3] = a4.w;
+            pv[0] = p4.x; pv[1] = p4.y; pv[2] = p4.z; pv[3] = p4.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const bool in = j * 4 + i < S;
+                lamv[i] = in ? prm.lam[bms0 + i] : 1.0f;
+                etav[i] = in ? prm.eta[bms0 + i] : 0.0f;
+                av[i] = in ? prm.a[ms0 + i] : 0.0f;
+                pv[i] = in ? prm.p[ms0 + i] : 1.0f;
+            }
+        }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int s = j * 4 + i;
-            if (s < S) {
-                const long long ms = (long long)m * S + s, bms = ((long long)b * M + m) * S + s;
-                const float kv = to_f32<T>(kb[s]), qv = to_f32<T>(qb[s]);
-                const float a = prm.a[ms];
-                const float p = fmaxf(prm.p[ms], kPMin);                 // kla_ops.py:316
-                const float a2 = fmaxf(a * a, kEps);                     // :317
-                const float phi = fmaxf(lv * kv * kv, kEps);             // :310-312
-                const float lam_prev = prm.lam[bms], eta_prev = prm.eta[bms];
-                const float inv = 1.0f / fmaxf(a2 + p * lam_prev, kEps); // :319
-                const float lam = lam_prev * inv + phi;                  // :320
-                const float eta = (a * inv) * eta_prev + vl * kv;        // :321
-                float var = 1.0f / fmaxf(lam, kEps);                     // :323
-                float mean = eta * var;                                  // :324
-                if (PRIOR) {                                             // :325-327
-                    mean = a * mean;
-                    var = a2 * var + p;
-                }
-                ys = fmaf(mean, qv, ys);                                 // :329
-                yvs = fmaf(var, qv * qv, yvs);                           // :330
-                prm.lam_out[bms] = lam;
-                prm.eta_out[bms] = eta;
+            const bool in = s < S;
+            const float kv = in ? to_f32<T>(kb[s]) : 0.0f, qv = in ? to_f32<T>(qb[s]) : 0.0f;
+            const float a = av[i];
+            const float p = fmaxf(pv[i], kPMin);                     // kla_ops.py:316
+            const float a2 = fmaxf(a * a, kEps);                     // :317
+            const float phi = fmaxf(lv * kv * kv, kEps);             // :310-312
+            const float inv = 1.0f / fmaxf(a2 + p * lamv[i], kEps);  // :319
+            const float lam = lamv[i] * inv + phi;                   // :320
+            const float eta = (a * inv) * etav[i] + vl * kv;         // :321
+            float var = 1.0f / fmaxf(lam, kEps);                     // :323
+            float mean = eta * var;                                  // :324
+            if (PRIOR) {                                             // :325-327
+                mean = a * mean;
+                var = a2 * var + p;
             }
+            if (in) {
+                ys = fmaf(mean, qv, ys);                             // :329
+                yvs = fmaf(var, qv * qv, yvs);                       // :330
+            }
+            lo[i] = lam;
+            eo[i] = eta;
+        }
+        if (vec) {
+            *reinterpret_cast<float4 *>(prm.lam_out + bms0) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+            *reinterpret_cast<float4 *>(prm.eta_out + bms0) = make_float4(eo[0], eo[1], eo[2], eo[3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (j * 4 + i < S) {
+                    prm.lam_out[bms0 + i] = lo[i];
+                    prm.eta_out[bms0 + i] = eo[i];
+                }
         }
     }
 #pragma unroll
