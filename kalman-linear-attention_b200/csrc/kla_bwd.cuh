@@ -65,6 +65,9 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
     using Sm = BwdSmem<T, TO, SPT, LPC, CH, NW, NH, TT>;
     constexpr int SPAD = Sh::kSPad, MC = Sh::kMC, MCP = Sh::kMCP, NTC = Sh::kCompute;
     constexpr int NS = kBwdStages, NQ = TT / kQuarter;
+    // helper warps split by task: the first loads and stages inputs, the others finish the sums
+    constexpr int kProducers = 32, kSummers = Sh::kHelpers - kProducers;
+    static_assert(NH >= 2, "one loading and one summing helper warp at least");
     static_assert(TT == kCkptInterval && TT % kQuarter == 0, "one checkpoint per tile, whole quarters");
 
     // Declared with its alignment (no run-time rounding of the pointer) so that
@@ -74,7 +77,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
     uint64_t *empty_in = full_in + NS;                       // [NS]   compute -> helpers: stage consumed
     uint64_t *part_full = empty_in + NS;                     // [NQ]   compute -> helpers: quarter's partials written
     uint64_t *part_empty = part_full + NQ;                   // [NQ]   helpers -> compute: quarter's rows reusable
-    uint64_t *helper_sync = part_empty + NQ;                 // [1]    helper warps among themselves
+    uint64_t *stage_done = part_empty + NQ;                  // [NS]   summing helpers -> loading helper: tile's inputs no longer read
     unsigned char *in_base = smem + Sm::kBars;
     float2 *traj = reinterpret_cast<float2 *>(in_base + NS * Sm::kIn);                   // [TT*CH*SPT][NTC]
     float2 *dpart = reinterpret_cast<float2 *>(in_base + NS * Sm::kIn + Sm::kTraj);      // [TT][LPC][MCP]
@@ -92,14 +95,14 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
-            mbar_init(&full_in[s], Sh::kHelpers);
+            mbar_init(&full_in[s], kProducers);
+            mbar_init(&stage_done[s], NH - 1);
             mbar_init(&empty_in[s], NW);
         }
         for (int qd = 0; qd < NQ; ++qd) {
             mbar_init(&part_full[qd], NW);
-            mbar_init(&part_empty[qd], NH);
+            mbar_init(&part_empty[qd], NH - 1);
         }
-        mbar_init(helper_sync, NH);
         mbar_fence_init();
     }
     __syncthreads();
@@ -368,31 +371,42 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
         // ================================================================ helpers
         const int htid = tid - Sh::kCompute;
         const int hlane = htid & 31;
-        const T *vb = static_cast<const T *>(prm.v.ptr) + (long long)b * prm.v.sb;
-        const T *lb = static_cast<const T *>(prm.lv.ptr) + (long long)b * prm.lv.sb;
-        const T *kb = static_cast<const T *>(prm.k.ptr) + (long long)b * prm.k.sb;
-        const T *qb = static_cast<const T *>(prm.q.ptr) + (long long)b * prm.q.sb;
-        const TO *dyb = static_cast<const TO *>(prm.dy.ptr) + (long long)b * prm.dy.sb;
-        const TO *dyvb = has_dyv ? static_cast<const TO *>(prm.dyv.ptr) + (long long)b * prm.dyv.sb : nullptr;
-        T *dvb = static_cast<T *>(prm.dv.ptr) + (long long)b * prm.dv.sb;
-        T *dlvb = static_cast<T *>(prm.dlv.ptr) + (long long)b * prm.dlv.sb;
         constexpr uint32_t kBytesI = sizeof(T) * TT * MC, kBytesO = sizeof(TO) * TT * MC;
         int produced = 0;
         bool ok = true;
 
-        if (!has_dyv) {  // dyvar absent: its stage buffers stay zero for the whole kernel
-            for (int s = 0; s < NS; ++s)
-                for (int idx = htid; idx < TT * MC; idx += Sh::kHelpers) dyvstage(s)[idx] = from_f32<TO>(0.0f);
-        }
-
-        for (int it = 0; it <= NT && ok; ++it) {
-            if (it < NT) {  // ---- produce the it-th tile from the end
+        if (htid < kProducers) {
+            // ---- loader: TMA tiles of v, lambda_v, dy, dy_var and (k^2, k, q, q^2), NS tiles ahead
+            const T *vb = static_cast<const T *>(prm.v.ptr) + (long long)b * prm.v.sb;
+            const T *lb = static_cast<const T *>(prm.lv.ptr) + (long long)b * prm.lv.sb;
+            const T *kb = static_cast<const T *>(prm.k.ptr) + (long long)b * prm.k.sb;
+            const T *qb = static_cast<const T *>(prm.q.ptr) + (long long)b * prm.q.sb;
+            const TO *dyb = static_cast<const TO *>(prm.dy.ptr) + (long long)b * prm.dy.sb;
+            const TO *dyvb = has_dyv ? static_cast<const TO *>(prm.dyv.ptr) + (long long)b * prm.dyv.sb : nullptr;
+            if (!has_dyv) {  // dyvar absent: its stage buffers stay zero for the whole kernel
+                for (int s = 0; s < NS; ++s)
+                    for (int idx = htid; idx < TT * MC; idx += kProducers) dyvstage(s)[idx] = from_f32<TO>(0.0f);
+            }
+            // (k, q) of the next tile are fetched into registers while the current one
+            // is handed over, so the loader never sits on a global-memory latency
+            constexpr int KQP = (TT * SPAD + kProducers - 1) / kProducers;
+            float kr[KQP], qr[KQP];
+            auto load_kq = [&](int t0) {
+#pragma unroll
+                for (int e = 0; e < KQP; ++e) {
+                    const int idx = htid + e * kProducers, row = idx / SPAD, sidx = idx % SPAD;
+                    const bool in = idx < TT * SPAD && sidx < S && t0 + row < L;
+                    kr[e] = in ? to_f32<T>(kb[(long long)(t0 + row) * prm.k.st + sidx]) : 0.0f;
+                    qr[e] = in ? to_f32<T>(qb[(long long)(t0 + row) * prm.q.st + sidx]) : 0.0f;
+                }
+            };
+            if (NT > 0) load_kq((NT - 1) * TT);
+            for (int it = 0; it < NT; ++it) {
                 const int tile = NT - 1 - it, s = it % NS, t0 = tile * TT;
-                if (it >= NS && !mbar_wait(&empty_in[s], (it / NS - 1) & 1, 13, 200)) { ok = false; break; }
-                // every helper warp has finished reading this stage's v / lambda_v tiles
-                __syncwarp();
-                if (hlane == 0) mbar_arrive(helper_sync);
-                if (!mbar_wait(helper_sync, it & 1, 16)) { ok = false; break; }
+                if (it >= NS) {  // the stage is free once the compute warps and the summing helpers are done with it
+                    if (!mbar_wait(&empty_in[s], (it / NS - 1) & 1, 13, 100)) { ok = false; break; }
+                    if (!mbar_wait(&stage_done[s], (it / NS - 1) & 1, 16, 100)) { ok = false; break; }
+                }
                 if (prm.use_tma) {
                     if (htid == 0) {
                         mbar_arrive_expect_tx(&full_in[s], 2 * kBytesI + (has_dyv ? 2 : 1) * kBytesO);
@@ -402,27 +416,28 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                         if (has_dyv) tma_load_3d(dyvstage(s), &prm.tm_dyv, m_cta, t0, b, &full_in[s]);
                     }
                 } else {
-                    stage_tile_plain<T, TT, MC, Sh::kHelpers>(vstage(s), vb, prm.v.st, t0, L, m_cta, M, htid);
-                    stage_tile_plain<T, TT, MC, Sh::kHelpers>(lstage(s), lb, prm.lv.st, t0, L, m_cta, M, htid);
-                    stage_tile_plain<TO, TT, MC, Sh::kHelpers>(dystage(s), dyb, prm.dy.st, t0, L, m_cta, M, htid);
+                    stage_tile_plain<T, TT, MC, kProducers>(vstage(s), vb, prm.v.st, t0, L, m_cta, M, htid);
+                    stage_tile_plain<T, TT, MC, kProducers>(lstage(s), lb, prm.lv.st, t0, L, m_cta, M, htid);
+                    stage_tile_plain<TO, TT, MC, kProducers>(dystage(s), dyb, prm.dy.st, t0, L, m_cta, M, htid);
                     if (has_dyv)
-                        stage_tile_plain<TO, TT, MC, Sh::kHelpers>(dyvstage(s), dyvb, prm.dyv.st, t0, L, m_cta, M, htid);
+                        stage_tile_plain<TO, TT, MC, kProducers>(dyvstage(s), dyvb, prm.dyv.st, t0, L, m_cta, M, htid);
                 }
                 float4 *kq = kqstage(s);
-                for (int idx = htid; idx < TT * SPAD; idx += Sh::kHelpers) {
-                    const int row = idx / SPAD, sidx = idx % SPAD;
-                    float kv = 0.0f, qv = 0.0f;
-                    if (sidx < S && t0 + row < L) {
-                        kv = to_f32<T>(kb[(long long)(t0 + row) * prm.k.st + sidx]);
-                        qv = to_f32<T>(qb[(long long)(t0 + row) * prm.q.st + sidx]);
-                    }
-                    kq[idx] = make_float4(kv * kv, kv, qv, qv * qv);
+#pragma unroll
+                for (int e = 0; e < KQP; ++e) {
+                    const int idx = htid + e * kProducers;
+                    if (idx < TT * SPAD) kq[idx] = make_float4(kr[e] * kr[e], kr[e], qr[e], qr[e] * qr[e]);
                 }
+                if (tile > 0) load_kq(t0 - TT);
                 if (!(prm.use_tma && htid == 0)) mbar_arrive(&full_in[s]);
                 produced = it + 1;
             }
-            const int jt = it - 1;  // ---- finish the sums of the jt-th processed tile
-            if (jt >= 0) {
+        } else {
+            // ---- summing helpers: finish the sums of each processed tile, a quarter at a time
+            const int ctid = htid - kProducers;
+            T *dvb = static_cast<T *>(prm.dv.ptr) + (long long)b * prm.dv.sb;
+            T *dlvb = static_cast<T *>(prm.dlv.ptr) + (long long)b * prm.dlv.sb;
+            for (int jt = 0; jt < NT && ok; ++jt) {
                 const int tile = NT - 1 - jt, s = jt % NS, t0 = tile * TT;
                 const int n = min(TT, L - t0);
                 const bool flip = jt & 1;
@@ -431,11 +446,11 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                     // the compute warps finish the quarters of a tile from its last steps to its first
                     const int qd = NQ - 1 - step;                 // quarter in time order
                     const int prq = flip ? NQ - 1 - qd : qd;      // its physical rows
-                    if (!mbar_wait(&part_full[prq], jt & 1, 14, 200)) { ok = false; break; }
+                    if (!mbar_wait(&part_full[prq], jt & 1, 14, 100)) { ok = false; break; }
                     // dk, dq: add the CTA's channels. Compute thread t holds lane
                     // group j = t % LPC, so the partials of state s = i*LPC + jj
                     // sit at columns jj, jj + LPC, ... of row (u, i).
-                    for (int pidx = htid; pidx < kQuarter * SPAD; pidx += Sh::kHelpers) {
+                    for (int pidx = ctid; pidx < kQuarter * SPAD; pidx += kSummers) {
                         const int jj = pidx % LPC, row = pidx / LPC;  // row = (step in quarter, i)
                         const int u = row / SPT, i = row % SPT;
                         const int tt = qd * kQuarter + u;
@@ -456,7 +471,8 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                     // dv, dlambda_v: add the lane groups. v enters only through
                     // v*lambda_v (kla_ops.py:177): with D = sum_s rbar k,
                     // dv = D lambda_v and dlambda_v = sum_s phibar k^2 + D v.
-                    for (int uidx = htid; uidx < kQuarter * (MC / 2); uidx += Sh::kHelpers) {
+                    // (threads taken from the other end, so the two loops spread over the warps)
+                    for (int uidx = kSummers - 1 - ctid; uidx < kQuarter * (MC / 2); uidx += kSummers) {
                         const int u = uidx / (MC / 2), c = (uidx % (MC / 2)) * 2;
                         const int pr = prq * kQuarter + u;
                         const int tt = qd * kQuarter + u;
@@ -492,6 +508,8 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                     __syncwarp();
                     if (hlane == 0) mbar_arrive(&part_empty[prq]);
                 }
+                __syncwarp();
+                if (hlane == 0) mbar_arrive(&stage_done[s]);
             }
         }
         if (!ok && prm.use_tma && htid == 0) {

@@ -90,9 +90,15 @@ __device__ __forceinline__ void chain_inputs(float lv, float v, float k, float &
 // chain_denominator: Pp = a2 P + p and d = 1 + phi Pp. d is evaluated as
 // (a2 phi) P + (phi p + 1): the same value with one FMA, not two, between the
 // carried P and the reciprocal, which is what bounds the serial chain.
+__device__ __forceinline__ void chain_denominator_coeffs(float phi, float a2, float p, float &c1, float &c0) {
+    c1 = __fmul_rn(a2, phi);
+    c0 = __fmaf_rn(phi, p, 1.0f);
+}
 __device__ __forceinline__ float chain_denominator(float P, float phi, float a2, float p, float &Pp) {
+    float c1, c0;
+    chain_denominator_coeffs(phi, a2, p, c1, c0);
     Pp = __fmaf_rn(a2, P, p);
-    return __fmaf_rn(__fmul_rn(a2, phi), P, __fmaf_rn(phi, p, 1.0f));
+    return __fmaf_rn(c1, P, c0);
 }
 // chain_update: P = Pp g, mean = g (a mean' + Pp r), with g = 1/d.
 __device__ __forceinline__ void chain_update(float &P, float &mean, float Pp, float g, float r, float a) {

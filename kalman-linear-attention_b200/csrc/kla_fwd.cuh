@@ -53,6 +53,9 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
     using Sm = FwdSmem<T, SPT, LPC, CH, NW, NH, TT>;
     constexpr int SPAD = Sh::kSPad, MC = Sh::kMC, MCP = Sh::kMCP;
     constexpr int NS = kInStages, NO = kOutStages;
+    // helper warps split by task: the first NH/2 load and stage inputs, the others sum and store outputs
+    constexpr int kProducers = (NH / 2) * 32, kDrainers = Sh::kHelpers - kProducers;
+    static_assert(NH >= 2, "one loading and one storing helper warp at least");
     static_assert(TT == kCkptInterval, "one checkpoint per tile");
 
     // Declared with its alignment (no run-time rounding of the pointer) so that
@@ -76,12 +79,12 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
-            mbar_init(&full_in[s], Sh::kHelpers);
+            mbar_init(&full_in[s], kProducers);
             mbar_init(&empty_in[s], NW);
         }
         for (int o = 0; o < NO; ++o) {
             mbar_init(&full_out[o], NW);
-            mbar_init(&empty_out[o], NH);
+            mbar_init(&empty_out[o], kDrainers / 32);
         }
         mbar_fence_init();
     }
@@ -122,10 +125,21 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         if (ck != nullptr) ck += ((long long)b * NT * M + (m_cta + cw)) * S + j;
         const long long ck_tile = (long long)M * S;
 
-        // Inputs of one time step, fetched from shared memory one step ahead of use.
+        // The time loop is software-pipelined by hand, because a single warp is
+        // bound by the latency of its dependent instructions, not by issue slots:
+        //   fetch(t+1)   shared-memory loads of the next step's inputs
+        //   update(t)    the serial part: P -> denominator -> reciprocal -> P, mean
+        //   readout(t)   this thread's share of y, y_var to shared memory
+        //   prep(t+1)    everything of the next step that does not depend on the
+        //                state (phi, r, the two denominator coefficients)
+        // so the loads and the state-independent arithmetic of step t+1 sit
+        // between the dependent instructions of step t.
         struct StepIn {
             float lv[CH], vv[CH];
             float2 c[SPT];  // (k, q) for this thread's states
+        };
+        struct StepPre {
+            float r[CH][SPT], c0[CH][SPT], c1[CH][SPT], q[SPT];
         };
         auto fetch = [&](StepIn &in, const T *lrow, const T *vrow, const float2 *kqrow, int tt) {
 #pragma unroll
@@ -136,42 +150,54 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
 #pragma unroll
             for (int i = 0; i < SPT; ++i) in.c[i] = kqrow[tt * SPAD + i * LPC];
         };
-        // One time step for every chain of this thread. The chains are advanced
-        // phase by phase (all denominators, all reciprocals, all updates) so that
-        // the independent reciprocals are in flight together. The thread's share
-        // of the read-out goes to shared memory.
-        auto step = [&](const StepIn &in, float2 *yrow, int tt) {
-            float Pp[CH][SPT], g[CH][SPT], r[CH][SPT], ys[CH], yvs[CH];
+        auto prep = [&](StepPre &pr, const StepIn &in) {
+#pragma unroll
+            for (int i = 0; i < SPT; ++i) {
+                pr.q[i] = in.c[i].y;
+#pragma unroll
+                for (int ci = 0; ci < CH; ++ci) {
+                    float phi;
+                    chain_inputs(in.lv[ci], in.vv[ci], in.c[i].x, phi, pr.r[ci][i]);
+                    chain_denominator_coeffs(phi, ca2[ci][i], cp[ci][i], pr.c1[ci][i], pr.c0[ci][i]);
+                }
+            }
+        };
+        auto update = [&](const StepPre &pr) {
+            float Pp[CH][SPT], g[CH][SPT];
 #pragma unroll
             for (int i = 0; i < SPT; ++i)
 #pragma unroll
                 for (int ci = 0; ci < CH; ++ci) {
-                    float phi;
-                    chain_inputs(in.lv[ci], in.vv[ci], in.c[i].x, phi, r[ci][i]);
-                    g[ci][i] = chain_denominator(P[ci][i], phi, ca2[ci][i], cp[ci][i], Pp[ci][i]);
+                    Pp[ci][i] = __fmaf_rn(ca2[ci][i], P[ci][i], cp[ci][i]);
+                    g[ci][i] = __fmaf_rn(pr.c1[ci][i], P[ci][i], pr.c0[ci][i]);
                 }
 #pragma unroll
             for (int i = 0; i < SPT; ++i)
 #pragma unroll
                 for (int ci = 0; ci < CH; ++ci) g[ci][i] = rcp_approx(g[ci][i]);
 #pragma unroll
-            for (int ci = 0; ci < CH; ++ci) ys[ci] = yvs[ci] = 0.0f;
-#pragma unroll
             for (int i = 0; i < SPT; ++i)
 #pragma unroll
-                for (int ci = 0; ci < CH; ++ci) {
-                    chain_update(P[ci][i], mean[ci][i], Pp[ci][i], g[ci][i], r[ci][i], ca[ci][i]);
-                    const float q = in.c[i].y;
+                for (int ci = 0; ci < CH; ++ci)
+                    chain_update(P[ci][i], mean[ci][i], Pp[ci][i], g[ci][i], pr.r[ci][i], ca[ci][i]);
+        };
+        auto readout = [&](const StepPre &pr, float2 *yrow, int tt) {
+#pragma unroll
+            for (int ci = 0; ci < CH; ++ci) {
+                float ys = 0.0f, yvs = 0.0f;
+#pragma unroll
+                for (int i = 0; i < SPT; ++i) {
+                    const float q = pr.q[i];
                     if (PRIOR) {  // read out the one-step-ahead prior, kla_ops.py:284-286
-                        ys[ci] = fmaf(q, ca[ci][i] * mean[ci][i], ys[ci]);
-                        yvs[ci] = fmaf(q, q * fmaf(ca2[ci][i], P[ci][i], cp[ci][i]), yvs[ci]);
+                        ys = fmaf(q, ca[ci][i] * mean[ci][i], ys);
+                        yvs = fmaf(q, q * fmaf(ca2[ci][i], P[ci][i], cp[ci][i]), yvs);
                     } else {
-                        ys[ci] = fmaf(q, mean[ci][i], ys[ci]);
-                        yvs[ci] = fmaf(q, q * P[ci][i], yvs[ci]);
+                        ys = fmaf(q, mean[ci][i], ys);
+                        yvs = fmaf(q, q * P[ci][i], yvs);
                     }
                 }
-#pragma unroll
-            for (int ci = 0; ci < CH; ++ci) yrow[tt * LPC * MCP + ci] = make_float2(ys[ci], yvs[ci]);
+                yrow[tt * LPC * MCP + ci] = make_float2(ys, yvs);
+            }
         };
 
         for (int tile = 0; tile < NT; ++tile) {
@@ -192,25 +218,31 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             const T *vrow = vstage(s) + cw;
             const float2 *kqrow = kqstage(s) + j;
             float2 *yrow = ystage(o) + j * MCP + cw;
-            StepIn in0, in1;
-            fetch(in0, lrow, vrow, kqrow, 0);
+            StepIn in;
+            StepPre pr, prn;
+            fetch(in, lrow, vrow, kqrow, 0);
+            prep(pr, in);
             if (t0 + TT <= L) {
                 // four steps per trip keeps the loop body inside the instruction cache
 #pragma unroll 1
                 for (int t4 = 0; t4 < TT; t4 += 4) {
 #pragma unroll
-                    for (int u = 0; u < 4; u += 2) {
+                    for (int u = 0; u < 4; ++u) {
                         const int tt = t4 + u;
-                        fetch(in1, lrow, vrow, kqrow, tt + 1);
-                        step(in0, yrow, tt);
-                        fetch(in0, lrow, vrow, kqrow, (tt + 2) % TT);
-                        step(in1, yrow, tt + 1);
+                        fetch(in, lrow, vrow, kqrow, (tt + 1) % TT);  // the wrap-around fetch is not used
+                        update(pr);
+                        readout(pr, yrow, tt);
+                        prep(prn, in);
+                        pr = prn;
                     }
                 }
             } else {
                 for (int tt = 0; t0 + tt < L; ++tt) {
-                    fetch(in0, lrow, vrow, kqrow, tt);
-                    step(in0, yrow, tt);
+                    fetch(in, lrow, vrow, kqrow, (tt + 1) % TT);
+                    update(pr);
+                    readout(pr, yrow, tt);
+                    prep(prn, in);
+                    pr = prn;
                 }
             }
             __syncwarp();
@@ -238,20 +270,32 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         // ================================================================ helpers
         const int htid = tid - Sh::kCompute;
         const int hlane = htid & 31;
-        const T *vb = static_cast<const T *>(prm.v.ptr) + (long long)b * prm.v.sb;
-        const T *lb = static_cast<const T *>(prm.lv.ptr) + (long long)b * prm.lv.sb;
-        const T *kb = static_cast<const T *>(prm.k.ptr) + (long long)b * prm.k.sb;
-        const T *qb = static_cast<const T *>(prm.q.ptr) + (long long)b * prm.q.sb;
-        TO *yb = static_cast<TO *>(prm.y.ptr) + (long long)b * prm.y.sb;
-        TO *yvb = static_cast<TO *>(prm.yv.ptr) + (long long)b * prm.yv.sb;
         constexpr uint32_t kTileBytes = sizeof(T) * TT * MC;
         int produced = 0;
         bool ok = true;
-
-        for (int it = 0; it < NT + NO && ok; ++it) {
-            if (it < NT) {  // ---- produce tile `it`
+        if (htid < kProducers) {
+            // ---- loaders: TMA tiles of v, lambda_v and the (k, q) pairs, NS tiles ahead
+            const T *vb = static_cast<const T *>(prm.v.ptr) + (long long)b * prm.v.sb;
+            const T *lb = static_cast<const T *>(prm.lv.ptr) + (long long)b * prm.lv.sb;
+            const T *kb = static_cast<const T *>(prm.k.ptr) + (long long)b * prm.k.sb;
+            const T *qb = static_cast<const T *>(prm.q.ptr) + (long long)b * prm.q.sb;
+            // (k, q) of the next tile are fetched into registers while the current one
+            // is handed over, so the loader never sits on a global-memory latency
+            constexpr int KQP = (TT * SPAD + kProducers - 1) / kProducers;
+            float kr[KQP], qr[KQP];
+            auto load_kq = [&](int t0) {
+#pragma unroll
+                for (int e = 0; e < KQP; ++e) {
+                    const int idx = htid + e * kProducers, row = idx / SPAD, sidx = idx % SPAD;
+                    const bool in = idx < TT * SPAD && sidx < S && t0 + row < L;
+                    kr[e] = in ? to_f32<T>(kb[(long long)(t0 + row) * prm.k.st + sidx]) : 0.0f;
+                    qr[e] = in ? to_f32<T>(qb[(long long)(t0 + row) * prm.q.st + sidx]) : 0.0f;
+                }
+            };
+            load_kq(0);
+            for (int it = 0; it < NT; ++it) {
                 const int s = it % NS, t0 = it * TT;
-                if (it >= NS && !mbar_wait(&empty_in[s], (it / NS - 1) & 1, 3, 1000)) { ok = false; break; }
+                if (it >= NS && !mbar_wait(&empty_in[s], (it / NS - 1) & 1, 3, 100)) { ok = false; break; }
                 if (prm.use_tma) {
                     if (htid == 0) {
                         mbar_arrive_expect_tx(&full_in[s], 2 * kTileBytes);
@@ -259,29 +303,30 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                         tma_load_3d(lstage(s), &prm.tm_lv, m_cta, t0, b, &full_in[s]);
                     }
                 } else {
-                    stage_tile_plain<T, TT, MC, Sh::kHelpers>(vstage(s), vb, prm.v.st, t0, L, m_cta, M, htid);
-                    stage_tile_plain<T, TT, MC, Sh::kHelpers>(lstage(s), lb, prm.lv.st, t0, L, m_cta, M, htid);
+                    stage_tile_plain<T, TT, MC, kProducers>(vstage(s), vb, prm.v.st, t0, L, m_cta, M, htid);
+                    stage_tile_plain<T, TT, MC, kProducers>(lstage(s), lb, prm.lv.st, t0, L, m_cta, M, htid);
                 }
                 float2 *kq = kqstage(s);
-                for (int idx = htid; idx < TT * SPAD; idx += Sh::kHelpers) {
-                    const int row = idx / SPAD, sidx = idx % SPAD;
-                    float kv = 0.0f, qv = 0.0f;
-                    if (sidx < S && t0 + row < L) {
-                        kv = to_f32<T>(kb[(long long)(t0 + row) * prm.k.st + sidx]);
-                        qv = to_f32<T>(qb[(long long)(t0 + row) * prm.q.st + sidx]);
-                    }
-                    kq[idx] = make_float2(kv, qv);
+#pragma unroll
+                for (int e = 0; e < KQP; ++e) {
+                    const int idx = htid + e * kProducers;
+                    if (idx < TT * SPAD) kq[idx] = make_float2(kr[e], qr[e]);
                 }
+                if (it + 1 < NT) load_kq(t0 + TT);
                 if (!(prm.use_tma && htid == 0)) mbar_arrive(&full_in[s]);
                 produced = it + 1;
             }
-            const int jt = it - NO;  // ---- drain the read-out of tile `jt`
-            if (jt >= 0) {
+        } else {
+            // ---- drainers: per finished tile, sum the LPC partial read-outs and store y, y_var
+            const int dtid = htid - kProducers;
+            TO *yb = static_cast<TO *>(prm.y.ptr) + (long long)b * prm.y.sb;
+            TO *yvb = static_cast<TO *>(prm.yv.ptr) + (long long)b * prm.yv.sb;
+            for (int jt = 0; jt < NT; ++jt) {
                 const int o = jt % NO, t0 = jt * TT;
-                if (!mbar_wait(&full_out[o], (jt / NO) & 1, 4, 1000)) { ok = false; break; }
-                output_pass<TO, LPC, MC, MCP, TT, Sh::kHelpers>(
+                if (!mbar_wait(&full_out[o], (jt / NO) & 1, 4, 100)) { ok = false; break; }
+                output_pass<TO, LPC, MC, MCP, TT, kDrainers>(
                     ystage(o), yb + (long long)t0 * prm.y.st, prm.y.st, prm.vec_y,
-                    yvb + (long long)t0 * prm.yv.st, prm.yv.st, prm.vec_yv, min(TT, L - t0), m_cta, M, htid,
+                    yvb + (long long)t0 * prm.yv.st, prm.yv.st, prm.vec_yv, min(TT, L - t0), m_cta, M, dtid,
                     [](float2 acc, int, int, float &o0, float &o1) { o0 = acc.x; o1 = acc.y; });
                 __syncwarp();
                 if (hlane == 0) mbar_arrive(&empty_out[o]);
