@@ -215,10 +215,13 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
             for (int qd = 0; qd < NQ; ++qd) {
                 const int prq = flip ? NQ - 1 - qd : qd;  // physical quarter written by steps 4qd..4qd+3
                 if (ti > 0 && !mbar_wait(&part_empty[prq], (ti - 1) & 1, 12)) { ok = false; break; }
+                if (n == TT) {
 #pragma unroll
-                for (int u = 0; u < kQuarter; ++u) {
-                    const int tt = qd * kQuarter + u;
-                    if (tt < n) replay_step(tt, prq, u);
+                    for (int u = 0; u < kQuarter; ++u) replay_step(qd * kQuarter + u, prq, u);
+                } else {
+#pragma unroll 1
+                    for (int u = 0; u < kQuarter; ++u)
+                        if (qd * kQuarter + u < n) replay_step(qd * kQuarter + u, prq, u);
                 }
             }
             if (!ok) break;
@@ -330,10 +333,13 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
 #pragma unroll 1
             for (int qd = NQ - 1; qd >= 0; --qd) {
                 const int prq = flip ? NQ - 1 - qd : qd;
+                if (n == TT) {
 #pragma unroll
-                for (int u = kQuarter - 1; u >= 0; --u) {
-                    const int tt = qd * kQuarter + u;
-                    if (tt < n) reverse_step(tt, prq, u);
+                    for (int u = kQuarter - 1; u >= 0; --u) reverse_step(qd * kQuarter + u, prq, u);
+                } else {
+#pragma unroll 1
+                    for (int u = kQuarter - 1; u >= 0; --u)
+                        if (qd * kQuarter + u < n) reverse_step(qd * kQuarter + u, prq, u);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&part_full[prq]);
