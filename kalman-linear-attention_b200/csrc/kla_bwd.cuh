@@ -17,7 +17,7 @@
 //   da += ubar mean'   da2 += Ppbar P'   dp += Ppbar
 //
 // Every sum that crosses threads is left in shared memory by the compute warps
-// and finished by the helper warps, four steps (one "quarter" of a tile) at a
+// and finished by the helper warps, eight steps (one "segment", half a tile) at a
 // time, while the compute warps carry on:
 //   * sums over s (dv, dlambda_v): LPC partials per (t, channel);
 //   * sums over m (dk, dq): one partial per compute thread per (t, state),
@@ -31,7 +31,7 @@
 namespace kla {
 
 constexpr int kBwdStages = 2;  // input stages in flight
-constexpr int kQuarter = 4;    // steps per hand-over of partial sums
+constexpr int kSeg = 8;         // steps per hand-over of partial sums (a "segment" of a tile)
 
 struct alignas(64) BwdParams {
     CUtensorMap tm_v, tm_lv, tm_dy, tm_dyv;
@@ -64,19 +64,19 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
     using Sh = ScanShape<SPT, LPC, CH, NW, NH, TT>;
     using Sm = BwdSmem<T, TO, SPT, LPC, CH, NW, NH, TT>;
     constexpr int SPAD = Sh::kSPad, MC = Sh::kMC, MCP = Sh::kMCP, NTC = Sh::kCompute;
-    constexpr int NS = kBwdStages, NQ = TT / kQuarter;
+    constexpr int NS = kBwdStages, NQ = TT / kSeg;
     // helper warps split by task: the first loads and stages inputs, the others finish the sums
     constexpr int kProducers = 32, kSummers = Sh::kHelpers - kProducers;
     static_assert(NH >= 2, "one loading and one summing helper warp at least");
-    static_assert(TT == kCkptInterval && TT % kQuarter == 0, "one checkpoint per tile, whole quarters");
+    static_assert(TT == kCkptInterval && TT % kSeg == 0, "one checkpoint per tile, whole segments");
 
     // Declared with its alignment (no run-time rounding of the pointer) so that
     // the compiler keeps every access below in the shared address space.
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t *full_in = reinterpret_cast<uint64_t *>(smem);  // [NS]   helpers -> compute: stage loaded
     uint64_t *empty_in = full_in + NS;                       // [NS]   compute -> helpers: stage consumed
-    uint64_t *part_full = empty_in + NS;                     // [NQ]   compute -> helpers: quarter's partials written
-    uint64_t *part_empty = part_full + NQ;                   // [NQ]   helpers -> compute: quarter's rows reusable
+    uint64_t *part_full = empty_in + NS;                     // [NQ]   compute -> helpers: segment's partials written
+    uint64_t *part_empty = part_full + NQ;                   // [NQ]   helpers -> compute: segment's rows reusable
     uint64_t *stage_done = part_empty + NQ;                  // [NS]   summing helpers -> loading helper: tile's inputs no longer read
     unsigned char *in_base = smem + Sm::kBars;
     float2 *traj = reinterpret_cast<float2 *>(in_base + NS * Sm::kIn);                   // [TT*CH*SPT][NTC]
@@ -108,15 +108,15 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
     __syncthreads();
 
     // traj holds one float2 per compute thread for every (step, channel ci,
-    // state i): row = ((pq*kQuarter + u)*CH + ci)*SPT + i, rows of NTC slots padded
+    // state i): row = ((pq*kSeg + u)*CH + ci)*SPT + i, rows of NTC slots padded
     // by kRowPad so that the helpers, whose lanes read different rows at the same
-    // column, do not collide on shared-memory banks. The quarter a time step
+    // column, do not collide on shared-memory banks. The segment a time step
     // lands in alternates direction from one processed tile to the next (pq = qd
-    // or NQ-1-qd), so that the replay of a tile writes quarters in the order in
+    // or NQ-1-qd), so that the replay of a tile writes segments in the order in
     // which the previous tile's partials were consumed; u is a compile-time
     // constant wherever a row is formed.
     constexpr int ROW = NTC + Sm::kRowPad;
-    auto trow = [&](int pq, int u, int ci, int i) { return (((pq * kQuarter + u) * CH + ci) * SPT + i) * ROW; };
+    auto trow = [&](int pq, int u, int ci, int i) { return (((pq * kSeg + u) * CH + ci) * SPT + i) * ROW; };
 
     if (warp < NW) {
         // =============================================================== compute
@@ -208,20 +208,20 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                     for (int ci = 0; ci < CH; ++ci)
                         chain_update(P[ci][i], mean[ci][i], Pp[ci][i], g[ci][i], r[ci][i], ca[ci][i]);
             };
-            // A quarter's rows hold the previous tile's partial sums until the
+            // A segment's rows hold the previous tile's partial sums until the
             // helpers have consumed them.
             bool ok = true;
 #pragma unroll 1
             for (int qd = 0; qd < NQ; ++qd) {
-                const int prq = flip ? NQ - 1 - qd : qd;  // physical quarter written by steps 4qd..4qd+3
+                const int prq = flip ? NQ - 1 - qd : qd;  // physical segment written by steps kSeg*qd .. kSeg*qd + kSeg - 1
                 if (ti > 0 && !mbar_wait(&part_empty[prq], (ti - 1) & 1, 12)) { ok = false; break; }
                 if (n == TT) {
 #pragma unroll
-                    for (int u = 0; u < kQuarter; ++u) replay_step(qd * kQuarter + u, prq, u);
+                    for (int u = 0; u < kSeg; ++u) replay_step(qd * kSeg + u, prq, u);
                 } else {
 #pragma unroll 1
-                    for (int u = 0; u < kQuarter; ++u)
-                        if (qd * kQuarter + u < n) replay_step(qd * kQuarter + u, prq, u);
+                    for (int u = 0; u < kSeg; ++u)
+                        if (qd * kSeg + u < n) replay_step(qd * kSeg + u, prq, u);
                 }
             }
             if (!ok) break;
@@ -328,18 +328,18 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                 // this thread's share of the sums over s
 #pragma unroll
                 for (int ci = 0; ci < CH; ++ci)
-                    dpart[((pq * kQuarter + u) * LPC + j) * MCP + cw + ci] = make_float2(dvl[ci], dlphi[ci]);
+                    dpart[((pq * kSeg + u) * LPC + j) * MCP + cw + ci] = make_float2(dvl[ci], dlphi[ci]);
             };
 #pragma unroll 1
             for (int qd = NQ - 1; qd >= 0; --qd) {
                 const int prq = flip ? NQ - 1 - qd : qd;
                 if (n == TT) {
 #pragma unroll
-                    for (int u = kQuarter - 1; u >= 0; --u) reverse_step(qd * kQuarter + u, prq, u);
+                    for (int u = kSeg - 1; u >= 0; --u) reverse_step(qd * kSeg + u, prq, u);
                 } else {
 #pragma unroll 1
-                    for (int u = kQuarter - 1; u >= 0; --u)
-                        if (qd * kQuarter + u < n) reverse_step(qd * kQuarter + u, prq, u);
+                    for (int u = kSeg - 1; u >= 0; --u)
+                        if (qd * kSeg + u < n) reverse_step(qd * kSeg + u, prq, u);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&part_full[prq]);
@@ -439,7 +439,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                 produced = it + 1;
             }
         } else {
-            // ---- summing helpers: finish the sums of each processed tile, a quarter at a time
+            // ---- summing helpers: finish the sums of each processed tile, a segment at a time
             const int ctid = htid - kProducers;
             T *dvb = static_cast<T *>(prm.dv.ptr) + (long long)b * prm.dv.sb;
             T *dlvb = static_cast<T *>(prm.dlv.ptr) + (long long)b * prm.dlv.sb;
@@ -449,17 +449,17 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                 const bool flip = jt & 1;
                 const T *lt = lstage(s), *vt = vstage(s);
                 for (int step = 0; step < NQ && ok; ++step) {
-                    // the compute warps finish the quarters of a tile from its last steps to its first
-                    const int qd = NQ - 1 - step;                 // quarter in time order
+                    // the compute warps finish the segments of a tile from its last steps to its first
+                    const int qd = NQ - 1 - step;                 // segment in time order
                     const int prq = flip ? NQ - 1 - qd : qd;      // its physical rows
                     if (!mbar_wait(&part_full[prq], jt & 1, 14, 100)) { ok = false; break; }
                     // dk, dq: add the CTA's channels. Compute thread t holds lane
                     // group j = t % LPC, so the partials of state s = i*LPC + jj
                     // sit at columns jj, jj + LPC, ... of row (u, i).
-                    for (int pidx = ctid; pidx < kQuarter * SPAD; pidx += kSummers) {
-                        const int jj = pidx % LPC, row = pidx / LPC;  // row = (step in quarter, i)
+                    for (int pidx = ctid; pidx < kSeg * SPAD; pidx += kSummers) {
+                        const int jj = pidx % LPC, row = pidx / LPC;  // row = (step in segment, i)
                         const int u = row / SPT, i = row % SPT;
-                        const int tt = qd * kQuarter + u;
+                        const int tt = qd * kSeg + u;
                         const int st = i * LPC + jj;
                         const float2 *src = traj + trow(prq, u, 0, i) + jj;
                         float sk0 = 0.0f, sq0 = 0.0f, sk1 = 0.0f, sq1 = 0.0f;
@@ -478,10 +478,10 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                     // v*lambda_v (kla_ops.py:177): with D = sum_s rbar k,
                     // dv = D lambda_v and dlambda_v = sum_s phibar k^2 + D v.
                     // (threads taken from the other end, so the two loops spread over the warps)
-                    for (int uidx = kSummers - 1 - ctid; uidx < kQuarter * (MC / 2); uidx += kSummers) {
+                    for (int uidx = kSummers - 1 - ctid; uidx < kSeg * (MC / 2); uidx += kSummers) {
                         const int u = uidx / (MC / 2), c = (uidx % (MC / 2)) * 2;
-                        const int pr = prq * kQuarter + u;
-                        const int tt = qd * kQuarter + u;
+                        const int pr = prq * kSeg + u;
+                        const int tt = qd * kSeg + u;
                         if (tt >= n || m_cta + c >= M) continue;
                         float ax = 0.0f, ay = 0.0f, bx = 0.0f, by = 0.0f;
 #pragma unroll
