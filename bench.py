@@ -49,7 +49,7 @@ def algorithmic_bytes_per_token(M, S, esz=4):
 
 # ncu-measured DRAM traffic per launch at the bench workload (bytes, read + write), copied
 # from profiles/kla_scan_fwd_bwd_B8_T4096_M1024_S16_f32.md.
-NCU_TRAFFIC = {"kla_bwd_kernel": 1074.9e6, "kla_fwd_kernel": 759.5e6}
+NCU_TRAFFIC = {"kla_bwd_kernel": 1074.4e6, "kla_fwd_kernel": 758.4e6}
 
 
 def make_inputs(seed=0, **w):
