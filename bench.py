@@ -341,15 +341,16 @@ def run_b200(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "raw KLA scan fwd+bwd, B=8 T=4096 M=1024 S=16 per GPU, fp32 I/O and state",
+            "config": {"workload": f"raw KLA scan fwd+bwd, B={B} T=4096 M=1024 S=16 per GPU, fp32 I/O and state"
+                                   + ("" if B == 8 else " (batch sweep, not the headline workload)"),
                        **WORK, "sharding": "batch shard per rank, no collective",
                        "l2": "inputs+outputs per step (1.1 GB) exceed the 126 MB L2; no explicit flush"},
             "roofline": {"bound": "hbm", "kernel": "kla_bwd_kernel", "achieved": ach_bwd, "peak": peak,
-                         "unit": "GB/s", "frac": ach_bwd / peak, "traffic": NCU_TRAFFIC["kla_bwd_kernel"],
+                         "unit": "GB/s", "frac": ach_bwd / peak, "traffic": NCU_TRAFFIC["kla_bwd_kernel"] * B / 8,
                          "peak_source": peak_src, "algorithmic_bytes": bwd_bytes, "ms": bwd_ms,
                          "nominal_peak_gbs": 8000.0, "frac_of_nominal": ach_bwd / 8000.0},
             "roofline_fwd": {"bound": "hbm", "kernel": "kla_fwd_kernel", "achieved": ach_fwd, "peak": peak,
-                             "unit": "GB/s", "frac": ach_fwd / peak, "traffic": NCU_TRAFFIC["kla_fwd_kernel"],
+                             "unit": "GB/s", "frac": ach_fwd / peak, "traffic": NCU_TRAFFIC["kla_fwd_kernel"] * B / 8,
                              "algorithmic_bytes": fwd_bytes, "ms": fwd_ms},
             "roofline_step": {"achieved": ach_step, "peak": peak, "unit": "GB/s", "frac": ach_step / peak},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -524,10 +525,15 @@ def main():
     ap.add_argument("--profile-batch", type=int, default=0,
                     help="profiling aid: run exactly one forward and one backward launch at this batch size "
                          "(same T, M, S) and exit without timing; for captures under ncu")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="raw workload only: batch size per GPU instead of 8, for the occupancy sweep "
+                         "(B=4 leaves one CTA per SM, B=16 fills every SM); the headline stays B=8")
     ap.add_argument("--workload", default="raw", choices=["raw", "seqshard", "decode"],
                     help="raw = the headline raw-op workload (default); seqshard = the long-sequence, "
                          "time-sharded workload (secondary line)")
     args = ap.parse_args()
+    if args.batch > 0:
+        WORK["B"] = args.batch
     if args.workload == "seqshard" and args.impl != "reference":
         return run_seqshard(args)
     if args.workload == "decode" and args.impl != "reference":

@@ -106,6 +106,35 @@ __device__ __forceinline__ void chain_update(float &P, float &mean, float Pp, fl
     mean = __fmul_rn(g, __fmaf_rn(Pp, r, __fmul_rn(a, mean)));
 }
 
+// The same pieces for two chains at a time. sm_100 issues an fp32 multiply, add
+// or FMA on a pair of values held in an aligned register pair as one
+// instruction; every lane of it rounds like the scalar instruction, so the pair
+// forms give bit-identical results while taking half the issue slots.
+__device__ __forceinline__ float2 mul2(float2 x, float2 y) { return __fmul2_rn(x, y); }
+__device__ __forceinline__ float2 fma2(float2 x, float2 y, float2 z) { return __ffma2_rn(x, y, z); }
+__device__ __forceinline__ float2 add2(float2 x, float2 y) { return __fadd2_rn(x, y); }
+__device__ __forceinline__ float2 neg2(float2 x) { return make_float2(-x.x, -x.y); }
+__device__ __forceinline__ float2 dup2(float x) { return make_float2(x, x); }
+__device__ __forceinline__ float2 rcp_approx2(float2 x) { return make_float2(rcp_approx(x.x), rcp_approx(x.y)); }
+// element i of an array of pairs (i is a compile-time constant after unrolling)
+template <int N>
+__device__ __forceinline__ float &pair_el(float2 (&arr)[N], int i) {
+    return (i & 1) ? arr[i >> 1].y : arr[i >> 1].x;
+}
+__device__ __forceinline__ void chain_inputs2(float2 lv, float2 v, float2 k, float2 &phi, float2 &r) {
+    const float2 lk = mul2(lv, k);
+    phi = mul2(lk, k);
+    r = mul2(v, lk);
+}
+__device__ __forceinline__ void chain_denominator_coeffs2(float2 phi, float2 a2, float2 p, float2 &c1, float2 &c0) {
+    c1 = mul2(a2, phi);
+    c0 = fma2(phi, p, make_float2(1.0f, 1.0f));
+}
+__device__ __forceinline__ void chain_update2(float2 &P, float2 &mean, float2 Pp, float2 g, float2 r, float2 a) {
+    P = mul2(Pp, g);
+    mean = mul2(g, fma2(Pp, r, mul2(a, mean)));
+}
+
 template <typename T>
 __device__ __forceinline__ float to_f32(T x);
 template <>

@@ -1,5 +1,6 @@
 // Fused forward scan kernel: lambda_v, v, k, q -> y, y_var, final state, and
-// (for training) a checkpoint of every chain's state once per tile.
+// (for training) a checkpoint of every chain's state once per checkpoint
+// interval.
 //
 // Nothing of shape [B, L, M, S] is ever written: phi, r, the gain, the
 // posterior and the read-out all live in registers. Per token the kernel reads
@@ -7,12 +8,18 @@
 // y_var (2M).
 //
 // The CTA is split into NW compute warps and NH helper warps.
-//   compute warps  run the recurrence only: per step they read their inputs
-//                  from a shared-memory stage and leave their share of the
-//                  read-out sums (over their SPT states) in shared memory;
-//   helper warps   feed them: TMA tile loads of v and lambda_v (one elected
-//                  thread), (k, q) interleaving, and per finished tile the sum
-//                  of the LPC partial read-outs and the stores of y, y_var.
+//   compute warps  run the recurrence only. A thread owns SPT states of one
+//                  channel and works on them two at a time with the paired
+//                  fp32 instructions of sm_100 (kla_common.cuh). Per step it
+//                  reads its inputs from a shared-memory stage and leaves its
+//                  share of the read-out sums in shared memory. The time loop
+//                  is software-pipelined by hand (see below).
+//   loader warps   (the first NH/2 helpers) feed them: TMA tile loads of v and
+//                  lambda_v issued by one elected thread, and the (k, q) values
+//                  of a tile regrouped by owning lane; k, q of the next tile are
+//                  already in registers when a stage becomes free.
+//   drainer warps  (the other helpers) finish a tile: they add the LPC partial
+//                  read-outs of every (step, channel) and store y, y_var.
 // Stages are handed over with mbarriers, so the compute warps see neither
 // global-memory latency nor a CTA-wide barrier inside the time loop.
 #pragma once
@@ -53,6 +60,8 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
     using Sm = FwdSmem<T, SPT, LPC, CH, NW, NH, TT>;
     constexpr int SPAD = Sh::kSPad, MC = Sh::kMC, MCP = Sh::kMCP;
     constexpr int NS = kInStages, NO = kOutStages;
+    constexpr int HP = SPT / 2;  // pairs of states per thread
+    static_assert(SPT % 2 == 0, "states are processed in pairs");
     // helper warps split by task: the first NH/2 load and stage inputs, the others sum and store outputs
     constexpr int kProducers = (NH / 2) * 32, kDrainers = Sh::kHelpers - kProducers;
     static_assert(NH >= 2, "one loading and one storing helper warp at least");
@@ -69,7 +78,8 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
     unsigned char *out_base = in_base + NS * Sm::kIn;
     auto vstage = [&](int s) { return reinterpret_cast<T *>(in_base + s * Sm::kIn); };
     auto lstage = [&](int s) { return reinterpret_cast<T *>(in_base + s * Sm::kIn + Sm::kTile); };
-    auto kqstage = [&](int s) { return reinterpret_cast<float2 *>(in_base + s * Sm::kIn + 2 * Sm::kTile); };
+    // (k, q) of a step, grouped by owning lane: [TT][LPC][2][SPT] floats, state s = i * LPC + j at [j][.][i]
+    auto kqstage = [&](int s) { return reinterpret_cast<float *>(in_base + s * Sm::kIn + 2 * Sm::kTile); };
     auto ystage = [&](int o) { return reinterpret_cast<float2 *>(out_base + o * Sm::kOut); };
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -95,9 +105,11 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         const int j = lane % LPC, cl = lane / LPC;
         const int cw = warp * Sh::kCPW + cl * CH;  // first channel of this thread, CTA-relative
 
-        // Per-chain constants and state. Padding chains (s >= S or m >= M) get
-        // a = 0, p = 1, so their variance sits at 1 and their mean at 0.
-        float ca[CH][SPT], ca2[CH][SPT], cp[CH][SPT], P[CH][SPT], mean[CH][SPT];
+        // Per-chain constants and state, held as pairs of chains (states i = 2h and
+        // 2h + 1) so that the arithmetic below runs on the paired fp32
+        // instructions. Padding chains (s >= S or m >= M) get a = 0, p = 1, so
+        // their variance sits at 1 and their mean at 0.
+        float2 ca[CH][HP], ca2[CH][HP], cp[CH][HP], P[CH][HP], mean[CH][HP];
 #pragma unroll
         for (int ci = 0; ci < CH; ++ci) {
             const int m = m_cta + cw + ci;
@@ -107,17 +119,17 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                 const bool live = (m < M) && (s < S);
                 const float av = live ? prm.a[(long long)m * S + s] : 0.0f;
                 const float pv = live ? prm.p[(long long)m * S + s] : 1.0f;
-                ca[ci][i] = av;
-                ca2[ci][i] = live ? fmaxf(av * av, kEps) : 0.0f;
-                cp[ci][i] = fmaxf(pv, kPMin);
+                pair_el(ca[ci], i) = av;
+                pair_el(ca2[ci], i) = live ? fmaxf(av * av, kEps) : 0.0f;
+                pair_el(cp[ci], i) = fmaxf(pv, kPMin);
                 float lam = 1.0f, eta = 0.0f;
                 if (live && prm.lam0 != nullptr) {
                     lam = prm.lam0[((long long)b * M + m) * S + s];
                     eta = prm.eta0[((long long)b * M + m) * S + s];
                 }
                 const float P0 = 1.0f / fmaxf(lam, kLamMin);
-                P[ci][i] = P0;
-                mean[ci][i] = eta * P0;
+                pair_el(P[ci], i) = P0;
+                pair_el(mean[ci], i) = eta * P0;
             }
         }
         // checkpoint pointer of chain (ci = 0, i = 0); advanced by one tile per tile
@@ -136,67 +148,89 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         // between the dependent instructions of step t.
         struct StepIn {
             float lv[CH], vv[CH];
-            float2 c[SPT];  // (k, q) for this thread's states
+            float2 k[HP], q[HP];  // this thread's states, in pairs
         };
         struct StepPre {
-            float r[CH][SPT], c0[CH][SPT], c1[CH][SPT], q[SPT];
+            float2 r[CH][HP], c0[CH][HP], c1[CH][HP], q[HP];
         };
-        auto fetch = [&](StepIn &in, const T *lrow, const T *vrow, const float2 *kqrow, int tt) {
+        auto fetch = [&](StepIn &in, const T *lrow, const T *vrow, const float *kqrow, int tt) {
 #pragma unroll
             for (int ci = 0; ci < CH; ++ci) {
                 in.lv[ci] = to_f32<T>(lrow[tt * MC + ci]);
                 in.vv[ci] = to_f32<T>(vrow[tt * MC + ci]);
             }
+            const float *row = kqrow + tt * 2 * SPAD;
+            if constexpr (SPT == 4) {
+                const float4 kk = *reinterpret_cast<const float4 *>(row);
+                const float4 qq = *reinterpret_cast<const float4 *>(row + SPT);
+                in.k[0] = make_float2(kk.x, kk.y);
+                in.k[1] = make_float2(kk.z, kk.w);
+                in.q[0] = make_float2(qq.x, qq.y);
+                in.q[1] = make_float2(qq.z, qq.w);
+            } else {
 #pragma unroll
-            for (int i = 0; i < SPT; ++i) in.c[i] = kqrow[tt * SPAD + i * LPC];
+                for (int h = 0; h < HP; ++h) {
+                    in.k[h] = *reinterpret_cast<const float2 *>(row + 2 * h);
+                    in.q[h] = *reinterpret_cast<const float2 *>(row + SPT + 2 * h);
+                }
+            }
         };
         auto prep = [&](StepPre &pr, const StepIn &in) {
 #pragma unroll
-            for (int i = 0; i < SPT; ++i) {
-                pr.q[i] = in.c[i].y;
+            for (int h = 0; h < HP; ++h) {
+                pr.q[h] = in.q[h];
 #pragma unroll
                 for (int ci = 0; ci < CH; ++ci) {
-                    float phi;
-                    chain_inputs(in.lv[ci], in.vv[ci], in.c[i].x, phi, pr.r[ci][i]);
-                    chain_denominator_coeffs(phi, ca2[ci][i], cp[ci][i], pr.c1[ci][i], pr.c0[ci][i]);
+                    float2 phi;
+                    chain_inputs2(dup2(in.lv[ci]), dup2(in.vv[ci]), in.k[h], phi, pr.r[ci][h]);
+                    chain_denominator_coeffs2(phi, ca2[ci][h], cp[ci][h], pr.c1[ci][h], pr.c0[ci][h]);
                 }
             }
         };
         auto update = [&](const StepPre &pr) {
-            float Pp[CH][SPT], g[CH][SPT];
+            float2 Pp[CH][HP], g[CH][HP];
 #pragma unroll
-            for (int i = 0; i < SPT; ++i)
+            for (int h = 0; h < HP; ++h)
 #pragma unroll
                 for (int ci = 0; ci < CH; ++ci) {
-                    Pp[ci][i] = __fmaf_rn(ca2[ci][i], P[ci][i], cp[ci][i]);
-                    g[ci][i] = __fmaf_rn(pr.c1[ci][i], P[ci][i], pr.c0[ci][i]);
+                    Pp[ci][h] = fma2(ca2[ci][h], P[ci][h], cp[ci][h]);
+                    g[ci][h] = fma2(pr.c1[ci][h], P[ci][h], pr.c0[ci][h]);
                 }
 #pragma unroll
-            for (int i = 0; i < SPT; ++i)
+            for (int h = 0; h < HP; ++h)
 #pragma unroll
-                for (int ci = 0; ci < CH; ++ci) g[ci][i] = rcp_approx(g[ci][i]);
+                for (int ci = 0; ci < CH; ++ci) g[ci][h] = rcp_approx2(g[ci][h]);
 #pragma unroll
-            for (int i = 0; i < SPT; ++i)
+            for (int h = 0; h < HP; ++h)
 #pragma unroll
                 for (int ci = 0; ci < CH; ++ci)
-                    chain_update(P[ci][i], mean[ci][i], Pp[ci][i], g[ci][i], pr.r[ci][i], ca[ci][i]);
+                    chain_update2(P[ci][h], mean[ci][h], Pp[ci][h], g[ci][h], pr.r[ci][h], ca[ci][h]);
         };
         auto readout = [&](const StepPre &pr, float2 *yrow, int tt) {
 #pragma unroll
             for (int ci = 0; ci < CH; ++ci) {
-                float ys = 0.0f, yvs = 0.0f;
+                float2 ys = make_float2(0.0f, 0.0f), yvs = ys;
 #pragma unroll
-                for (int i = 0; i < SPT; ++i) {
-                    const float q = pr.q[i];
+                for (int h = 0; h < HP; ++h) {
+                    const float2 q = pr.q[h];
+                    float2 mo, Po;
                     if (PRIOR) {  // read out the one-step-ahead prior, kla_ops.py:284-286
-                        ys = fmaf(q, ca[ci][i] * mean[ci][i], ys);
-                        yvs = fmaf(q, q * fmaf(ca2[ci][i], P[ci][i], cp[ci][i]), yvs);
+                        mo = mul2(ca[ci][h], mean[ci][h]);
+                        Po = fma2(ca2[ci][h], P[ci][h], cp[ci][h]);
                     } else {
-                        ys = fmaf(q, mean[ci][i], ys);
-                        yvs = fmaf(q, q * P[ci][i], yvs);
+                        mo = mean[ci][h];
+                        Po = P[ci][h];
+                    }
+                    const float2 qP = mul2(q, Po);
+                    if (h == 0) {
+                        ys = mul2(q, mo);
+                        yvs = mul2(q, qP);
+                    } else {
+                        ys = fma2(q, mo, ys);
+                        yvs = fma2(q, qP, yvs);
                     }
                 }
-                yrow[tt * LPC * MCP + ci] = make_float2(ys, yvs);
+                yrow[tt * LPC * MCP + ci] = make_float2(ys.x + ys.y, yvs.x + yvs.y);
             }
         };
 
@@ -211,12 +245,12 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
 #pragma unroll
                     for (int i = 0; i < SPT; ++i)
                         if (m_cta + cw + ci < M && i * LPC + j < S)
-                            ck[ci * S + i * LPC] = make_float2(P[ci][i], mean[ci][i]);
+                            ck[ci * S + i * LPC] = make_float2(pair_el(P[ci], i), pair_el(mean[ci], i));
                 ck += ck_tile;
             }
             const T *lrow = lstage(s) + cw;
             const T *vrow = vstage(s) + cw;
-            const float2 *kqrow = kqstage(s) + j;
+            const float *kqrow = kqstage(s) + j * 2 * SPT;
             float2 *yrow = ystage(o) + j * MCP + cw;
             StepIn in;
             StepPre pr, prn;
@@ -260,9 +294,9 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             for (int i = 0; i < SPT; ++i) {
                 const int s = i * LPC + j;
                 if (m < M && s < S) {
-                    const float lam = 1.0f / P[ci][i];
+                    const float lam = 1.0f / pair_el(P[ci], i);
                     prm.lam_fin[((long long)b * M + m) * S + s] = lam;
-                    prm.eta_fin[((long long)b * M + m) * S + s] = mean[ci][i] * lam;
+                    prm.eta_fin[((long long)b * M + m) * S + s] = pair_el(mean[ci], i) * lam;
                 }
             }
         }
@@ -306,11 +340,15 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                     stage_tile_plain<T, TT, MC, kProducers>(vstage(s), vb, prm.v.st, t0, L, m_cta, M, htid);
                     stage_tile_plain<T, TT, MC, kProducers>(lstage(s), lb, prm.lv.st, t0, L, m_cta, M, htid);
                 }
-                float2 *kq = kqstage(s);
+                float *kq = kqstage(s);
 #pragma unroll
                 for (int e = 0; e < KQP; ++e) {
-                    const int idx = htid + e * kProducers;
-                    if (idx < TT * SPAD) kq[idx] = make_float2(kr[e], qr[e]);
+                    const int idx = htid + e * kProducers, row = idx / SPAD, sidx = idx % SPAD;
+                    if (idx < TT * SPAD) {
+                        float *dst = kq + row * 2 * SPAD + (sidx % LPC) * 2 * SPT + sidx / LPC;
+                        dst[0] = kr[e];
+                        dst[SPT] = qr[e];
+                    }
                 }
                 if (it + 1 < NT) load_kq(t0 + TT);
                 if (!(prm.use_tma && htid == 0)) mbar_arrive(&full_in[s]);
