@@ -515,6 +515,98 @@ def run_decode(args):
     }), flush=True)
 
 
+def run_rawpair(args):
+    """Secondary line: the raw scan pair over materialised [B, L, M, S] coefficients
+    (Moebius scan + affine scan, forward and backward: four launches per step), at the
+    headline shape. These kernels move 12-40 bytes per lane-step and are HBM-bound."""
+    import torch
+
+    lib = __import__("importlib").import_module("kalman-linear-attention_b200._lib")
+    L_ = lib.load()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, T, M, S = (args.batch or 4), WORK["L"], WORK["M"], WORK["S"]
+    N = M * S
+    g = torch.Generator(device=dev).manual_seed(0)
+    f32 = dict(device=dev, dtype=torch.float32)
+    shape = (B, T, N)
+    # leaves in the filter's operating range: a contracting Moebius map and gains below one
+    A = 0.5 + 0.5 * torch.rand(shape, generator=g, **f32)
+    Bc = 0.1 * torch.rand(shape, generator=g, **f32)
+    C = 0.2 * torch.rand(shape, generator=g, **f32)
+    D = torch.ones(shape, **f32)
+    alpha = 0.5 + 0.5 * torch.rand(shape, generator=g, **f32)
+    r = torch.randn(shape, generator=g, **f32)
+    dout = torch.randn(shape, generator=g, **f32)
+    lam, eta = torch.empty(shape, **f32), torch.empty(shape, **f32)
+    d4 = [torch.empty(shape, **f32) for _ in range(4)]
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+    def mk(ins, outs):
+        a = lib.RawScanArgs(B=B, L=T, N=N)
+        for i, t in enumerate(ins):
+            a.inp[i] = t.data_ptr()
+        for i, t in enumerate(outs):
+            a.out[i] = t.data_ptr()
+        return a
+
+    calls = [
+        ("mobius_scan_fwd", mk((A, Bc, C, D), (lam,)), 5),
+        ("mobius_scan_bwd", mk((A, Bc, C, D, lam, dout), d4), 10),
+        ("affine_scan_fwd", mk((alpha, r), (eta,)), 3),
+        ("affine_scan_bwd", mk((alpha, eta, dout), d4[:2]), 5),
+    ]
+    fns = [(name, getattr(L_, "kla_b200_" + name), a, words) for name, a, words in calls]
+
+    def one_step(ev=None):
+        for i, (name, fn, a, _) in enumerate(fns):
+            if ev is not None:
+                ev[i][0].record()
+            lib.check(fn(ctypes.byref(a), stream))
+            if ev is not None:
+                ev[i][1].record()
+
+    for _ in range(max(args.warmup, 3)):
+        one_step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in fns]
+           for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        one_step(evs[i])
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    total_ms = e0.elapsed_time(e1)
+    peak, src = peaks()
+    per = {}
+    for i, (name, _, _, words) in enumerate(fns):
+        ms = sum(e[i][0].elapsed_time(e[i][1]) for e in evs) / args.steps
+        by = words * 4 * B * T * N
+        per[name] = {"ms": ms, "algorithmic_bytes": by, "achieved": by / (ms * 1e-3) / 1e9,
+                     "frac": by / (ms * 1e-3) / 1e9 / peak}
+    top = "mobius_scan_bwd"
+    all_bytes = sum(v["algorithmic_bytes"] for v in per.values())
+    print(json.dumps({
+        "metric": "raw scan pair (Moebius + affine, fwd+bwd) tokens/s", "value": B * T * args.steps / (total_ms * 1e-3),
+        "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "gpu_launches": 4 * args.steps,
+        "config": {"workload": f"raw scan pair over [B, L, M, S] coefficients, B={B} T={T} M={M} S={S}, fp32; "
+                               "four launches per step (Moebius fwd, bwd, affine fwd, bwd)",
+                   "l2": f"each launch streams {5 * 4 * B * T * N / 1e9:.1f}-{10 * 4 * B * T * N / 1e9:.1f} GB, far beyond the 126 MB L2"},
+        "roofline": {"bound": "hbm", "kernel": "kla_rawscan_kernel<MobiusBwd>", "achieved": per[top]["achieved"],
+                     "peak": peak, "unit": "GB/s", "frac": per[top]["frac"], "traffic": NCU_TRAFFIC.get("rawscan_mobius_bwd"),
+                     "peak_source": src, "algorithmic_bytes": per[top]["algorithmic_bytes"], "ms": per[top]["ms"]},
+        "roofline_all": per,
+        "step_gbs": all_bytes / (total_ms / args.steps * 1e-3) / 1e9,
+        "clocks": clocks,
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -528,7 +620,7 @@ def main():
     ap.add_argument("--batch", type=int, default=0,
                     help="raw workload only: batch size per GPU instead of 8, for the occupancy sweep "
                          "(B=4 leaves one CTA per SM, B=16 fills every SM); the headline stays B=8")
-    ap.add_argument("--workload", default="raw", choices=["raw", "seqshard", "decode"],
+    ap.add_argument("--workload", default="raw", choices=["raw", "seqshard", "decode", "rawpair"],
                     help="raw = the headline raw-op workload (default); seqshard = the long-sequence, "
                          "time-sharded workload (secondary line)")
     args = ap.parse_args()
@@ -538,6 +630,8 @@ def main():
         return run_seqshard(args)
     if args.workload == "decode" and args.impl != "reference":
         return run_decode(args)
+    if args.workload == "rawpair" and args.impl != "reference":
+        return run_rawpair(args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -197,6 +197,38 @@ typedef struct kla_b200_step_args {
 
 int kla_b200_step(const kla_b200_step_args *args, void *stream);
 
+/*
+ * Raw scan pair over materialised coefficients. Replaces the reference's
+ * tiled_mobius_scan(A, B, C, D, lam0) and tiled_affine_scan(alpha, r)
+ * (src/kla/ops/kernels/triton/tiled_mobius_scan.py:301-311) and their exact
+ * backwards (TiledMobiusScan.backward, :266-279; TiledAffineScan.backward,
+ * :289-296), for callers that already hold the per-(b, t, m, s) coefficients:
+ *
+ *   Moebius  lam_t = (A_t lam' + B_t) / max(C_t lam' + D_t, 1e-12),  lam_{-1} = lam0 (default 1)
+ *   affine   eta_t = alpha_t eta' + r_t,                             eta_{-1} = 0
+ *
+ * Every tensor is a contiguous float32 [B, L, N] with N = M*S lanes per row
+ * (the reference's [B, L, M, S]); state0 / dstate0 are [B, N].
+ *
+ *   call             in[]                       out[]
+ *   mobius_scan_fwd  A B C D                    lam
+ *   mobius_scan_bwd  A B C D lam dlam           dA dB dC dD   (+ dstate0 = dlam0, may be NULL)
+ *   affine_scan_fwd  alpha r                    eta
+ *   affine_scan_bwd  alpha eta deta             dalpha dr
+ */
+typedef struct kla_b200_rawscan_args {
+    int64_t B, L, N;
+    const float *in[6];
+    float *out[4];
+    const float *state0; /* Moebius calls: lam0 [B, N] or NULL = 1; affine calls: must be NULL */
+    float *dstate0;      /* mobius_scan_bwd: out [B, N] or NULL; other calls: must be NULL */
+} kla_b200_rawscan_args;
+
+int kla_b200_mobius_scan_fwd(const kla_b200_rawscan_args *args, void *stream);
+int kla_b200_mobius_scan_bwd(const kla_b200_rawscan_args *args, void *stream);
+int kla_b200_affine_scan_fwd(const kla_b200_rawscan_args *args, void *stream);
+int kla_b200_affine_scan_bwd(const kla_b200_rawscan_args *args, void *stream);
+
 /* Human-readable text for a return code; for KLA_B200_ECUDA it includes the
  * CUDA error string of the failing call on this thread. */
 const char *kla_b200_strerror(int code);

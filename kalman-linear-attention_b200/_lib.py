@@ -23,6 +23,10 @@ SYMBOLS = (
     "kla_b200_scan_bwd",
     "kla_b200_step",
     "kla_b200_slab_aggregate",
+    "kla_b200_mobius_scan_fwd",
+    "kla_b200_mobius_scan_bwd",
+    "kla_b200_affine_scan_fwd",
+    "kla_b200_affine_scan_bwd",
     "kla_b200_strerror",
     "kla_b200_version",
     "kla_b200_launch_count",
@@ -32,6 +36,14 @@ SYMBOLS = (
 
 class Tensor3(Structure):
     _fields_ = [("ptr", c_void_p), ("stride_b", c_int64), ("stride_t", c_int64)]
+
+
+class RawScanArgs(Structure):
+    _fields_ = [
+        ("B", c_int64), ("L", c_int64), ("N", c_int64),
+        ("inp", c_void_p * 6), ("out", c_void_p * 4),
+        ("state0", c_void_p), ("dstate0", c_void_p),
+    ]
 
 
 class FwdArgs(Structure):
@@ -113,6 +125,10 @@ def load() -> ctypes.CDLL:
     lib.kla_b200_scan_bwd.argtypes = [POINTER(BwdArgs), c_void_p]
     lib.kla_b200_slab_aggregate.restype = c_int
     lib.kla_b200_slab_aggregate.argtypes = [POINTER(SlabArgs), c_void_p]
+    for name in ("mobius_scan_fwd", "mobius_scan_bwd", "affine_scan_fwd", "affine_scan_bwd"):
+        fn = getattr(lib, "kla_b200_" + name)
+        fn.restype = c_int
+        fn.argtypes = [POINTER(RawScanArgs), c_void_p]
     lib.kla_b200_step.restype = c_int
     lib.kla_b200_step.argtypes = [POINTER(StepArgs), c_void_p]
     lib.kla_b200_strerror.restype = c_char_p

@@ -9,6 +9,7 @@
 #include "../../include/kla_b200.h"
 #include "kla_bwd.cuh"
 #include "kla_fwd.cuh"
+#include "kla_rawscan.cuh"
 #include "kla_slab.cuh"
 #include "kla_step.cuh"
 
@@ -213,6 +214,50 @@ int dispatch_step(int din, int dout, bool prior, int lpc, const StepParams &prm,
 }
 
 }  // namespace
+
+namespace {
+template <class Op>
+int launch_rawscan(const kla_b200_rawscan_args *a, void *stream, bool takes_state0, bool gives_dstate0) {
+    if (a == nullptr || a->B < 0 || a->L < 0 || a->N < 0) return KLA_B200_EINVAL;
+    if (a->B > 65535 || a->L > (1 << 30) || a->N > (1 << 30)) return KLA_B200_EUNSUPPORTED;
+    if ((!takes_state0 && a->state0 != nullptr) || (!gives_dstate0 && a->dstate0 != nullptr)) return KLA_B200_EINVAL;
+    for (int i = 0; i < Op::NIN; ++i) {
+        if (a->in[i] == nullptr) return KLA_B200_EINVAL;
+        if (!aligned(a->in[i], sizeof(float))) return KLA_B200_EALIGN;
+    }
+    for (int k = 0; k < Op::NOUT; ++k) {
+        if (a->out[k] == nullptr) return KLA_B200_EINVAL;
+        if (!aligned(a->out[k], sizeof(float))) return KLA_B200_EALIGN;
+    }
+    if (a->B == 0 || a->N == 0) return KLA_B200_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    RawParams prm{};
+    prm.B = (int)a->B; prm.L = (int)a->L; prm.N = (int)a->N;
+    prm.NT = (int)((a->L + kRawTT - 1) / kRawTT);
+    prm.state0 = a->state0; prm.dstate0 = a->dstate0;
+    bool tma = !g_no_tma && a->L > 0;
+    for (int i = 0; i < Op::NIN; ++i) {
+        prm.in[i] = a->in[i];
+        const kla_b200_tensor3 t{const_cast<float *>(a->in[i]), a->L * a->N, a->N};
+        tma = tma && make_tile_map<float>(&prm.tm_in[i], t, a->B, a->L, a->N, kRawLC, kRawTT + (i == Op::HALO ? 1 : 0));
+    }
+    for (int k = 0; k < Op::NOUT; ++k) {
+        prm.out[k] = a->out[k];
+        const kla_b200_tensor3 t{a->out[k], a->L * a->N, a->N};
+        tma = tma && make_tile_map<float>(&prm.tm_out[k], t, a->B, a->L, a->N, kRawLC, kRawTT);
+    }
+    prm.use_tma = tma;
+    auto kern = kla_rawscan_kernel<Op>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RawSmem<Op>::kTotal);
+    if (e != cudaSuccess) return cuda_fail(e);
+    dim3 grid((unsigned)((a->N + kRawLC - 1) / kRawLC), (unsigned)a->B);
+    kern<<<grid, kRawLC + 32, RawSmem<Op>::kTotal, st>>>(prm);
+    g_launches++;
+    e = cudaGetLastError();
+    return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
+}
+}  // namespace
+
 
 extern "C" {
 
@@ -420,6 +465,19 @@ int kla_b200_scan_fwd_static(const kla_b200_fwd_args *args, void *stream, const 
     rc = kla_b200_scan_fwd(&a, stream);
     if (rc == KLA_B200_OK) *ckpt = scratch;
     return rc;
+}
+
+int kla_b200_mobius_scan_fwd(const kla_b200_rawscan_args *a, void *stream) {
+    return launch_rawscan<MobiusFwd>(a, stream, true, false);
+}
+int kla_b200_mobius_scan_bwd(const kla_b200_rawscan_args *a, void *stream) {
+    return launch_rawscan<MobiusBwd>(a, stream, true, true);
+}
+int kla_b200_affine_scan_fwd(const kla_b200_rawscan_args *a, void *stream) {
+    return launch_rawscan<AffineFwd>(a, stream, false, false);
+}
+int kla_b200_affine_scan_bwd(const kla_b200_rawscan_args *a, void *stream) {
+    return launch_rawscan<AffineBwd>(a, stream, false, false);
 }
 
 int kla_b200_device_status(int *status) {
