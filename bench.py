@@ -48,8 +48,10 @@ def algorithmic_bytes_per_token(M, S, esz=4):
 
 
 # ncu-measured DRAM traffic per launch at the bench workload (bytes, read + write), copied
-# from profiles/kla_scan_fwd_bwd_B8_T4096_M1024_S16_f32.md.
-NCU_TRAFFIC = {"kla_bwd_kernel": 1074.4e6, "kla_fwd_kernel": 758.4e6}
+# from profiles/kla_scan_fwd_bwd_B8_T4096_M1024_S16_f32.md; the raw-scan figure is per batch
+# entry (captured at B=1, T=4096, M*S=16384; traffic is proportional to B), from
+# profiles/kla_rawscan_T4096_N16384_f32.md.
+NCU_TRAFFIC = {"kla_bwd_kernel": 1074.4e6, "kla_fwd_kernel": 763.2e6, "rawscan_mobius_bwd_per_batch": 2651.5e6}
 
 
 def make_inputs(seed=0, **w):
@@ -599,7 +601,7 @@ def run_rawpair(args):
                                "four launches per step (Moebius fwd, bwd, affine fwd, bwd)",
                    "l2": f"each launch streams {5 * 4 * B * T * N / 1e9:.1f}-{10 * 4 * B * T * N / 1e9:.1f} GB, far beyond the 126 MB L2"},
         "roofline": {"bound": "hbm", "kernel": "kla_rawscan_kernel<MobiusBwd>", "achieved": per[top]["achieved"],
-                     "peak": peak, "unit": "GB/s", "frac": per[top]["frac"], "traffic": NCU_TRAFFIC.get("rawscan_mobius_bwd"),
+                     "peak": peak, "unit": "GB/s", "frac": per[top]["frac"], "traffic": NCU_TRAFFIC["rawscan_mobius_bwd_per_batch"] * B,
                      "peak_source": src, "algorithmic_bytes": per[top]["algorithmic_bytes"], "ms": per[top]["ms"]},
         "roofline_all": per,
         "step_gbs": all_bytes / (total_ms / args.steps * 1e-3) / 1e9,

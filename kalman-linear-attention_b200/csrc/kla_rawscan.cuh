@@ -59,7 +59,7 @@ constexpr float kRawDenMin = 1e-12f;  // floor on the Moebius denominator, tiled
 // step(x, prev, y): x = this step's inputs, prev = the HALO input at t-1 (the
 // initial state at t = 0).
 struct MobiusFwd {  // in: A B C D   out: lam
-    static constexpr int NIN = 4, NOUT = 1, HALO = -1, NSI = 3;
+    static constexpr int NIN = 4, NOUT = 1, HALO = -1, NSI = 2;
     static constexpr bool REV = false;
     static constexpr float kPrior = 1.0f;  // lam0 when none is given, tiled_mobius_scan.py:303-305
     float lam;
@@ -107,7 +107,7 @@ struct MobiusBwd {  // in: A B C D lam dlam   out: dA dB dC dD
 // Adjoint of the affine scan (tiled_mobius_scan.py:289-296): mu_t = deta_t + alpha_{t+1} mu_{t+1},
 // dalpha = mu eta', dr = mu.
 struct AffineBwd {  // in: alpha eta deta   out: dalpha dr
-    static constexpr int NIN = 3, NOUT = 2, HALO = 1, NSI = 3;
+    static constexpr int NIN = 3, NOUT = 2, HALO = 1, NSI = 2;
     static constexpr bool REV = true;
     static constexpr float kPrior = 0.0f;
     float c;

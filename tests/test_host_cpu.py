@@ -157,6 +157,36 @@ def test_register_into_reference_dispatch(oracle_launches):
         sys.path.remove(REF_SRC)
 
 
+@needs_ref
+def test_cli_rows_for_the_reference_command_line(capsys):
+    """`python -m kla --check-backends` with the b200 row added: listed, described, and reported
+    unusable on a machine without a CUDA device (src/kla/__main__.py:104-150, :290-300)."""
+    pytest.importorskip("tyro")
+    sys.path.insert(0, REF_SRC)
+    try:
+        import kla.__main__ as kla_main
+        from importlib import import_module
+
+        cli = import_module("kalman-linear-attention_b200.cli")
+        try:
+            assert cli.main(["--check-backends"]) == 0
+            out = capsys.readouterr().out
+            row = [ln for ln in out.splitlines() if " b200 " in ln]
+            assert len(row) == 1 and "sm_100a" in row[0]
+            if not torch.cuda.is_available():
+                assert row[0].lstrip().startswith("[ ]") and "needs a CUDA device" in row[0]
+                # the reference's own checks run the backend and report its refusal as a skip, not a crash
+                assert cli.main(["--test-backends", "b200"]) == 1
+                assert "skipped" in capsys.readouterr().out
+            assert "b200" in kla_main._requirements() and kla_main._MODULES["b200"] == "kla_b200"
+            cli.install_rows()  # idempotent
+            assert getattr(kla_main._requirements, "_kla_b200", False)
+        finally:
+            kla_b200.unregister()
+    finally:
+        sys.path.remove(REF_SRC)
+
+
 # ------------------------------------------------------------------- sharding
 
 def test_blocks_tile_the_lane_grid():
