@@ -198,6 +198,73 @@ typedef struct kla_b200_step_args {
 int kla_b200_step(const kla_b200_step_args *args, void *stream);
 
 /*
+ * Decode of one layer, token by token: the elementwise work around the layer's
+ * three projections as two calls. The projections themselves (in_proj,
+ * sensor_proj, out_proj: plain GEMMs) stay with the caller.
+ *
+ * kla_b200_conv_step advances the causal depthwise convolution by one token.
+ * Replaces CausalConv1d.forward for L = 1 (src/kla/layers/common.py:87-96):
+ * z = act(bias + sum_j w[d, j] window[j]), window = (state, x), then the state
+ * keeps the last K-1 inputs. x, state and z share one element type (dtype).
+ */
+#define KLA_B200_ACT_SILU 0
+#define KLA_B200_ACT_GELU 1
+#define KLA_B200_ACT_RELU 2
+#define KLA_B200_ACT_NONE 3
+#define KLA_B200_MAX_CONV_TAPS 8
+
+typedef struct kla_b200_conv_step_args {
+    int64_t B, D, K;      /* K taps, 1 <= K <= KLA_B200_MAX_CONV_TAPS */
+    int32_t dtype;        /* KLA_B200_F32 or KLA_B200_BF16 */
+    int32_t activation;   /* KLA_B200_ACT_* */
+    const void *x;        /* in  [B, D] */
+    int64_t x_stride_b;
+    const float *weight;  /* in  [D, K] contiguous float32 (the [D, 1, K] parameter) */
+    const float *bias;    /* in  [D] float32 or NULL */
+    void *state;          /* in/out [B, D, K-1] contiguous */
+    void *z;              /* out [B, D] contiguous */
+} kla_b200_conv_step_args;
+
+int kla_b200_conv_step(const kla_b200_conv_step_args *args, void *stream);
+
+/*
+ * kla_b200_step_layer is kla_b200_step with the layer's prologue and epilogue
+ * folded in (src/kla/layers/kla_layer.py:199-231, 277-293, 329-338): it takes
+ * the sensor projection's raw outputs and produces the input of out_proj.
+ *   k, q       l2-normalised over S when qk_norm (x / max(|x|, 1e-12)), then
+ *              clamped to [-clip_value, clip_value] when clip_value > 0
+ *   lambda_v   1 / min(softplus(log_sigma_v) + obs_var_min, obs_var_max)
+ *              (no upper clamp when obs_var_max <= 0)
+ *   y, y_var   of kla_step, then y += lambda_skip * z (lambda_skip: one value or
+ *              one per channel; skipped when NULL), then y *= g, y_var *= g^2 with
+ *              g = act(gate) (skipped when gate is NULL)
+ * All arithmetic is float32; with bfloat16 tensors the result is rounded once,
+ * at the store (the reference rounds after several of these steps).
+ */
+typedef struct kla_b200_step_layer_args {
+    int64_t B, M, S;
+    int32_t in_dtype, out_dtype;
+    int32_t decode_from_prior;
+    int32_t qk_norm;
+    int32_t gate_activation;      /* KLA_B200_ACT_* */
+    int32_t lambda_skip_len;      /* 0 (none), 1 or M */
+    float obs_var_min, obs_var_max, clip_value;
+    const void *v, *log_sigma_v;  /* [B, M] */
+    int64_t v_stride_b, log_sigma_v_stride_b;
+    const void *k, *q;            /* [B, S], raw */
+    int64_t k_stride_b, q_stride_b;
+    const void *z, *gate;         /* [B, M] or NULL */
+    int64_t z_stride_b, gate_stride_b;
+    const float *lambda_skip;     /* [lambda_skip_len] float32 or NULL */
+    const float *a, *p;           /* [M, S] */
+    const float *lam, *eta;       /* [B, M, S] */
+    void *y, *y_var;              /* [B, M] contiguous */
+    float *lam_out, *eta_out;     /* [B, M, S]; may alias lam, eta */
+} kla_b200_step_layer_args;
+
+int kla_b200_step_layer(const kla_b200_step_layer_args *args, void *stream);
+
+/*
  * Raw scan pair over materialised coefficients. Replaces the reference's
  * tiled_mobius_scan(A, B, C, D, lam0) and tiled_affine_scan(alpha, r)
  * (src/kla/ops/kernels/triton/tiled_mobius_scan.py:301-311) and their exact

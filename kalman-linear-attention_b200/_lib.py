@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, Structure, c_char_p, c_int, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("KLA_B200_LIB") or os.path.join(HERE, "libkla_b200.so")
@@ -23,6 +23,8 @@ SYMBOLS = (
     "kla_b200_scan_bwd",
     "kla_b200_step",
     "kla_b200_slab_aggregate",
+    "kla_b200_conv_step",
+    "kla_b200_step_layer",
     "kla_b200_mobius_scan_fwd",
     "kla_b200_mobius_scan_bwd",
     "kla_b200_affine_scan_fwd",
@@ -36,6 +38,33 @@ SYMBOLS = (
 
 class Tensor3(Structure):
     _fields_ = [("ptr", c_void_p), ("stride_b", c_int64), ("stride_t", c_int64)]
+
+
+ACT = {"silu": 0, "gelu": 1, "relu": 2, None: 3}
+MAX_CONV_TAPS = 8
+
+
+class ConvStepArgs(Structure):
+    _fields_ = [
+        ("B", c_int64), ("D", c_int64), ("K", c_int64),
+        ("dtype", c_int32), ("activation", c_int32),
+        ("x", c_void_p), ("x_stride_b", c_int64),
+        ("weight", c_void_p), ("bias", c_void_p), ("state", c_void_p), ("z", c_void_p),
+    ]
+
+
+class StepLayerArgs(Structure):
+    _fields_ = [
+        ("B", c_int64), ("M", c_int64), ("S", c_int64),
+        ("in_dtype", c_int32), ("out_dtype", c_int32), ("decode_from_prior", c_int32),
+        ("qk_norm", c_int32), ("gate_activation", c_int32), ("lambda_skip_len", c_int32),
+        ("obs_var_min", c_float), ("obs_var_max", c_float), ("clip_value", c_float),
+        ("v", c_void_p), ("log_sigma_v", c_void_p), ("v_stride_b", c_int64), ("log_sigma_v_stride_b", c_int64),
+        ("k", c_void_p), ("q", c_void_p), ("k_stride_b", c_int64), ("q_stride_b", c_int64),
+        ("z", c_void_p), ("gate", c_void_p), ("z_stride_b", c_int64), ("gate_stride_b", c_int64),
+        ("lambda_skip", c_void_p), ("a", c_void_p), ("p", c_void_p), ("lam", c_void_p), ("eta", c_void_p),
+        ("y", c_void_p), ("y_var", c_void_p), ("lam_out", c_void_p), ("eta_out", c_void_p),
+    ]
 
 
 class RawScanArgs(Structure):
@@ -129,6 +158,10 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, "kla_b200_" + name)
         fn.restype = c_int
         fn.argtypes = [POINTER(RawScanArgs), c_void_p]
+    lib.kla_b200_conv_step.restype = c_int
+    lib.kla_b200_conv_step.argtypes = [POINTER(ConvStepArgs), c_void_p]
+    lib.kla_b200_step_layer.restype = c_int
+    lib.kla_b200_step_layer.argtypes = [POINTER(StepLayerArgs), c_void_p]
     lib.kla_b200_step.restype = c_int
     lib.kla_b200_step.argtypes = [POINTER(StepArgs), c_void_p]
     lib.kla_b200_strerror.restype = c_char_p

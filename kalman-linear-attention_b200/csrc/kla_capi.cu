@@ -8,6 +8,7 @@
 
 #include "../../include/kla_b200.h"
 #include "kla_bwd.cuh"
+#include "kla_decode.cuh"
 #include "kla_fwd.cuh"
 #include "kla_rawscan.cuh"
 #include "kla_slab.cuh"
@@ -212,6 +213,18 @@ int dispatch_slab(int din, int dout, bool prior, int lpc, const SlabParams &prm,
 int dispatch_step(int din, int dout, bool prior, int lpc, const StepParams &prm, cudaStream_t st) {
     KLA_DISPATCH(launch_step, din, dout, prior, lpc, prm, st);
 }
+template <typename T, typename TO, int LPC, bool PRIOR>
+int launch_step_layer(const StepLayerParams &prm, cudaStream_t st) {
+    const long long threads = (long long)prm.B * prm.M * LPC;
+    const unsigned blocks = (unsigned)((threads + 127) / 128);
+    kla_step_layer_kernel<T, TO, LPC, PRIOR><<<blocks, 128, 0, st>>>(prm);
+    g_launches++;
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
+}
+int dispatch_step_layer(int din, int dout, bool prior, int lpc, const StepLayerParams &prm, cudaStream_t st) {
+    KLA_DISPATCH(launch_step_layer, din, dout, prior, lpc, prm, st);
+}
 
 }  // namespace
 
@@ -398,6 +411,60 @@ int kla_b200_step(const kla_b200_step_args *a, void *stream) {
     int lpc = 1;
     while (lpc * 4 < a->S) lpc *= 2;
     return dispatch_step(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc, prm, static_cast<cudaStream_t>(stream));
+}
+
+int kla_b200_conv_step(const kla_b200_conv_step_args *a, void *stream) {
+    if (a == nullptr || a->B < 0 || a->D < 0) return KLA_B200_EINVAL;
+    if (a->K < 1 || a->K > KLA_B200_MAX_CONV_TAPS) return KLA_B200_EUNSUPPORTED;
+    if (a->dtype != KLA_B200_F32 && a->dtype != KLA_B200_BF16) return KLA_B200_EUNSUPPORTED;
+    if (a->activation < KLA_B200_ACT_SILU || a->activation > KLA_B200_ACT_NONE) return KLA_B200_EINVAL;
+    if (a->B == 0 || a->D == 0) return KLA_B200_OK;
+    if (!a->x || !a->weight || !a->z || (a->K > 1 && !a->state) || a->x_stride_b < 0) return KLA_B200_EINVAL;
+    if (a->B * a->D > (1ll << 40)) return KLA_B200_EUNSUPPORTED;
+    const size_t esz = a->dtype == KLA_B200_F32 ? 4 : 2;
+    if (!aligned(a->x, esz) || !aligned(a->z, esz) || (a->state && !aligned(a->state, esz))) return KLA_B200_EALIGN;
+    ConvStepParams prm{};
+    prm.B = (int)a->B; prm.D = (int)a->D; prm.K = (int)a->K;
+    prm.x = a->x; prm.x_sb = a->x_stride_b; prm.w = a->weight; prm.bias = a->bias;
+    prm.state = a->state; prm.z = a->z; prm.act = a->activation;
+    const unsigned blocks = (unsigned)((a->B * a->D + 127) / 128);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (a->dtype == KLA_B200_F32) kla_conv_step_kernel<float><<<blocks, 128, 0, st>>>(prm);
+    else kla_conv_step_kernel<__nv_bfloat16><<<blocks, 128, 0, st>>>(prm);
+    g_launches++;
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
+}
+
+int kla_b200_step_layer(const kla_b200_step_layer_args *a, void *stream) {
+    if (a == nullptr) return KLA_B200_EINVAL;
+    int rc = check_common(a->B, 1, a->M, a->S, a->in_dtype, a->out_dtype);
+    if (rc) return rc;
+    if (a->gate_activation < KLA_B200_ACT_SILU || a->gate_activation > KLA_B200_ACT_NONE) return KLA_B200_EINVAL;
+    if (a->lambda_skip_len != 0 && a->lambda_skip_len != 1 && a->lambda_skip_len != a->M) return KLA_B200_EINVAL;
+    if (a->B == 0 || a->M == 0) return KLA_B200_OK;
+    if (!a->v || !a->log_sigma_v || !a->y || !a->y_var || !a->a || !a->p) return KLA_B200_EINVAL;
+    if (a->S > 0 && (!a->k || !a->q || !a->lam || !a->eta || !a->lam_out || !a->eta_out)) return KLA_B200_EINVAL;
+    if (a->lambda_skip_len != 0 && (!a->lambda_skip || !a->z)) return KLA_B200_EINVAL;
+    const size_t esz = a->in_dtype == KLA_B200_F32 ? 4 : 2, osz = a->out_dtype == KLA_B200_F32 ? 4 : 2;
+    const void *ps[] = {a->v, a->log_sigma_v, a->k, a->q, a->z, a->gate};
+    for (const void *p : ps)
+        if (p && !aligned(p, esz)) return KLA_B200_EALIGN;
+    if (!aligned(a->y, osz) || !aligned(a->y_var, osz)) return KLA_B200_EALIGN;
+    StepLayerParams prm{};
+    prm.B = (int)a->B; prm.M = (int)a->M; prm.S = (int)a->S;
+    prm.v = a->v; prm.ls = a->log_sigma_v; prm.k = a->k; prm.q = a->q;
+    prm.z = a->lambda_skip_len != 0 ? a->z : nullptr; prm.gate = a->gate;
+    prm.v_sb = a->v_stride_b; prm.ls_sb = a->log_sigma_v_stride_b; prm.k_sb = a->k_stride_b; prm.q_sb = a->q_stride_b;
+    prm.z_sb = a->z_stride_b; prm.gate_sb = a->gate_stride_b;
+    prm.a = a->a; prm.p = a->p; prm.lam = a->lam; prm.eta = a->eta;
+    prm.lam_out = a->lam_out; prm.eta_out = a->eta_out; prm.y = a->y; prm.yv = a->y_var;
+    prm.skip = a->lambda_skip_len != 0 ? a->lambda_skip : nullptr; prm.skip_len = a->lambda_skip_len;
+    prm.obs_var_min = a->obs_var_min; prm.obs_var_max = a->obs_var_max; prm.clip = a->clip_value;
+    prm.qk_norm = a->qk_norm; prm.gate_act = a->gate_activation;
+    int lpc = 1;
+    while (lpc * 4 < a->S) lpc *= 2;
+    return dispatch_step_layer(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc, prm, static_cast<cudaStream_t>(stream));
 }
 
 const char *kla_b200_strerror(int code) {

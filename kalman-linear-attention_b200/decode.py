@@ -1,0 +1,158 @@
+"""Token-by-token decode of one KLA layer on the B200 kernels.
+
+The reference layer's decode route (``KLALayer.forward`` with a state and ``L == 1``,
+src/kla/layers/kla_layer.py:295-345) is three projections with elementwise work between
+them. ``LayerDecoder.step`` keeps the projections as library GEMMs and runs the rest as two
+kernels: ``kla_b200_conv_step`` (``CausalConv1d`` advanced by one token,
+src/kla/layers/common.py:87-96) and ``kla_b200_step_layer`` (sensor post-processing, the
+filter step, skip path and gate; kla_layer.py:199-231, 277-293, 329-338).
+
+A decoder is built from plain tensors and a plain config dict, so it does not need the
+reference package at run time; ``LayerDecoder.from_layer`` reads both off a reference
+``KLALayer``. All state is updated in place, which makes a step capturable in a CUDA graph.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+CONFIG_KEYS = (
+    "d_state", "discretization", "zero_process_noise", "clip_value", "obs_var_min", "obs_var_max",
+    "value_rank", "qk_norm", "use_conv", "conv_kernel_size", "conv_activation", "use_gating",
+    "gating_activation", "use_lambda_skip", "return_variance", "decode_from_prior",
+)
+
+
+def discretize(weights: dict, config: dict):
+    """Discrete (a_bar, p_bar), each [M, S]: the reference's ``KLALayer._compute_aq``
+    (src/kla/layers/kla_layer.py:164-190) restated on plain tensors."""
+    a = -torch.exp(weights["lambda_log"].float())
+    p = weights["process_noise"].float()
+    if config["zero_process_noise"]:
+        p = p + 1e-12
+    else:
+        p = p.clamp_min(1e-7)
+        if config["clip_value"] is not None:
+            p = p.clamp_max(config["clip_value"])
+    delta = F.softplus(weights["delta"].float()) + 1e-7
+    a_bar = torch.exp(delta * a)
+    if config["discretization"] == "ou":
+        lam_pos = a.abs().clamp_min(1e-8)
+        p_bar = (p / (2.0 * lam_pos)) * (-torch.expm1(-2.0 * lam_pos * delta))
+    else:
+        p_bar = p * delta
+    return a_bar.contiguous(), p_bar.contiguous()
+
+
+class LayerDecoder:
+    def __init__(self, weights: dict, config: dict):
+        missing = [k for k in CONFIG_KEYS if k not in config]
+        if missing:
+            raise ValueError(f"decode config lacks {missing}")
+        self.w = weights
+        self.cfg = dict(config)
+        self.M, self.S = weights["delta"].shape
+        if self.S > _lib.MAX_DSTATE:
+            raise NotImplementedError(f"The b200 decode kernels support d_state <= {_lib.MAX_DSTATE}; use backend='torch'.")
+        if config["use_conv"] and config["conv_kernel_size"] > _lib.MAX_CONV_TAPS:
+            raise NotImplementedError(f"The b200 conv step supports up to {_lib.MAX_CONV_TAPS} taps; use backend='torch'.")
+        self.a_bar, self.p_bar = discretize(weights, config)
+        sensor_out = weights["sensor_proj.weight"].shape[0]
+        self.w_value = 0 if config["value_rank"] == "conv" else (
+            weights["value_expand.weight"].shape[1] if "value_expand.weight" in weights else self.M)
+        self.w_var = sensor_out - self.w_value - 2 * self.S
+        skip = weights.get("lambda_skip") if config["use_lambda_skip"] else None
+        self.skip = None if skip is None else skip.detach().float().reshape(-1).contiguous()
+        self.conv_w = None
+        if config["use_conv"]:
+            self.conv_w = weights["conv.weight"].detach().float().reshape(self.M, -1).contiguous()
+            cb = weights.get("conv.bias")
+            self.conv_b = None if cb is None else cb.detach().float().contiguous()
+
+    @classmethod
+    def from_layer(cls, layer) -> "LayerDecoder":
+        """Read weights and config off a reference ``kla.KLALayer``."""
+        weights = {k: v.detach() for k, v in layer.state_dict().items()}
+        config = {k: getattr(layer.config, k) for k in CONFIG_KEYS}
+        return cls(weights, config)
+
+    def to(self, device) -> "LayerDecoder":
+        out = LayerDecoder.__new__(LayerDecoder)
+        out.__dict__.update(self.__dict__)
+        out.w = {k: v.to(device) for k, v in self.w.items()}
+        for name in ("a_bar", "p_bar", "skip", "conv_w", "conv_b"):
+            t = getattr(self, name, None)
+            setattr(out, name, None if t is None else t.to(device))
+        return out
+
+    def init_state(self, batch: int, device, dtype=torch.float32):
+        """(conv window [B, M, K-1] or None, lam [B, M, S], eta [B, M, S]) -- kla_layer.py:152-160."""
+        conv = None
+        if self.cfg["use_conv"]:
+            conv = torch.zeros(batch, self.M, self.cfg["conv_kernel_size"] - 1, device=device, dtype=dtype)
+        lam = torch.ones(batch, self.M, self.S, device=device, dtype=torch.float32)
+        return conv, lam, torch.zeros_like(lam)
+
+    def _linear(self, x, name):
+        return F.linear(x, self.w[name + ".weight"], self.w.get(name + ".bias"))
+
+    def step(self, x: torch.Tensor, state):
+        """One token. ``x``: [B, d_model]; ``state``: the tuple of ``init_state``, updated in place.
+        Returns ``out`` [B, d_model], or ``(out, out_var)`` when the config returns variances."""
+        if not x.is_cuda:
+            raise NotImplementedError("The b200 decode kernels need CUDA tensors; use the reference layer on this device.")
+        if x.dtype not in (torch.float32, torch.bfloat16):
+            raise NotImplementedError(f"The b200 decode kernels take float32 or bfloat16 activations, not {x.dtype}.")
+        cfg, M, S = self.cfg, self.M, self.S
+        conv_state, lam, eta = state
+        B = x.shape[0]
+        dt = _lib.F32 if x.dtype == torch.float32 else _lib.BF16
+        lib = _lib.load()
+        P = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())
+        with torch.cuda.device(x.device):
+            stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            projected = self._linear(x, "in_proj")
+            z, gate = (projected[:, :M], projected[:, M:]) if cfg["use_gating"] else (projected, None)
+            if cfg["use_conv"]:
+                zc = torch.empty(B, M, device=x.device, dtype=x.dtype)
+                ca = _lib.ConvStepArgs(B=B, D=M, K=cfg["conv_kernel_size"], dtype=dt,
+                                       activation=_lib.ACT[cfg["conv_activation"]], x=P(z), x_stride_b=z.stride(0),
+                                       weight=P(self.conv_w), bias=P(self.conv_b), state=P(conv_state), z=P(zc))
+                _lib.check(lib.kla_b200_conv_step(ctypes.byref(ca), stream))
+                z = zc
+            sens = self._linear(z, "sensor_proj")
+            o = 0
+            if cfg["value_rank"] == "conv":
+                v = z
+            else:
+                v = sens[:, o:o + self.w_value]
+                o += self.w_value
+                if "value_expand.weight" in self.w:
+                    v = self._linear(v, "value_expand")
+            ls = sens[:, o:o + self.w_var]
+            o += self.w_var
+            if "var_expand.weight" in self.w:
+                ls = self._linear(ls, "var_expand")
+            k, q = sens[:, o:o + S], sens[:, o + S:o + 2 * S]
+            y = torch.empty(B, M, device=x.device, dtype=x.dtype)
+            y_var = torch.empty_like(y)
+            sa = _lib.StepLayerArgs(
+                B=B, M=M, S=S, in_dtype=dt, out_dtype=dt, decode_from_prior=int(cfg["decode_from_prior"]),
+                qk_norm=int(cfg["qk_norm"]), gate_activation=_lib.ACT[cfg["gating_activation"] if gate is not None else None],
+                lambda_skip_len=0 if self.skip is None else self.skip.numel(),
+                obs_var_min=cfg["obs_var_min"], obs_var_max=cfg["obs_var_max"] or 0.0, clip_value=cfg["clip_value"] or 0.0,
+                v=P(v), log_sigma_v=P(ls), v_stride_b=v.stride(0), log_sigma_v_stride_b=ls.stride(0),
+                k=P(k), q=P(q), k_stride_b=k.stride(0), q_stride_b=q.stride(0),
+                z=P(z), gate=P(gate), z_stride_b=z.stride(0), gate_stride_b=0 if gate is None else gate.stride(0),
+                lambda_skip=P(self.skip), a=P(self.a_bar), p=P(self.p_bar), lam=P(lam), eta=P(eta),
+                y=P(y), y_var=P(y_var), lam_out=P(lam), eta_out=P(eta))
+            _lib.check(lib.kla_b200_step_layer(ctypes.byref(sa), stream))
+            out = self._linear(y, "out_proj")
+            if cfg["return_variance"]:
+                return out, F.linear(y_var, self.w["out_proj.weight"].pow(2))
+            return out

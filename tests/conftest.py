@@ -22,7 +22,7 @@ def golden_names():
     return sorted(
         os.path.splitext(os.path.basename(p))[0]
         for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz"))
-        if os.path.basename(p) != "step.npz" and not os.path.basename(p).startswith("raw_")
+        if os.path.basename(p) != "step.npz" and not os.path.basename(p).startswith(("raw_", "decode_"))
     )
 
 

@@ -1,0 +1,144 @@
+"""Layer decode (conv step + fused sensor/filter/gate step): the B200 kernels against the
+reference layer's own token-by-token outputs (tests/golden/decode_*.npz)."""
+
+import glob
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(HERE))
+import kla_b200  # noqa: E402
+from importlib import import_module  # noqa: E402
+
+decode = import_module("kalman-linear-attention_b200.decode")
+CASES = sorted(os.path.basename(p)[7:-4] for p in glob.glob(os.path.join(HERE, "golden", "decode_*.npz")))
+REF_SRC = "/root/reference/src"
+needs_ref = pytest.mark.skipif(not os.path.isdir(REF_SRC), reason="reference package not present")
+
+
+def load(name):
+    z = dict(np.load(os.path.join(HERE, "golden", f"decode_{name}.npz")))
+    weights = {k[2:]: torch.from_numpy(v) for k, v in z.items() if k.startswith("w:")}
+    config = {}
+    for k, v in z.items():
+        if k.startswith("c:"):
+            val = v.item()
+            config[k[2:]] = None if val == "" else val
+    return z, weights, config
+
+
+def test_cases_present():
+    assert CASES == ["bare", "default", "lowrank", "variant"]
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_discretisation_matches_the_layer(name):
+    z, weights, config = load(name)
+    a_bar, p_bar = decode.discretize(weights, config)
+    np.testing.assert_allclose(a_bar.numpy(), z["a_bar"], rtol=1e-6, atol=1e-8)
+    np.testing.assert_allclose(p_bar.numpy(), z["p_bar"], rtol=1e-6, atol=1e-10)
+    dec = kla_b200.LayerDecoder(weights, config)
+    assert (dec.M, dec.S) == z["lam0"].shape[1:]
+    assert dec.w_value + dec.w_var + 2 * dec.S == weights["sensor_proj.weight"].shape[0]
+
+
+def test_cpu_tensors_are_refused():
+    _, weights, config = load("default")
+    dec = kla_b200.LayerDecoder(weights, config)
+    with pytest.raises(NotImplementedError, match="CUDA"):
+        dec.step(torch.zeros(2, 32), dec.init_state(2, "cpu"))
+    with pytest.raises(ValueError, match="lacks"):
+        kla_b200.LayerDecoder(weights, {"d_state": 8})
+
+
+@needs_ref
+def test_from_layer_reads_a_reference_layer():
+    sys.path.insert(0, REF_SRC)
+    try:
+        import kla
+
+        torch.manual_seed(0)
+        layer = kla.KLALayer(32, kla.KLAConfig(d_state=8, lambda_skip_mode="vector"))
+        dec = kla_b200.LayerDecoder.from_layer(layer)
+        a_bar, p_bar = layer._compute_aq()
+        torch.testing.assert_close(dec.a_bar, a_bar.detach())
+        torch.testing.assert_close(dec.p_bar, p_bar.detach())
+        assert dec.skip.shape == (layer.d_inner,) and dec.conv_w.shape == (layer.d_inner, 4)
+    finally:
+        sys.path.remove(REF_SRC)
+
+
+# ----------------------------------------------------------------------- GPU
+
+def _run(name, dtype, steps=3):
+    dev = torch.device("cuda:0")
+    z, weights, config = load(name)
+    weights = {k: (v.to(dtype) if k.split(".")[0] in ("in_proj", "sensor_proj", "out_proj", "value_expand", "var_expand")
+                   else v) for k, v in weights.items()}
+    dec = kla_b200.LayerDecoder(weights, config).to(dev)
+    conv = torch.from_numpy(z["conv0"]).to(dev, dtype) if "conv0" in z else None
+    state = (conv, torch.from_numpy(z["lam0"]).to(dev), torch.from_numpy(z["eta0"]).to(dev))
+    outs = []
+    for t in range(steps):
+        res = dec.step(torch.from_numpy(z["x"][t]).to(dev, dtype), state)
+        outs.append(tuple(r.float().cpu() for r in (res if isinstance(res, tuple) else (res,))))
+        outs[-1] += tuple(None if s is None else s.float().cpu().clone() for s in state)
+    return z, config, outs
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", CASES)
+def test_decode_matches_reference_layer_f32(name):
+    z, config, outs = _run(name, torch.float32)
+    for t, got in enumerate(outs):
+        n_out = 2 if config["return_variance"] else 1
+        torch.testing.assert_close(got[0], torch.from_numpy(z[f"out{t}"]), rtol=1e-4, atol=1e-5, msg=lambda m: f"out{t}: {m}")
+        if n_out == 2:
+            torch.testing.assert_close(got[1], torch.from_numpy(z[f"outvar{t}"]), rtol=1e-4, atol=1e-5)
+        conv, lam, eta = got[n_out:]
+        if conv is not None:
+            torch.testing.assert_close(conv, torch.from_numpy(z[f"conv{t + 1}"]), rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(lam, torch.from_numpy(z[f"lam{t + 1}"]), rtol=2e-5, atol=1e-6)
+        torch.testing.assert_close(eta, torch.from_numpy(z[f"eta{t + 1}"]), rtol=2e-5, atol=2e-6)
+    L = import_module("kalman-linear-attention_b200._lib")
+    assert L.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_decode_bf16_activations_stay_close():
+    z, config, outs = _run("default", torch.bfloat16)
+    for t, got in enumerate(outs):
+        ref = torch.from_numpy(z[f"out{t}"])
+        assert (got[0] - ref).abs().max() <= 3e-2 * (1.0 + ref.abs().max())
+
+
+@pytest.mark.gpu
+def test_decode_step_is_graph_capturable():
+    dev = torch.device("cuda:0")
+    z, weights, config = load("default")
+    dec = kla_b200.LayerDecoder(weights, config).to(dev)
+
+    def fresh():
+        return (torch.from_numpy(z["conv0"]).to(dev), torch.from_numpy(z["lam0"]).to(dev), torch.from_numpy(z["eta0"]).to(dev))
+
+    x = torch.from_numpy(z["x"][0]).to(dev)
+    state = fresh()
+    dec.step(x, state)  # warm-up outside capture (library handles, lazy loads)
+    state = fresh()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = dec.step(x, state)
+    torch.cuda.current_stream().wait_stream(s)
+    for buf, src in zip(state, fresh()):
+        buf.copy_(src)
+    g.replay()
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.cpu(), torch.from_numpy(z["out0"]), rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(state[1].cpu(), torch.from_numpy(z["lam1"]), rtol=2e-5, atol=1e-6)
