@@ -67,6 +67,38 @@ def test_bad_arguments_are_rejected_without_cuda(L):
     assert lib.kla_b200_launch_count() == 0
 
 
+def test_new_entry_points_reject_bad_arguments_without_cuda(L):
+    lib = L.load()
+    for name in ("mobius_scan_fwd", "mobius_scan_bwd", "affine_scan_fwd", "affine_scan_bwd"):
+        fn = getattr(lib, "kla_b200_" + name)
+        assert fn(None, None) == 1
+        assert fn(ctypes.byref(L.RawScanArgs(B=1, L=4, N=8)), None) == 1       # NULL tensors
+        assert fn(ctypes.byref(L.RawScanArgs(B=-1, L=4, N=8)), None) == 1
+        assert fn(ctypes.byref(L.RawScanArgs(B=1 << 20, L=4, N=8)), None) == 2  # batch above the grid limit
+    buf = (ctypes.c_float * 64)()
+    a = L.RawScanArgs(B=1, L=4, N=8, state0=ctypes.addressof(buf))
+    assert lib.kla_b200_affine_scan_fwd(ctypes.byref(a), None) == 1            # the affine scan takes no initial state
+    a = L.RawScanArgs(B=1, L=4, N=8)
+    for i in range(2):
+        a.inp[i] = ctypes.addressof(buf) + 2                                   # not aligned to a float
+    a.out[0] = ctypes.addressof(buf)
+    assert lib.kla_b200_affine_scan_fwd(ctypes.byref(a), None) == 4
+
+    assert lib.kla_b200_conv_step(None, None) == 1
+    assert lib.kla_b200_conv_step(ctypes.byref(L.ConvStepArgs(B=1, D=4, K=9)), None) == 2   # more taps than supported
+    assert lib.kla_b200_conv_step(ctypes.byref(L.ConvStepArgs(B=1, D=4, K=4, dtype=5)), None) == 2
+    assert lib.kla_b200_conv_step(ctypes.byref(L.ConvStepArgs(B=1, D=4, K=4, activation=9)), None) == 1
+    assert lib.kla_b200_conv_step(ctypes.byref(L.ConvStepArgs(B=1, D=4, K=4)), None) == 1   # NULL tensors
+    assert lib.kla_b200_conv_step(ctypes.byref(L.ConvStepArgs(B=0, D=4, K=4)), None) == 0
+
+    assert lib.kla_b200_step_layer(None, None) == 1
+    assert lib.kla_b200_step_layer(ctypes.byref(L.StepLayerArgs(B=1, M=4, S=200)), None) == 2
+    assert lib.kla_b200_step_layer(ctypes.byref(L.StepLayerArgs(B=1, M=4, S=4, gate_activation=7)), None) == 1
+    assert lib.kla_b200_step_layer(ctypes.byref(L.StepLayerArgs(B=1, M=4, S=4, lambda_skip_len=3)), None) == 1
+    assert lib.kla_b200_step_layer(ctypes.byref(L.StepLayerArgs(B=1, M=4, S=4)), None) == 1  # NULL tensors
+    assert lib.kla_b200_launch_count() == 0
+
+
 def test_error_text_and_exception_mapping(L):
     lib = L.load()
     assert lib.kla_b200_strerror(0) == b"ok"
