@@ -4,10 +4,11 @@ A training step whose activations arrive in pinned host buffers and whose result
 to host buffers is bound by the PCIe link, not by the kernels: at the headline shape the
 step moves 0.54 GB each way for 2.2 ms of GPU work. The scan is independent over the batch
 (``y[b]`` depends on ``v[b], lambda_v[b], k[b], q[b]`` only; ``da, dp`` are sums over ``b``),
-so ``scan_fwd_bwd_host`` cuts the batch into chunks and runs each chunk's
-copy-in -> forward -> backward -> copy-out on its own CUDA stream. The two copy engines then
-work at the same time (PCIe is full duplex) and the kernels of one chunk run under the
-copies of the next, instead of copy-in, compute and copy-out taking turns.
+so ``scan_fwd_bwd_host`` cuts the batch into chunks and pipelines them over one copy-in
+stream, a few kernel streams and one copy-out stream, tied together with events: a chunk's
+forward starts when its ``v, lambda_v, k, q`` have landed (the upstream gradients follow
+behind), its ``y, y_var`` leave while its backward runs, and the two copy engines work at
+the same time (PCIe is full duplex) instead of copy-in, compute and copy-out taking turns.
 
 Same kernels and same numerics as ``kla_scan_b200`` + autograd on the whole batch (float32
 activations; the entry point calls the forward and backward launches directly): the chunks
@@ -55,33 +56,58 @@ def scan_fwd_bwd_host(host: dict, device, out: dict | None = None, chunk: int = 
                               else host[src].dtype, pin_memory=True) for n, src in like.items()}
     _require_sm100(device)
     main = torch.cuda.current_stream(device)
-    streams = _side_streams(device, max(1, min(n_streams, (B + chunk - 1) // chunk)))
+    n_chunks = (B + chunk - 1) // chunk
+    pool = _side_streams(device, 2 + max(1, min(n_streams, n_chunks)))
+    s_in, s_out, s_cmp = pool[0], pool[1], pool[2:]  # one stream per copy engine, several for the kernels
+    for s in pool:
+        s.wait_stream(main)
     with torch.cuda.device(device):
-        a = host["a"].to(device, non_blocking=True)
-        p = host["p"].to(device, non_blocking=True)
-        ready = torch.cuda.Event()
-        ready.record(main)
+        with torch.cuda.stream(s_in):
+            a = host["a"].to(device, non_blocking=True)
+            p = host["p"].to(device, non_blocking=True)
         partial = []  # per chunk (da, dp), added in chunk order at the end
+        keep = [a, p]
         for ci, b0 in enumerate(range(0, B, chunk)):
-            s = streams[ci % len(streams)]
-            s.wait_event(ready)
+            sc = s_cmp[ci % len(s_cmp)]
             sl = slice(b0, min(B, b0 + chunk))
-            with torch.cuda.stream(s):
-                g = {n: host[n][sl].to(device, non_blocking=True) for n in (*_IN, "dy", "dyvar")}
-                ins = [g[n] for n in _IN]
+            # copy-in: what the forward needs first, the upstream gradients behind it
+            with torch.cuda.stream(s_in):
+                g = {n: host[n][sl].to(device, non_blocking=True) for n in _IN}
+                in_fwd = torch.cuda.Event()
+                in_fwd.record(s_in)
+                g.update({n: host[n][sl].to(device, non_blocking=True) for n in ("dy", "dyvar")})
+                in_bwd = torch.cuda.Event()
+                in_bwd.record(s_in)
+            ins = [g[n] for n in _IN]
+            with torch.cuda.stream(sc):
+                sc.wait_event(in_fwd)
                 y, y_var, _, _, ckpt = _launch_fwd(*ins, a, p, None, None, decode_from_prior, torch.float32, True)
+                fwd_done = torch.cuda.Event()
+                fwd_done.record(sc)
+                sc.wait_event(in_bwd)
                 dv, dlv, dk, dq, da, dp, _, _ = _launch_bwd(*ins, a, p, None, None, ckpt, g["dy"], g["dyvar"], None, None,
                                                             decode_from_prior, torch.float32)
-                for name, t in (("y", y), ("y_var", y_var), ("dv", dv), ("dlambda_v", dlv), ("dk", dk), ("dq", dq)):
+                bwd_done = torch.cuda.Event()
+                bwd_done.record(sc)
+            # copy-out: y, y_var can leave while the backward runs
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(fwd_done)
+                out["y"][sl].copy_(y, non_blocking=True)
+                out["y_var"][sl].copy_(y_var, non_blocking=True)
+                s_out.wait_event(bwd_done)
+                for name, t in (("dv", dv), ("dlambda_v", dlv), ("dk", dk), ("dq", dq)):
                     out[name][sl].copy_(t, non_blocking=True)
-                partial.append((da, dp))
-        for s in streams:
+            partial.append((da, dp))
+            # every buffer of the chunk is touched by up to three streams; tell the allocator
+            for t in (*g.values(), y, y_var, ckpt, dv, dlv, dk, dq, da, dp):
+                for s in (s_in, sc, s_out):
+                    t.record_stream(s)
+        for s in pool:
             main.wait_stream(s)
         da = torch.stack([x[0] for x in partial]).sum(0) if len(partial) > 1 else partial[0][0]
         dp = torch.stack([x[1] for x in partial]).sum(0) if len(partial) > 1 else partial[0][1]
         out["da"].copy_(da, non_blocking=True)
         out["dp"].copy_(dp, non_blocking=True)
-        for t in (a, p):
-            for s in streams:
-                t.record_stream(s)
+        for t in (*keep, *(x for pr in partial for x in pr)):
+            t.record_stream(main)
     return out
