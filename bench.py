@@ -715,6 +715,61 @@ def run_decode_layer(args):
     }), flush=True)
 
 
+def run_prologue(args):
+    """Secondary line: the scan with the layer's sensor prologue fused in (log-variance in, its
+    gradient out; kla_layer.py:224-231) beside the same step with the prologue as the eager torch
+    ops the reference layer issues (softplus, add, reciprocal and their autograd backward), both
+    through the public autograd API at the headline shape."""
+    import torch
+    import torch.nn.functional as F
+    import kla_b200
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, T, M, S = (args.batch or WORK["B"]), WORK["L"], WORK["M"], WORK["S"]
+    host = make_inputs(seed=0, **{**WORK, "B": B})
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(B, T, M, generator=g).to(dev)
+    d = {n: t.to(dev) for n, t in host.items()}
+    leaves = [d["v"], x, d["k"], d["q"], d["a"], d["p"]]
+
+    def fused():
+        ins = [t.detach().requires_grad_(True) for t in leaves]
+        y, yv, _ = kla_b200.kla_scan_b200(*ins, log_variance=(1e-4, None))
+        return torch.autograd.grad([y, yv], ins, [d["dy"], d["dyvar"]])
+
+    def eager():
+        ins = [t.detach().requires_grad_(True) for t in leaves]
+        lam_v = 1.0 / (F.softplus(ins[1]) + 1e-4)
+        y, yv, _ = kla_b200.kla_scan_b200(ins[0], lam_v, *ins[2:])
+        return torch.autograd.grad([y, yv], ins, [d["dy"], d["dyvar"]])
+
+    def timeit(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+
+    gf, ge = fused(), eager()
+    diff = float((gf[1] - ge[1]).abs().max() / (ge[1].abs().max() + 1e-12))
+    ms_f, ms_e = timeit(fused), timeit(eager)
+    print(json.dumps({
+        "metric": "KLA scan fwd+bwd with fused sensor prologue, tokens/s", "value": B * T / (ms_f * 1e-3), "unit": UNIT,
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_f, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"raw KLA scan fwd+bwd through autograd, B={B} T={T} M={M} S={S}, log-variance input "
+                               "(precision formed inside the kernels)",
+                   "ms_fused": ms_f, "ms_eager_prologue": ms_e, "speedup_vs_eager_prologue": ms_e / ms_f,
+                   "max_rel_diff_of_dx": diff},
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -728,7 +783,7 @@ def main():
     ap.add_argument("--batch", type=int, default=0,
                     help="raw workload only: batch size per GPU instead of 8, for the occupancy sweep "
                          "(B=4 leaves one CTA per SM, B=16 fills every SM); the headline stays B=8")
-    ap.add_argument("--workload", default="raw", choices=["raw", "seqshard", "decode", "rawpair", "decode_layer"],
+    ap.add_argument("--workload", default="raw", choices=["raw", "seqshard", "decode", "rawpair", "decode_layer", "prologue"],
                     help="raw = the headline raw-op workload (default); seqshard = the long-sequence, "
                          "time-sharded workload (secondary line)")
     args = ap.parse_args()
@@ -742,6 +797,8 @@ def main():
         return run_rawpair(args)
     if args.workload == "decode_layer" and args.impl != "reference":
         return run_decode_layer(args)
+    if args.workload == "prologue" and args.impl != "reference":
+        return run_prologue(args)
     if args.impl == "reference":
         run_reference(args)
     else:

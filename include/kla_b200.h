@@ -75,6 +75,13 @@ typedef struct kla_b200_fwd_args {
     kla_b200_tensor3 y, y_var;    /* out [B, L, M] */
     float *lam_fin, *eta_fin;     /* out [B, M, S] contiguous float32 */
     void *ckpt;                   /* out scratch of kla_b200_ckpt_bytes(), or NULL when no backward will follow */
+    /* Fused sensor prologue (src/kla/layers/kla_layer.py:224-231). When
+     * lambda_v_is_log_variance != 0 the lambda_v tensor holds the sensor
+     * projection's raw log-variance output x and the kernels form
+     * Lambda_v = 1 / min(softplus(x) + obs_var_min, obs_var_max) themselves
+     * (no ceiling when obs_var_max <= 0), in float32 whatever in_dtype is. */
+    int32_t lambda_v_is_log_variance;
+    float obs_var_min, obs_var_max;
 } kla_b200_fwd_args;
 
 /* Bytes of the checkpoint scratch the forward writes for the backward:
@@ -139,6 +146,9 @@ typedef struct kla_b200_bwd_args {
     float *dk, *dq;                     /* out [B, L, S] contiguous float32 */
     float *da, *dp;                     /* out [M, S] contiguous float32 */
     float *dlam0, *deta0;               /* out [B, M, S] contiguous float32 */
+    /* as in kla_b200_fwd_args; dlambda_v then receives the gradient with respect to the log-variances */
+    int32_t lambda_v_is_log_variance;
+    float obs_var_min, obs_var_max;
 } kla_b200_bwd_args;
 
 int kla_b200_scan_bwd(const kla_b200_bwd_args *args, void *stream);

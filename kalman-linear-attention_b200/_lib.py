@@ -83,6 +83,7 @@ class FwdArgs(Structure):
         ("a", c_void_p), ("p", c_void_p), ("lam0", c_void_p), ("eta0", c_void_p),
         ("y", Tensor3), ("y_var", Tensor3),
         ("lam_fin", c_void_p), ("eta_fin", c_void_p), ("ckpt", c_void_p),
+        ("lambda_v_is_log_variance", c_int32), ("obs_var_min", c_float), ("obs_var_max", c_float),
     ]
 
 
@@ -98,6 +99,7 @@ class BwdArgs(Structure):
         ("dv", Tensor3), ("dlambda_v", Tensor3),
         ("dk", c_void_p), ("dq", c_void_p), ("da", c_void_p), ("dp", c_void_p),
         ("dlam0", c_void_p), ("deta0", c_void_p),
+        ("lambda_v_is_log_variance", c_int32), ("obs_var_min", c_float), ("obs_var_max", c_float),
     ]
 
 

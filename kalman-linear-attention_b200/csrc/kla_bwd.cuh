@@ -43,6 +43,9 @@ struct alignas(64) BwdParams {
     const float *dlam_fin, *deta_fin;
     float *dk, *dq, *da, *dp, *dlam0, *deta0;
     int vec_dv, vec_dlv;
+    // lv holds log-variances (see FwdParams); dlv then receives the gradient with respect to them
+    int lv_log_sigma;
+    float obs_var_min, obs_var_max;
 };
 
 template <typename T, typename TO, int SPT, int LPC, int CH, int NW, int NH, int TT>
@@ -52,7 +55,8 @@ struct BwdSmem {
     static constexpr size_t kTileI = ((sizeof(T) * TT * Sh::kMC + 127) / 128) * 128;   // v or lambda_v
     static constexpr size_t kTileO = ((sizeof(TO) * TT * Sh::kMC + 127) / 128) * 128;  // dy or dyvar
     static constexpr size_t kKq = ((sizeof(float4) * TT * Sh::kSPad + 127) / 128) * 128;
-    static constexpr size_t kIn = 2 * kTileI + 2 * kTileO + kKq;
+    static constexpr size_t kLamF = sizeof(T) == 4 ? 0 : ((sizeof(float) * TT * Sh::kMC + 127) / 128) * 128;  // as in FwdSmem
+    static constexpr size_t kIn = 2 * kTileI + 2 * kTileO + kKq + kLamF;
     static constexpr int kRowPad = 4;  // slots; 8 words = the span of LPC lanes' float2 reads
     static constexpr size_t kTraj = ((sizeof(float2) * TT * CH * SPT * (Sh::kCompute + kRowPad) + 127) / 128) * 128;
     static constexpr size_t kDpart = ((sizeof(float2) * TT * LPC * Sh::kMCP + 127) / 128) * 128;
@@ -78,6 +82,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
     uint64_t *part_full = empty_in + NS;                     // [NQ]   compute -> helpers: segment's partials written
     uint64_t *part_empty = part_full + NQ;                   // [NQ]   helpers -> compute: segment's rows reusable
     uint64_t *stage_done = part_empty + NQ;                  // [NS]   summing helpers -> loading helper: tile's inputs no longer read
+    uint64_t *ready_in = stage_done + NS;                    // [NS]   loader -> compute: precision tile formed (log-variance input only)
     unsigned char *in_base = smem + Sm::kBars;
     float2 *traj = reinterpret_cast<float2 *>(in_base + NS * Sm::kIn);                   // [TT*CH*SPT][NTC]
     float2 *dpart = reinterpret_cast<float2 *>(in_base + NS * Sm::kIn + Sm::kTraj);      // [TT][LPC][MCP]
@@ -86,6 +91,11 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
     auto dystage = [&](int s) { return reinterpret_cast<TO *>(in_base + s * Sm::kIn + 2 * Sm::kTileI); };
     auto dyvstage = [&](int s) { return reinterpret_cast<TO *>(in_base + s * Sm::kIn + 2 * Sm::kTileI + Sm::kTileO); };
     auto kqstage = [&](int s) { return reinterpret_cast<float4 *>(in_base + s * Sm::kIn + 2 * Sm::kTileI + 2 * Sm::kTileO); };
+    auto lfstage = [&](int s) {
+        return reinterpret_cast<float *>(in_base + s * Sm::kIn +
+                                         (sizeof(T) == 4 ? Sm::kTileI : 2 * Sm::kTileI + 2 * Sm::kTileO + Sm::kKq));
+    };
+    const bool pro = prm.lv_log_sigma != 0;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.y;
@@ -97,6 +107,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
         for (int s = 0; s < NS; ++s) {
             mbar_init(&full_in[s], kProducers);
             mbar_init(&stage_done[s], NH - 1);
+            mbar_init(&ready_in[s], 1);
             mbar_init(&empty_in[s], NW);
         }
         for (int qd = 0; qd < NQ; ++qd) {
@@ -161,9 +172,14 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
             const int t0 = tile * TT;
             const int n = min(TT, L - t0);
             const bool flip = ti & 1;
-            if (!mbar_wait(&full_in[s], (ti / NS) & 1, 11)) break;
+            if (!mbar_wait(pro ? &ready_in[s] : &full_in[s], (ti / NS) & 1, 11)) break;
 
             const T *lrow = lstage(s) + cw;
+            const float *lfrow = lfstage(s) + cw;
+            auto load_lv = [&](int tt, int ci) -> float {
+                if constexpr (sizeof(T) == 4) return lfrow[tt * MC + ci];  // the same tile as lrow
+                else return pro ? lfrow[tt * MC + ci] : to_f32<T>(lrow[tt * MC + ci]);
+            };
             const T *vrow = vstage(s) + cw;
             const TO *dyrow = dystage(s) + cw;
             const TO *dyvrow = dyvstage(s) + cw;
@@ -184,7 +200,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                 float lv[CH], vv[CH], Pp[CH][SPT], g[CH][SPT], r[CH][SPT];
 #pragma unroll
                 for (int ci = 0; ci < CH; ++ci) {
-                    lv[ci] = to_f32<T>(lrow[tt * MC + ci]);
+                    lv[ci] = load_lv(tt, ci);
                     vv[ci] = to_f32<T>(vrow[tt * MC + ci]);
                 }
 #pragma unroll
@@ -254,7 +270,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                 float lv[CH], lv2[CH], vv[CH], vl[CH], dy[CH], dyv[CH], dyv2[CH], dvl[CH], dlphi[CH];
 #pragma unroll
                 for (int ci = 0; ci < CH; ++ci) {
-                    lv[ci] = to_f32<T>(lrow[tt * MC + ci]);
+                    lv[ci] = load_lv(tt, ci);
                     vv[ci] = to_f32<T>(vrow[tt * MC + ci]);
                     dy[ci] = to_f32<TO>(dyrow[tt * MC + ci]);
                     dyv[ci] = to_f32<TO>(dyvrow[tt * MC + ci]);
@@ -407,8 +423,26 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                 }
             };
             if (NT > 0) load_kq((NT - 1) * TT);
+            // log-variance input: once a tile has landed, turn its lambda_v tile into precisions
+            // (float32, in place for float32 activations) and tell the compute warps
+            int formed = 0;
+            auto form_upto = [&](int limit) {
+                for (; formed < limit && ok; ++formed) {
+                    const int fs = formed % NS;
+                    if (!mbar_wait(&full_in[fs], (formed / NS) & 1, 17, 100)) { ok = false; break; }
+                    const T *raw = lstage(fs);
+                    float *lf = lfstage(fs);
+                    for (int idx = htid; idx < TT * MC; idx += kProducers)
+                        lf[idx] = precision_from_log_variance(to_f32<T>(raw[idx]), prm.obs_var_min, prm.obs_var_max);
+                    fence_proxy_async();  // these plain stores are ordered before the bulk copy that refills the stage
+                    __syncwarp();
+                    if (hlane == 0) mbar_arrive(&ready_in[fs]);
+                }
+            };
             for (int it = 0; it < NT; ++it) {
                 const int tile = NT - 1 - it, s = it % NS, t0 = tile * TT;
+                if (it >= NS && pro) form_upto(it);
+                if (!ok) break;
                 if (it >= NS) {  // the stage is free once the compute warps and the summing helpers are done with it
                     if (!mbar_wait(&empty_in[s], (it / NS - 1) & 1, 13, 100)) { ok = false; break; }
                     if (!mbar_wait(&stage_done[s], (it / NS - 1) & 1, 16, 100)) { ok = false; break; }
@@ -438,6 +472,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                 if (!(prm.use_tma && htid == 0)) mbar_arrive(&full_in[s]);
                 produced = it + 1;
             }
+            if (pro && ok) form_upto(NT);
         } else {
             // ---- summing helpers: finish the sums of each processed tile, a segment at a time
             const int ctid = htid - kProducers;
@@ -448,6 +483,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                 const int n = min(TT, L - t0);
                 const bool flip = jt & 1;
                 const T *lt = lstage(s), *vt = vstage(s);
+                const float *lft = lfstage(s);
                 for (int step = 0; step < NQ && ok; ++step) {
                     // the compute warps finish the segments of a tile from its last steps to its first
                     const int qd = NQ - 1 - step;                 // segment in time order
@@ -489,10 +525,21 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                             const float4 x = *reinterpret_cast<const float4 *>(dpart + (pr * LPC + jj) * MCP + c);
                             ax += x.x; ay += x.y; bx += x.z; by += x.w;
                         }
-                        const float l0 = to_f32<T>(lt[tt * MC + c]), l1 = to_f32<T>(lt[tt * MC + c + 1]);
+                        float l0, l1;
+                        if (pro || sizeof(T) == 4) {
+                            l0 = lft[tt * MC + c];
+                            l1 = lft[tt * MC + c + 1];
+                        } else {
+                            l0 = to_f32<T>(lt[tt * MC + c]);
+                            l1 = to_f32<T>(lt[tt * MC + c + 1]);
+                        }
                         const float v0 = to_f32<T>(vt[tt * MC + c]), v1 = to_f32<T>(vt[tt * MC + c + 1]);
                         const float dv0 = ax * l0, dv1 = bx * l1;
-                        const float dl0 = fmaf(ax, v0, ay), dl1 = fmaf(bx, v1, by);
+                        float dl0 = fmaf(ax, v0, ay), dl1 = fmaf(bx, v1, by);
+                        if (pro) {  // chain through Lambda_v = 1 / min(softplus(x) + floor, ceiling)
+                            dl0 *= precision_slope(l0, prm.obs_var_min, prm.obs_var_max);
+                            dl1 *= precision_slope(l1, prm.obs_var_min, prm.obs_var_max);
+                        }
                         T *p0 = dvb + (long long)(t0 + tt) * prm.dv.st + m_cta + c;
                         T *p1 = dlvb + (long long)(t0 + tt) * prm.dlv.st + m_cta + c;
                         const bool full = m_cta + c + 1 < M;

@@ -307,6 +307,8 @@ int kla_b200_scan_fwd(const kla_b200_fwd_args *a, void *stream) {
     prm.a = a->a; prm.p = a->p; prm.lam0 = a->lam0; prm.eta0 = a->eta0;
     prm.lam_fin = a->lam_fin; prm.eta_fin = a->eta_fin;
     prm.ckpt = static_cast<float2 *>(a->ckpt);
+    prm.lv_log_sigma = a->lambda_v_is_log_variance != 0;
+    prm.obs_var_min = a->obs_var_min; prm.obs_var_max = a->obs_var_max;
     prm.vec_y = a->out_dtype == KLA_B200_F32 ? vec2_ok<float>(a->y) : vec2_ok<__nv_bfloat16>(a->y);
     prm.vec_yv = a->out_dtype == KLA_B200_F32 ? vec2_ok<float>(a->y_var) : vec2_ok<__nv_bfloat16>(a->y_var);
     return dispatch_fwd(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc_for(a->S), prm, *a, st);
@@ -358,6 +360,8 @@ int kla_b200_scan_bwd(const kla_b200_bwd_args *a, void *stream) {
     prm.dy = t3(a->dy); prm.dyv = t3(a->dy_var); prm.dv = t3(a->dv); prm.dlv = t3(a->dlambda_v);
     prm.a = a->a; prm.p = a->p; prm.lam0 = a->lam0; prm.eta0 = a->eta0;
     prm.ckpt = static_cast<const float2 *>(a->ckpt);
+    prm.lv_log_sigma = a->lambda_v_is_log_variance != 0;
+    prm.obs_var_min = a->obs_var_min; prm.obs_var_max = a->obs_var_max;
     prm.dlam_fin = a->dlam_fin; prm.deta_fin = a->deta_fin;
     prm.dk = a->dk; prm.dq = a->dq; prm.da = a->da; prm.dp = a->dp;
     prm.dlam0 = a->dlam0; prm.deta0 = a->deta0;

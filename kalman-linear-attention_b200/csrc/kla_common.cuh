@@ -135,6 +135,23 @@ __device__ __forceinline__ void chain_update2(float2 &P, float2 &mean, float2 Pp
     mean = mul2(g, fma2(Pp, r, mul2(a, mean)));
 }
 
+// torch.nn.functional.softplus with its default threshold of 20
+__device__ __forceinline__ float softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+// Value precision from the sensor projection's raw output, as the reference layer forms it
+// (src/kla/layers/kla_layer.py:224-231): 1 / min(softplus(x) + obs_var_min, obs_var_max); no ceiling when obs_var_max <= 0.
+__device__ __forceinline__ float precision_from_log_variance(float x, float vmin, float vmax) {
+    float sig = softplus(x) + vmin;
+    if (vmax > 0.0f) sig = fminf(sig, vmax);
+    return 1.0f / sig;
+}
+// d(precision)/dx expressed through the precision itself: -lam^2 sigmoid(x) with
+// softplus(x) = 1/lam - vmin, sigmoid(x) = 1 - exp(-softplus(x)); zero where the ceiling binds.
+__device__ __forceinline__ float precision_slope(float lam, float vmin, float vmax) {
+    const float sig = 1.0f / lam;
+    if (vmax > 0.0f && sig >= vmax) return 0.0f;
+    return -(lam * lam) * (1.0f - expf(-fmaxf(sig - vmin, 0.0f)));
+}
+
 template <typename T>
 __device__ __forceinline__ float to_f32(T x);
 template <>

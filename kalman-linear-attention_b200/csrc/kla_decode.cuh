@@ -31,8 +31,6 @@ __device__ __forceinline__ float activate(float x, int act) {
         default: return x;
     }
 }
-// torch.nn.functional.softplus with its default threshold of 20
-__device__ __forceinline__ float softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 
 struct ConvStepParams {
     int B, D, K;           // K taps, window of K-1 past inputs
@@ -129,9 +127,8 @@ __global__ void __launch_bounds__(128) kla_step_layer_kernel(const StepLayerPara
     float ys = 0.0f, yvs = 0.0f;
     if (row_live) {
         // observation-noise variance -> value precision, kla_layer.py:224-231
-        float sig = softplus(to_f32<T>(static_cast<const T *>(prm.ls)[(long long)b * prm.ls_sb + m])) + prm.obs_var_min;
-        if (prm.obs_var_max > 0.0f) sig = fminf(sig, prm.obs_var_max);
-        const float lv = 1.0f / sig;
+        const float lv = precision_from_log_variance(
+            to_f32<T>(static_cast<const T *>(prm.ls)[(long long)b * prm.ls_sb + m]), prm.obs_var_min, prm.obs_var_max);
         const float vl = to_f32<T>(static_cast<const T *>(prm.v)[(long long)b * prm.v_sb + m]) * lv;
         const long long ms0 = (long long)m * S + j * 4, bms0 = ((long long)b * M + m) * S + j * 4;
         const bool vec = (S % 4) == 0;

@@ -40,6 +40,10 @@ struct alignas(64) FwdParams {
     float *lam_fin, *eta_fin;
     float2 *ckpt;  // [B, NT, M, S] (P, mean) at the start of each tile, or nullptr
     int vec_y, vec_yv;
+    // lv holds the sensor projection's raw log-variance output instead of the precision:
+    // Lambda_v = 1 / min(softplus(lv) + obs_var_min, obs_var_max) is formed in shared memory by the loader warps
+    int lv_log_sigma;
+    float obs_var_min, obs_var_max;
 };
 
 // Shared-memory carve-up, shared by the kernel and the launcher.
@@ -49,7 +53,10 @@ struct FwdSmem {
     static constexpr size_t kBars = 128;
     static constexpr size_t kTile = ((sizeof(T) * TT * Sh::kMC + 127) / 128) * 128;   // one of v / lambda_v
     static constexpr size_t kKq = ((sizeof(float2) * TT * Sh::kSPad + 127) / 128) * 128;
-    static constexpr size_t kIn = 2 * kTile + kKq;
+    // float32 precision tile written by the loaders when lambda_v arrives as a log-variance;
+    // for float32 activations it is the lambda_v tile itself (transformed in place)
+    static constexpr size_t kLamF = sizeof(T) == 4 ? 0 : ((sizeof(float) * TT * Sh::kMC + 127) / 128) * 128;
+    static constexpr size_t kIn = 2 * kTile + kKq + kLamF;
     static constexpr size_t kOut = ((sizeof(float2) * TT * LPC * Sh::kMCP + 127) / 128) * 128;
     static constexpr size_t kTotal = kBars + kInStages * kIn + kOutStages * kOut;
 };
@@ -74,12 +81,17 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
     uint64_t *empty_in = full_in + NS;                       // [NS]
     uint64_t *full_out = empty_in + NS;                      // [NO]
     uint64_t *empty_out = full_out + NO;                     // [NO]
+    uint64_t *ready_in = empty_out + NO;                     // [NS]  loaders -> compute: precision tile formed (log-variance input only)
     unsigned char *in_base = smem + Sm::kBars;
     unsigned char *out_base = in_base + NS * Sm::kIn;
     auto vstage = [&](int s) { return reinterpret_cast<T *>(in_base + s * Sm::kIn); };
     auto lstage = [&](int s) { return reinterpret_cast<T *>(in_base + s * Sm::kIn + Sm::kTile); };
     // (k, q) of a step, grouped by owning lane: [TT][LPC][2][SPT] floats, state s = i * LPC + j at [j][.][i]
     auto kqstage = [&](int s) { return reinterpret_cast<float *>(in_base + s * Sm::kIn + 2 * Sm::kTile); };
+    auto lfstage = [&](int s) {
+        return reinterpret_cast<float *>(in_base + s * Sm::kIn + (sizeof(T) == 4 ? Sm::kTile : 2 * Sm::kTile + Sm::kKq));
+    };
+    const bool pro = prm.lv_log_sigma != 0;
     auto ystage = [&](int o) { return reinterpret_cast<float2 *>(out_base + o * Sm::kOut); };
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -90,6 +102,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(&full_in[s], kProducers);
+            mbar_init(&ready_in[s], kProducers / 32);
             mbar_init(&empty_in[s], NW);
         }
         for (int o = 0; o < NO; ++o) {
@@ -153,10 +166,11 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         struct StepPre {
             float2 r[CH][HP], c0[CH][HP], c1[CH][HP], q[HP];
         };
-        auto fetch = [&](StepIn &in, const T *lrow, const T *vrow, const float *kqrow, int tt) {
+        auto fetch = [&](StepIn &in, const T *lrow, const float *lfrow, const T *vrow, const float *kqrow, int tt) {
 #pragma unroll
             for (int ci = 0; ci < CH; ++ci) {
-                in.lv[ci] = to_f32<T>(lrow[tt * MC + ci]);
+                if constexpr (sizeof(T) == 4) in.lv[ci] = lfrow[tt * MC + ci];  // the same tile as lrow
+                else in.lv[ci] = pro ? lfrow[tt * MC + ci] : to_f32<T>(lrow[tt * MC + ci]);
                 in.vv[ci] = to_f32<T>(vrow[tt * MC + ci]);
             }
             const float *row = kqrow + tt * 2 * SPAD;
@@ -237,7 +251,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         for (int tile = 0; tile < NT; ++tile) {
             const int s = tile % NS, o = tile % NO;
             const int t0 = tile * TT;
-            if (!mbar_wait(&full_in[s], (tile / NS) & 1, 1)) break;
+            if (!mbar_wait(pro ? &ready_in[s] : &full_in[s], (tile / NS) & 1, 1)) break;
             if (tile >= NO && !mbar_wait(&empty_out[o], (tile / NO - 1) & 1, 2)) break;
             if (ck != nullptr) {
 #pragma unroll
@@ -249,12 +263,13 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                 ck += ck_tile;
             }
             const T *lrow = lstage(s) + cw;
+            const float *lfrow = lfstage(s) + cw;
             const T *vrow = vstage(s) + cw;
             const float *kqrow = kqstage(s) + j * 2 * SPT;
             float2 *yrow = ystage(o) + j * MCP + cw;
             StepIn in;
             StepPre pr, prn;
-            fetch(in, lrow, vrow, kqrow, 0);
+            fetch(in, lrow, lfrow, vrow, kqrow, 0);
             prep(pr, in);
             if (t0 + TT <= L) {
                 // four steps per trip keeps the loop body inside the instruction cache
@@ -263,7 +278,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         const int tt = t4 + u;
-                        fetch(in, lrow, vrow, kqrow, (tt + 1) % TT);  // the wrap-around fetch is not used
+                        fetch(in, lrow, lfrow, vrow, kqrow, (tt + 1) % TT);  // the wrap-around fetch is not used
                         update(pr);
                         readout(pr, yrow, tt);
                         prep(prn, in);
@@ -272,7 +287,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                 }
             } else {
                 for (int tt = 0; t0 + tt < L; ++tt) {
-                    fetch(in, lrow, vrow, kqrow, (tt + 1) % TT);
+                    fetch(in, lrow, lfrow, vrow, kqrow, (tt + 1) % TT);
                     update(pr);
                     readout(pr, yrow, tt);
                     prep(prn, in);
@@ -327,9 +342,28 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                 }
             };
             load_kq(0);
+            // log-variance input: once a tile has landed, turn its lambda_v tile into precisions
+            // (float32, in place for float32 activations) and tell the compute warps
+            int formed = 0;
+            auto form_upto = [&](int limit) {
+                for (; formed < limit && ok; ++formed) {
+                    const int fs = formed % NS;
+                    if (!mbar_wait(&full_in[fs], (formed / NS) & 1, 6, 100)) { ok = false; break; }
+                    const T *raw = lstage(fs);
+                    float *lf = lfstage(fs);
+                    for (int idx = htid; idx < TT * MC; idx += kProducers)
+                        lf[idx] = precision_from_log_variance(to_f32<T>(raw[idx]), prm.obs_var_min, prm.obs_var_max);
+                    fence_proxy_async();  // these plain stores are ordered before the bulk copy that refills the stage
+                    __syncwarp();
+                    if (hlane == 0) mbar_arrive(&ready_in[fs]);
+                }
+            };
             for (int it = 0; it < NT; ++it) {
                 const int s = it % NS, t0 = it * TT;
-                if (it >= NS && !mbar_wait(&empty_in[s], (it / NS - 1) & 1, 3, 100)) { ok = false; break; }
+                if (it >= NS) {
+                    if (pro) form_upto(it);
+                    if (!ok || !mbar_wait(&empty_in[s], (it / NS - 1) & 1, 3, 100)) { ok = false; break; }
+                }
                 if (prm.use_tma) {
                     if (htid == 0) {
                         mbar_arrive_expect_tx(&full_in[s], 2 * kTileBytes);
@@ -354,6 +388,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                 if (!(prm.use_tma && htid == 0)) mbar_arrive(&full_in[s]);
                 produced = it + 1;
             }
+            if (pro && ok) form_upto(NT);
         } else {
             // ---- drainers: per finished tile, sum the LPC partial read-outs and store y, y_var
             const int dtid = htid - kProducers;

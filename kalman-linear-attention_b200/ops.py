@@ -101,7 +101,14 @@ def _dt(t: torch.dtype) -> int:
     return BF16 if t == torch.bfloat16 else F32
 
 
-def _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype, need_ckpt: bool):
+def _sensor_fields(sensors):
+    """C-ABI fields of the fused sensor prologue: ``sensors`` is None or (obs_var_min, obs_var_max or None)."""
+    if sensors is None:
+        return dict(lambda_v_is_log_variance=0, obs_var_min=0.0, obs_var_max=0.0)
+    return dict(lambda_v_is_log_variance=1, obs_var_min=float(sensors[0]), obs_var_max=float(sensors[1] or 0.0))
+
+
+def _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype, need_ckpt: bool, sensors=None):
     """Allocate outputs (and the checkpoint scratch when a backward will follow)
     and enqueue ``kla_b200_scan_fwd`` on the current stream of the inputs' device."""
     lib = _lib.load()
@@ -121,7 +128,7 @@ def _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype, nee
         v=_t3(v), lambda_v=_t3(lambda_v), k=_t3(k), q=_t3(q),
         a=_ptr(a), p=_ptr(p), lam0=_ptr(lam0), eta0=_ptr(eta0),
         y=_t3(y), y_var=_t3(y_var), lam_fin=_ptr(lam_fin), eta_fin=_ptr(eta_fin),
-        ckpt=_ptr(ckpt),
+        ckpt=_ptr(ckpt), **_sensor_fields(sensors),
     )
     with torch.cuda.device(dev):
         _lib.check(lib.kla_b200_scan_fwd(ctypes.byref(args), _stream(dev)))
@@ -129,7 +136,7 @@ def _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype, nee
 
 
 def _launch_bwd(v, lambda_v, k, q, a, p, lam0, eta0, ckpt, dy, dy_var, dlam_fin, deta_fin,
-                prior: bool, out_dtype):
+                prior: bool, out_dtype, sensors=None):
     """Allocate the gradients and enqueue ``kla_b200_scan_bwd``."""
     lib = _lib.load()
     B, L, M = v.shape
@@ -150,7 +157,7 @@ def _launch_bwd(v, lambda_v, k, q, a, p, lam0, eta0, ckpt, dy, dy_var, dlam_fin,
         a=_ptr(a), p=_ptr(p), lam0=_ptr(lam0), eta0=_ptr(eta0), ckpt=_ptr(ckpt),
         dy=_t3(dy), dy_var=_t3(dy_var), dlam_fin=_ptr(dlam_fin), deta_fin=_ptr(deta_fin),
         dv=_t3(dv), dlambda_v=_t3(dlv), dk=_ptr(dk), dq=_ptr(dq), da=_ptr(da), dp=_ptr(dp),
-        dlam0=_ptr(dlam0), deta0=_ptr(deta0),
+        dlam0=_ptr(dlam0), deta0=_ptr(deta0), **_sensor_fields(sensors),
     )
     with torch.cuda.device(dev):
         _lib.check(lib.kla_b200_scan_bwd(ctypes.byref(args), _stream(dev)))
@@ -165,12 +172,13 @@ class _KLAScanB200(torch.autograd.Function):
     float32 contiguous [B, M, S] or None."""
 
     @staticmethod
-    def forward(ctx, v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype: torch.dtype):
+    def forward(ctx, v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype: torch.dtype, sensors=None):
         need_grad = any(ctx.needs_input_grad[:8])
         y, y_var, lam_fin, eta_fin, ckpt = _launch_fwd(
-            v, lambda_v, k, q, a, p, lam0, eta0, prior, out_dtype, need_grad)
+            v, lambda_v, k, q, a, p, lam0, eta0, prior, out_dtype, need_grad, sensors)
         ctx.save_for_backward(v, lambda_v, k, q, a, p, lam0, eta0, ckpt)
         ctx.prior = prior
+        ctx.sensors = sensors
         ctx.out_dtype = out_dtype
         return y, y_var, lam_fin, eta_fin
 
@@ -201,12 +209,12 @@ class _KLAScanB200(torch.autograd.Function):
             dlam_fin = dlam_fin.float().contiguous()
             deta_fin = deta_fin.float().contiguous()
         dv, dlv, dk, dq, da, dp, dlam0, deta0 = _launch_bwd(
-            v, lambda_v, k, q, a, p, lam0, eta0, ckpt, dy, dy_var, dlam_fin, deta_fin, ctx.prior, od)
+            v, lambda_v, k, q, a, p, lam0, eta0, ckpt, dy, dy_var, dlam_fin, deta_fin, ctx.prior, od, ctx.sensors)
         if k.dtype != torch.float32:
             dk, dq = dk.to(k.dtype), dq.to(k.dtype)
         has_state = lam0 is not None
         return (dv, dlv, dk, dq, da, dp,
-                dlam0 if has_state else None, deta0 if has_state else None, None, None)
+                dlam0 if has_state else None, deta0 if has_state else None, None, None, None)
 
 
 def kla_scan_b200(
@@ -220,6 +228,7 @@ def kla_scan_b200(
     decode_from_prior: bool = False,
     *,
     out_dtype: Optional[torch.dtype] = None,
+    log_variance: Optional[tuple] = None,
 ):
     """B200 KLA scan. Same call and return contract as the reference's
     ``kla_scan_torch`` (src/kla/ops/kla_ops.py:188-290): returns
@@ -231,6 +240,12 @@ def kla_scan_b200(
     widens them with a copy (kla_ops.py:126-137). ``out_dtype=torch.bfloat16``
     (bfloat16 inputs only) also writes y, y_var as bfloat16 -- what the layer
     would cast them to anyway (kla_layer.py:329-330).
+
+    ``log_variance=(obs_var_min, obs_var_max or None)`` fuses the layer's sensor
+    prologue (kla_layer.py:224-231): the ``lambda_v`` argument then holds the
+    sensor projection's raw log-variance output ``x``, the kernels form
+    ``1 / min(softplus(x) + obs_var_min, obs_var_max)`` in float32 on the way in,
+    and the gradient returned for that argument is the one with respect to ``x``.
     """
     _require_device(v)
     if a.dim() != 2:
@@ -270,8 +285,12 @@ def kla_scan_b200(
         lam0 = lam0.float().contiguous()
         eta0 = eta0.float().contiguous()
 
+    if log_variance is not None:
+        if len(log_variance) != 2 or not log_variance[0] >= 0.0:
+            raise ValueError("log_variance must be (obs_var_min >= 0, obs_var_max or None)")
+        log_variance = (float(log_variance[0]), None if log_variance[1] is None else float(log_variance[1]))
     y, y_var, lam_fin, eta_fin = _KLAScanB200.apply(
-        v, lambda_v, k, q, a, p, lam0, eta0, bool(decode_from_prior), out_dtype)
+        v, lambda_v, k, q, a, p, lam0, eta0, bool(decode_from_prior), out_dtype, log_variance)
     return y, y_var, _state_cls()(lam=lam_fin, eta=eta_fin)
 
 

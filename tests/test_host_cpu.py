@@ -43,19 +43,28 @@ def oracle_launches(monkeypatch):
     through, so that everything above the C-ABI call runs here."""
     monkeypatch.setattr(ops, "_require_device", lambda t: None)
 
-    def fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior, out_dtype, need_ckpt):
+    def precision(x, sensors):  # the sensor prologue, src/kla/layers/kla_layer.py:224-231, and its slope
+        sig = np.logaddexp(0.0, x) + sensors[0]
+        free = np.ones_like(sig) if sensors[1] is None else (sig < sensors[1]).astype(np.float64)
+        if sensors[1] is not None:
+            sig = np.minimum(sig, sensors[1])
+        return 1.0 / sig, -free / (sig * sig) / (1.0 + np.exp(-x))
+
+    def fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior, out_dtype, need_ckpt, sensors=None):
         n = lambda t: None if t is None else t.detach().double().numpy()
-        f = O.scan_fwd(n(v), n(lambda_v), n(k), n(q), n(a), n(p), n(lam0), n(eta0), prior=prior)
+        lv = n(lambda_v) if sensors is None else precision(n(lambda_v), sensors)[0]
+        f = O.scan_fwd(n(v), lv, n(k), n(q), n(a), n(p), n(lam0), n(eta0), prior=prior)
         return (torch.tensor(f.y, dtype=out_dtype), torch.tensor(f.y_var, dtype=out_dtype),
                 torch.tensor(f.lam, dtype=torch.float32), torch.tensor(f.eta, dtype=torch.float32),
                 torch.zeros(1, dtype=torch.uint8) if need_ckpt else None)
 
-    def bwd(v, lambda_v, k, q, a, p, lam0, eta0, ckpt, dy, dy_var, dlam_fin, deta_fin, prior, out_dtype):
+    def bwd(v, lambda_v, k, q, a, p, lam0, eta0, ckpt, dy, dy_var, dlam_fin, deta_fin, prior, out_dtype, sensors=None):
         n = lambda t: None if t is None else t.detach().double().numpy()
-        g = O.scan_bwd(n(v), n(lambda_v), n(k), n(q), n(a), n(p), n(dy), n(dy_var), n(lam0), n(eta0),
+        lv, slope = (n(lambda_v), 1.0) if sensors is None else precision(n(lambda_v), sensors)
+        g = O.scan_bwd(n(v), lv, n(k), n(q), n(a), n(p), n(dy), n(dy_var), n(lam0), n(eta0),
                        n(dlam_fin), n(deta_fin), prior=prior)
         f32 = lambda x, dt=torch.float32: torch.tensor(x, dtype=dt)
-        return (f32(g.dv, v.dtype), f32(g.dlambda_v, v.dtype), f32(g.dk), f32(g.dq), f32(g.da), f32(g.dp),
+        return (f32(g.dv, v.dtype), f32(g.dlambda_v * slope, v.dtype), f32(g.dk), f32(g.dq), f32(g.da), f32(g.dp),
                 f32(g.dlam0), f32(g.deta0))
 
     monkeypatch.setattr(ops, "_launch_fwd", fwd)
@@ -77,6 +86,29 @@ def test_wrapper_contract(oracle_launches):
     grads = torch.autograd.grad(loss, ins + [lam0, eta0])
     for n, gr in zip(["dv", "dlambda_v", "dk", "dq", "da", "dp", "dlam0", "deta0"], grads):
         np.testing.assert_allclose(gr.numpy(), g[n], rtol=2e-4, atol=2e-5, err_msg=n)
+
+
+def test_wrapper_passes_the_sensor_prologue_through(oracle_launches):
+    """log_variance=(floor, ceiling): the second argument is the raw log-variance, and its gradient is with
+    respect to that; both must equal the explicit torch prologue in front of the plain call."""
+    g = load_golden("backends")
+    ins = _t(g)
+    x = torch.randn(ins[1].shape, generator=torch.Generator().manual_seed(5)).requires_grad_(True)
+    for sensors in ((1e-4, None), (0.05, 1.2)):
+        leaves = [t.clone().requires_grad_(True) for t in (ins[0], x, *ins[2:])]
+        y, y_var, _ = kla_b200.kla_scan_b200(*leaves, log_variance=sensors)
+        got = torch.autograd.grad((y.square().sum() + y_var.sum()), leaves)
+        ref_leaves = [t.clone().requires_grad_(True) for t in (ins[0], x, *ins[2:])]
+        sig = torch.nn.functional.softplus(ref_leaves[1]) + sensors[0]
+        if sensors[1] is not None:
+            sig = sig.clamp_max(sensors[1])
+        y2, y_var2, _ = kla_b200.kla_scan_b200(ref_leaves[0], 1.0 / sig, *ref_leaves[2:])
+        ref = torch.autograd.grad((y2.square().sum() + y_var2.sum()), ref_leaves)
+        torch.testing.assert_close(y, y2, rtol=1e-5, atol=1e-6)
+        for a_, b_ in zip(got, ref):
+            torch.testing.assert_close(a_, b_, rtol=1e-4, atol=1e-5)
+    with pytest.raises(ValueError, match="log_variance"):
+        kla_b200.kla_scan_b200(*ins, log_variance=(-1.0, None))
 
 
 def test_wrapper_widens_and_validates(oracle_launches):

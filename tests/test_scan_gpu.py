@@ -298,3 +298,70 @@ def test_full_size_slice_against_oracle(kb):
         print(f"\n  full-size slice b={b_} m={m0}: " + " ".join(f"{n} {x:.2f}" for n, x in r.items()))
         assert max(r.values()) <= 1.0, r
     assert all(torch.isfinite(t).all() for t in grads)
+
+
+# ------------------------------------------------------------ fused sensor prologue
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("sensors", [(1e-4, None), (0.05, 1.2)])
+@pytest.mark.parametrize("L", [1, 16, 37, 100])
+def test_log_variance_prologue_matches_explicit_prologue(kb, sensors, L):
+    """log_variance=(floor, ceiling): the kernels form Lambda_v = 1/min(softplus(x)+floor, ceiling)
+    themselves (src/kla/layers/kla_layer.py:224-231). Outputs must equal the plain call on the
+    torch-formed precision, and the gradient for x must be the chain rule through it, checked
+    against the float64 oracle with the prologue applied in numpy."""
+    kla_b200 = kb
+    dev = torch.device("cuda:0")
+    B, M, S = 2, 40, 16
+    g = torch.Generator().manual_seed(L)
+    F = torch.nn.functional
+    v = torch.randn(B, L, M, generator=g)
+    x = 1.5 * torch.randn(B, L, M, generator=g)
+    k = F.normalize(torch.randn(B, L, S, generator=g), dim=-1)
+    q = F.normalize(torch.randn(B, L, S, generator=g), dim=-1)
+    a = torch.sigmoid(torch.randn(M, S, generator=g))
+    p = F.softplus(torch.randn(M, S, generator=g))
+    dy, dyv = torch.randn(B, L, M, generator=g), torch.randn(B, L, M, generator=g)
+    ins = [t.to(dev).requires_grad_(True) for t in (v, x, k, q, a, p)]
+    y, y_var, st = kla_b200.kla_scan_b200(*ins, log_variance=sensors)
+    grads = torch.autograd.grad([y, y_var], ins, [dy.to(dev), dyv.to(dev)])
+
+    xd = x.double().numpy()
+    sig = np.logaddexp(0.0, xd) + sensors[0]
+    free = np.ones_like(sig) if sensors[1] is None else (sig < sensors[1]).astype(np.float64)
+    if sensors[1] is not None:
+        sig = np.minimum(sig, sensors[1])
+    lv = 1.0 / sig
+    n = lambda t: t.double().numpy()
+    f = O.scan_fwd(n(v), lv, n(k), n(q), n(a), n(p))
+    b = O.scan_bwd(n(v), lv, n(k), n(q), n(a), n(p), n(dy), n(dyv))
+    dx = b.dlambda_v * (-free / (sig * sig) / (1.0 + np.exp(-xd)))
+
+    assert ratio(y, f.y) <= 1.0 and ratio(y_var, f.y_var) <= 1.0 and ratio(st.lam, f.lam) <= 1.0
+    assert ratio(grads[0], b.dv) <= 1.0
+    assert ratio(grads[1], dx) <= 1.5, ratio(grads[1], dx)  # one more float32 factor (the slope) than dlambda_v
+    for got, ref in ((grads[2], b.dk), (grads[3], b.dq), (grads[4], b.da), (grads[5], b.dp)):
+        assert ratio(got, ref) <= 30.0
+    L_ = __import__("importlib").import_module("kalman-linear-attention_b200._lib")
+    assert L_.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_log_variance_prologue_bf16_keeps_float32_precision_inside(kb):
+    kla_b200 = kb
+    dev = torch.device("cuda:0")
+    B, L, M, S = 2, 50, 64, 16
+    g = torch.Generator().manual_seed(11)
+    F = torch.nn.functional
+    v = torch.randn(B, L, M, generator=g).to(dev, torch.bfloat16)
+    x = torch.randn(B, L, M, generator=g).to(dev, torch.bfloat16)
+    k = F.normalize(torch.randn(B, L, S, generator=g), dim=-1).to(dev, torch.bfloat16)
+    q = F.normalize(torch.randn(B, L, S, generator=g), dim=-1).to(dev, torch.bfloat16)
+    a = torch.sigmoid(torch.randn(M, S, generator=g)).to(dev)
+    p = F.softplus(torch.randn(M, S, generator=g)).to(dev)
+    y, y_var, _ = kla_b200.kla_scan_b200(v, x, k, q, a, p, log_variance=(1e-4, None))
+    # the reference layer forms the precision in float32 from the bfloat16 projection and hands it over in float32
+    lam_v = 1.0 / (F.softplus(x.float()) + 1e-4)
+    y2, y_var2, _ = kla_b200.kla_scan_b200(v.float(), lam_v, k.float(), q.float(), a, p)
+    torch.testing.assert_close(y, y2, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(y_var, y_var2, rtol=1e-5, atol=1e-5)
