@@ -82,7 +82,6 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
     uint64_t *part_full = empty_in + NS;                     // [NQ]   compute -> helpers: segment's partials written
     uint64_t *part_empty = part_full + NQ;                   // [NQ]   helpers -> compute: segment's rows reusable
     uint64_t *stage_done = part_empty + NQ;                  // [NS]   summing helpers -> loading helper: tile's inputs no longer read
-    uint64_t *ready_in = stage_done + NS;                    // [NS]   loader -> compute: precision tile formed (log-variance input only)
     unsigned char *in_base = smem + Sm::kBars;
     float2 *traj = reinterpret_cast<float2 *>(in_base + NS * Sm::kIn);                   // [TT*CH*SPT][NTC]
     float2 *dpart = reinterpret_cast<float2 *>(in_base + NS * Sm::kIn + Sm::kTraj);      // [TT][LPC][MCP]
@@ -107,7 +106,6 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
         for (int s = 0; s < NS; ++s) {
             mbar_init(&full_in[s], kProducers);
             mbar_init(&stage_done[s], NH - 1);
-            mbar_init(&ready_in[s], 1);
             mbar_init(&empty_in[s], NW);
         }
         for (int qd = 0; qd < NQ; ++qd) {
@@ -172,7 +170,17 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
             const int t0 = tile * TT;
             const int n = min(TT, L - t0);
             const bool flip = ti & 1;
-            if (!mbar_wait(pro ? &ready_in[s] : &full_in[s], (ti / NS) & 1, 11)) break;
+            if (!mbar_wait(&full_in[s], (ti / NS) & 1, 11)) break;
+            if (pro) {  // this warp's channels of the tile: log-variance -> precision, float32
+                const T *raw = lstage(s) + warp * Sh::kCPW;
+                float *lf = lfstage(s) + warp * Sh::kCPW;
+                for (int e = lane; e < TT * Sh::kCPW; e += 32) {
+                    const int at = (e / Sh::kCPW) * MC + e % Sh::kCPW;
+                    lf[at] = precision_from_log_variance_fast(to_f32<T>(raw[at]), prm.obs_var_min, prm.obs_var_max);
+                }
+                fence_proxy_async();  // these plain stores are ordered before the bulk copy that refills the stage
+                __syncwarp();
+            }
 
             const T *lrow = lstage(s) + cw;
             const float *lfrow = lfstage(s) + cw;
@@ -423,26 +431,8 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                 }
             };
             if (NT > 0) load_kq((NT - 1) * TT);
-            // log-variance input: once a tile has landed, turn its lambda_v tile into precisions
-            // (float32, in place for float32 activations) and tell the compute warps
-            int formed = 0;
-            auto form_upto = [&](int limit) {
-                for (; formed < limit && ok; ++formed) {
-                    const int fs = formed % NS;
-                    if (!mbar_wait(&full_in[fs], (formed / NS) & 1, 17, 100)) { ok = false; break; }
-                    const T *raw = lstage(fs);
-                    float *lf = lfstage(fs);
-                    for (int idx = htid; idx < TT * MC; idx += kProducers)
-                        lf[idx] = precision_from_log_variance(to_f32<T>(raw[idx]), prm.obs_var_min, prm.obs_var_max);
-                    fence_proxy_async();  // these plain stores are ordered before the bulk copy that refills the stage
-                    __syncwarp();
-                    if (hlane == 0) mbar_arrive(&ready_in[fs]);
-                }
-            };
             for (int it = 0; it < NT; ++it) {
                 const int tile = NT - 1 - it, s = it % NS, t0 = tile * TT;
-                if (it >= NS && pro) form_upto(it);
-                if (!ok) break;
                 if (it >= NS) {  // the stage is free once the compute warps and the summing helpers are done with it
                     if (!mbar_wait(&empty_in[s], (it / NS - 1) & 1, 13, 100)) { ok = false; break; }
                     if (!mbar_wait(&stage_done[s], (it / NS - 1) & 1, 16, 100)) { ok = false; break; }
@@ -472,7 +462,6 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                 if (!(prm.use_tma && htid == 0)) mbar_arrive(&full_in[s]);
                 produced = it + 1;
             }
-            if (pro && ok) form_upto(NT);
         } else {
             // ---- summing helpers: finish the sums of each processed tile, a segment at a time
             const int ctid = htid - kProducers;

@@ -41,7 +41,8 @@ struct alignas(64) FwdParams {
     float2 *ckpt;  // [B, NT, M, S] (P, mean) at the start of each tile, or nullptr
     int vec_y, vec_yv;
     // lv holds the sensor projection's raw log-variance output instead of the precision:
-    // Lambda_v = 1 / min(softplus(lv) + obs_var_min, obs_var_max) is formed in shared memory by the loader warps
+    // Lambda_v = 1 / min(softplus(lv) + obs_var_min, obs_var_max) is formed in shared memory by the compute warps,
+    // each for the channels it owns, when a tile arrives
     int lv_log_sigma;
     float obs_var_min, obs_var_max;
 };
@@ -53,7 +54,7 @@ struct FwdSmem {
     static constexpr size_t kBars = 128;
     static constexpr size_t kTile = ((sizeof(T) * TT * Sh::kMC + 127) / 128) * 128;   // one of v / lambda_v
     static constexpr size_t kKq = ((sizeof(float2) * TT * Sh::kSPad + 127) / 128) * 128;
-    // float32 precision tile written by the loaders when lambda_v arrives as a log-variance;
+    // float32 precision tile written by the compute warps when lambda_v arrives as a log-variance;
     // for float32 activations it is the lambda_v tile itself (transformed in place)
     static constexpr size_t kLamF = sizeof(T) == 4 ? 0 : ((sizeof(float) * TT * Sh::kMC + 127) / 128) * 128;
     static constexpr size_t kIn = 2 * kTile + kKq + kLamF;
@@ -81,7 +82,6 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
     uint64_t *empty_in = full_in + NS;                       // [NS]
     uint64_t *full_out = empty_in + NS;                      // [NO]
     uint64_t *empty_out = full_out + NO;                     // [NO]
-    uint64_t *ready_in = empty_out + NO;                     // [NS]  loaders -> compute: precision tile formed (log-variance input only)
     unsigned char *in_base = smem + Sm::kBars;
     unsigned char *out_base = in_base + NS * Sm::kIn;
     auto vstage = [&](int s) { return reinterpret_cast<T *>(in_base + s * Sm::kIn); };
@@ -102,7 +102,6 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(&full_in[s], kProducers);
-            mbar_init(&ready_in[s], kProducers / 32);
             mbar_init(&empty_in[s], NW);
         }
         for (int o = 0; o < NO; ++o) {
@@ -251,7 +250,17 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         for (int tile = 0; tile < NT; ++tile) {
             const int s = tile % NS, o = tile % NO;
             const int t0 = tile * TT;
-            if (!mbar_wait(pro ? &ready_in[s] : &full_in[s], (tile / NS) & 1, 1)) break;
+            if (!mbar_wait(&full_in[s], (tile / NS) & 1, 1)) break;
+            if (pro) {  // this warp's channels of the tile: log-variance -> precision, float32
+                const T *raw = lstage(s) + warp * Sh::kCPW;
+                float *lf = lfstage(s) + warp * Sh::kCPW;
+                for (int e = lane; e < TT * Sh::kCPW; e += 32) {
+                    const int at = (e / Sh::kCPW) * MC + e % Sh::kCPW;
+                    lf[at] = precision_from_log_variance_fast(to_f32<T>(raw[at]), prm.obs_var_min, prm.obs_var_max);
+                }
+                fence_proxy_async();  // these plain stores are ordered before the bulk copy that refills the stage
+                __syncwarp();
+            }
             if (tile >= NO && !mbar_wait(&empty_out[o], (tile / NO - 1) & 1, 2)) break;
             if (ck != nullptr) {
 #pragma unroll
@@ -342,28 +351,9 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                 }
             };
             load_kq(0);
-            // log-variance input: once a tile has landed, turn its lambda_v tile into precisions
-            // (float32, in place for float32 activations) and tell the compute warps
-            int formed = 0;
-            auto form_upto = [&](int limit) {
-                for (; formed < limit && ok; ++formed) {
-                    const int fs = formed % NS;
-                    if (!mbar_wait(&full_in[fs], (formed / NS) & 1, 6, 100)) { ok = false; break; }
-                    const T *raw = lstage(fs);
-                    float *lf = lfstage(fs);
-                    for (int idx = htid; idx < TT * MC; idx += kProducers)
-                        lf[idx] = precision_from_log_variance(to_f32<T>(raw[idx]), prm.obs_var_min, prm.obs_var_max);
-                    fence_proxy_async();  // these plain stores are ordered before the bulk copy that refills the stage
-                    __syncwarp();
-                    if (hlane == 0) mbar_arrive(&ready_in[fs]);
-                }
-            };
             for (int it = 0; it < NT; ++it) {
                 const int s = it % NS, t0 = it * TT;
-                if (it >= NS) {
-                    if (pro) form_upto(it);
-                    if (!ok || !mbar_wait(&empty_in[s], (it / NS - 1) & 1, 3, 100)) { ok = false; break; }
-                }
+                if (it >= NS && !mbar_wait(&empty_in[s], (it / NS - 1) & 1, 3, 100)) { ok = false; break; }
                 if (prm.use_tma) {
                     if (htid == 0) {
                         mbar_arrive_expect_tx(&full_in[s], 2 * kTileBytes);
@@ -388,7 +378,6 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                 if (!(prm.use_tma && htid == 0)) mbar_arrive(&full_in[s]);
                 produced = it + 1;
             }
-            if (pro && ok) form_upto(NT);
         } else {
             // ---- drainers: per finished tile, sum the LPC partial read-outs and store y, y_var
             const int dtid = htid - kProducers;
