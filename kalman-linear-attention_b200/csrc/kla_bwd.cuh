@@ -63,7 +63,9 @@ struct BwdSmem {
     static constexpr size_t kTotal = kBars + kBwdStages * kIn + kTraj + kDpart;
 };
 
-template <typename T, typename TO, int SPT, int LPC, int CH, int NW, int NH, int TT, bool PRIOR>
+// LOGV: lambda_v arrives as a log-variance (BwdParams::lv_log_sigma). A separate instantiation, so that the plain
+// kernel does not carry that code: even untaken it cost the plain path 1.6 %.
+template <typename T, typename TO, int SPT, int LPC, int CH, int NW, int NH, int TT, bool PRIOR, bool LOGV>
 __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_constant__ BwdParams prm) {
     using Sh = ScanShape<SPT, LPC, CH, NW, NH, TT>;
     using Sm = BwdSmem<T, TO, SPT, LPC, CH, NW, NH, TT>;
@@ -94,7 +96,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
         return reinterpret_cast<float *>(in_base + s * Sm::kIn +
                                          (sizeof(T) == 4 ? Sm::kTileI : 2 * Sm::kTileI + 2 * Sm::kTileO + Sm::kKq));
     };
-    const bool pro = prm.lv_log_sigma != 0;
+    constexpr bool pro = LOGV;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.y;

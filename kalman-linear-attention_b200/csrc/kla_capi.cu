@@ -140,7 +140,8 @@ template <typename T, typename TO, int LPC, bool PRIOR>
 int launch_bwd(BwdParams &prm, const kla_b200_bwd_args &a, cudaStream_t st) {
     using Sh = ScanShape<kSPT, LPC, kCH, kNW, kNH, kTT>;
     using Sm = BwdSmem<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT>;
-    auto kern = kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR>;
+    auto kern = prm.lv_log_sigma ? kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, true>
+                                 : kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, false>;
     prm.use_tma = !g_no_tma && make_tile_map<T>(&prm.tm_v, a.v, a.B, a.L, a.M, Sh::kMC, kTT) &&
                   make_tile_map<T>(&prm.tm_lv, a.lambda_v, a.B, a.L, a.M, Sh::kMC, kTT) &&
                   make_tile_map<TO>(&prm.tm_dy, a.dy, a.B, a.L, a.M, Sh::kMC, kTT) &&
