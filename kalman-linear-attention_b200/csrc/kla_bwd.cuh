@@ -32,6 +32,14 @@ namespace kla {
 
 constexpr int kBwdStages = 2;  // input stages in flight
 constexpr int kSeg = 8;         // steps per hand-over of partial sums (a "segment" of a tile)
+#ifndef KLA_REV_UNROLL
+#define KLA_REV_UNROLL 2
+#endif
+constexpr int kRevUnroll = KLA_REV_UNROLL;  // steps of the reverse walk unrolled per loop trip
+#ifndef KLA_REP_UNROLL
+#define KLA_REP_UNROLL 4
+#endif
+constexpr int kRepUnroll = KLA_REP_UNROLL;  // steps of the replay unrolled per loop trip
 
 struct alignas(64) BwdParams {
     CUtensorMap tm_v, tm_lv, tm_dy, tm_dyv;
@@ -242,8 +250,11 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                 const int prq = flip ? NQ - 1 - qd : qd;  // physical segment written by steps kSeg*qd .. kSeg*qd + kSeg - 1
                 if (ti > 0 && !mbar_wait(&part_empty[prq], (ti - 1) & 1, 12)) { ok = false; break; }
                 if (n == TT) {
+#pragma unroll 1
+                    for (int h = 0; h < kSeg; h += kRepUnroll) {
 #pragma unroll
-                    for (int u = 0; u < kSeg; ++u) replay_step(qd * kSeg + u, prq, u);
+                        for (int u = 0; u < kRepUnroll; ++u) replay_step(qd * kSeg + h + u, prq, h + u);
+                    }
                 } else {
 #pragma unroll 1
                     for (int u = 0; u < kSeg; ++u)
@@ -360,8 +371,12 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
             for (int qd = NQ - 1; qd >= 0; --qd) {
                 const int prq = flip ? NQ - 1 - qd : qd;
                 if (n == TT) {
+                    // unrolled by kRevUnroll steps, not the whole segment: the walk's code then stays within the instruction cache
+#pragma unroll 1
+                    for (int h = kSeg - kRevUnroll; h >= 0; h -= kRevUnroll) {
 #pragma unroll
-                    for (int u = kSeg - 1; u >= 0; --u) reverse_step(qd * kSeg + u, prq, u);
+                        for (int u = kRevUnroll - 1; u >= 0; --u) reverse_step(qd * kSeg + h + u, prq, h + u);
+                    }
                 } else {
 #pragma unroll 1
                     for (int u = kSeg - 1; u >= 0; --u)

@@ -30,6 +30,10 @@ namespace kla {
 
 constexpr int kInStages = 3;   // input stages in flight
 constexpr int kOutStages = 2;  // read-out partial buffers
+#ifndef KLA_FWD_UNROLL
+#define KLA_FWD_UNROLL 16
+#endif
+constexpr int kFwdUnroll = KLA_FWD_UNROLL;  // steps unrolled per trip of the time loop
 
 struct alignas(64) FwdParams {
     CUtensorMap tm_v, tm_lv;  // rank-3 (M, L, B) maps with box (MC, TT, 1); valid when use_tma
@@ -281,11 +285,11 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             fetch(in, lrow, lfrow, vrow, kqrow, 0);
             prep(pr, in);
             if (t0 + TT <= L) {
-                // four steps per trip keeps the loop body inside the instruction cache
+                // kFwdUnroll steps per trip: with the paired arithmetic a whole tile fits the instruction cache
 #pragma unroll 1
-                for (int t4 = 0; t4 < TT; t4 += 4) {
+                for (int t4 = 0; t4 < TT; t4 += kFwdUnroll) {
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
+                    for (int u = 0; u < kFwdUnroll; ++u) {
                         const int tt = t4 + u;
                         fetch(in, lrow, lfrow, vrow, kqrow, (tt + 1) % TT);  // the wrap-around fetch is not used
                         update(pr);
