@@ -51,7 +51,7 @@ def algorithmic_bytes_per_token(M, S, esz=4):
 # from profiles/kla_scan_fwd_bwd_B8_T4096_M1024_S16_f32.md; the raw-scan figure is per batch
 # entry (captured at B=1, T=4096, M*S=16384; traffic is proportional to B), from
 # profiles/kla_rawscan_T4096_N16384_f32.md.
-NCU_TRAFFIC = {"kla_bwd_kernel": 1074.4e6, "kla_fwd_kernel": 763.2e6, "rawscan_mobius_bwd_per_batch": 2651.5e6}
+NCU_TRAFFIC = {"kla_bwd_kernel": 1075.5e6, "kla_fwd_kernel": 760.4e6, "rawscan_mobius_bwd_per_batch": 2651.5e6}
 
 
 def make_inputs(seed=0, **w):
