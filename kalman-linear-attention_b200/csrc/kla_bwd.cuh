@@ -24,6 +24,11 @@
 //     parked in the slot its (P', mean') occupied; the helpers add the CTA's
 //     channels and issue one atomic add per (t, s) per CTA.
 // Sums over b and t (da, dp) stay in registers until the end.
+//
+// Helper warps by task: the first one loads (TMA tiles of v, lambda_v, dy, dy_var
+// issued by one elected thread, and the (k^2, k, q, q^2) values of a tile, with
+// those of the next tile already in registers); the others finish the sums and
+// store dv, dlambda_v. Two input stages; all hand-overs through mbarriers.
 #pragma once
 
 #include "kla_fwd.cuh"
