@@ -16,7 +16,7 @@ from importlib import import_module  # noqa: E402
 
 decode = import_module("kalman-linear-attention_b200.decode")
 CASES = sorted(os.path.basename(p)[7:-4] for p in glob.glob(os.path.join(HERE, "golden", "decode_*.npz")))
-REF_SRC = "/root/reference/src"
+REF_SRC = os.environ.get("KLA_REFERENCE_SRC", "/root/reference/src")  # the reference package, when it is on this machine
 needs_ref = pytest.mark.skipif(not os.path.isdir(REF_SRC), reason="reference package not present")
 
 

@@ -16,7 +16,7 @@ from oracle import kla_oracle as O
 import kla_b200
 
 ops = importlib.import_module("kalman-linear-attention_b200.ops")
-REF_SRC = "/root/reference/src"
+REF_SRC = os.environ.get("KLA_REFERENCE_SRC", "/root/reference/src")  # the reference package, when it is on this machine
 INPUTS = ("v", "lambda_v", "k", "q", "a", "p")
 
 
