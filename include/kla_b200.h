@@ -49,6 +49,12 @@ extern "C" {
 #define KLA_B200_F32 0
 #define KLA_B200_BF16 1
 
+/* Activation functions of the layer's gate and of its causal convolution. */
+#define KLA_B200_ACT_SILU 0
+#define KLA_B200_ACT_GELU 1
+#define KLA_B200_ACT_RELU 2
+#define KLA_B200_ACT_NONE 3
+
 /* A [B, L, X] activation tensor: base pointer plus batch and time strides. */
 typedef struct kla_b200_tensor3 {
     void *ptr;
@@ -82,6 +88,16 @@ typedef struct kla_b200_fwd_args {
      * (no ceiling when obs_var_max <= 0), in float32 whatever in_dtype is. */
     int32_t lambda_v_is_log_variance;
     float obs_var_min, obs_var_max;
+    /* Fused layer epilogue, forward only (src/kla/layers/kla_layer.py:329-338):
+     * y += lambda_skip * z (when lambda_skip_len is 1 or M; z: [B, L, M] in
+     * in_dtype), then y *= g, y_var *= g^2 with g = act(gate) (when gate.ptr is
+     * not NULL; KLA_B200_ACT_*). For inference (prefill): refused with
+     * KLA_B200_EUNSUPPORTED together with ckpt != NULL, because the backward
+     * kernel has no counterpart for it. */
+    kla_b200_tensor3 z, gate;
+    const float *lambda_skip;
+    int32_t lambda_skip_len;
+    int32_t gate_activation;
 } kla_b200_fwd_args;
 
 /* Bytes of the checkpoint scratch the forward writes for the backward:
@@ -217,10 +233,6 @@ int kla_b200_step(const kla_b200_step_args *args, void *stream);
  * z = act(bias + sum_j w[d, j] window[j]), window = (state, x), then the state
  * keeps the last K-1 inputs. x, state and z share one element type (dtype).
  */
-#define KLA_B200_ACT_SILU 0
-#define KLA_B200_ACT_GELU 1
-#define KLA_B200_ACT_RELU 2
-#define KLA_B200_ACT_NONE 3
 #define KLA_B200_MAX_CONV_TAPS 8
 
 typedef struct kla_b200_conv_step_args {

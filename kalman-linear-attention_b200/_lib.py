@@ -84,6 +84,8 @@ class FwdArgs(Structure):
         ("y", Tensor3), ("y_var", Tensor3),
         ("lam_fin", c_void_p), ("eta_fin", c_void_p), ("ckpt", c_void_p),
         ("lambda_v_is_log_variance", c_int32), ("obs_var_min", c_float), ("obs_var_max", c_float),
+        ("z", Tensor3), ("gate", Tensor3), ("lambda_skip", c_void_p),
+        ("lambda_skip_len", c_int32), ("gate_activation", c_int32),
     ]
 
 

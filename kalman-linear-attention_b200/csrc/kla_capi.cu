@@ -310,6 +310,20 @@ int kla_b200_scan_fwd(const kla_b200_fwd_args *a, void *stream) {
     prm.ckpt = static_cast<float2 *>(a->ckpt);
     prm.lv_log_sigma = a->lambda_v_is_log_variance != 0;
     prm.obs_var_min = a->obs_var_min; prm.obs_var_max = a->obs_var_max;
+    {
+        const bool has_skip = a->lambda_skip_len != 0, has_gate = a->gate.ptr != nullptr;
+        if (has_skip || has_gate) {
+            if (a->ckpt != nullptr) return KLA_B200_EUNSUPPORTED;  // forward only
+            if (has_skip && ((a->lambda_skip_len != 1 && a->lambda_skip_len != a->M) || !a->lambda_skip || !a->z.ptr))
+                return KLA_B200_EINVAL;
+            if (a->gate_activation < KLA_B200_ACT_SILU || a->gate_activation > KLA_B200_ACT_NONE) return KLA_B200_EINVAL;
+            if (has_skip && (rc = check_t3(a->z, esz, true))) return rc;
+            if (has_gate && (rc = check_t3(a->gate, esz, true))) return rc;
+            prm.epilogue = 1;
+            if (has_skip) { prm.z = t3(a->z); prm.skip = a->lambda_skip; prm.skip_len = a->lambda_skip_len; }
+            if (has_gate) { prm.gate = t3(a->gate); prm.gate_act = a->gate_activation; }
+        }
+    }
     prm.vec_y = a->out_dtype == KLA_B200_F32 ? vec2_ok<float>(a->y) : vec2_ok<__nv_bfloat16>(a->y);
     prm.vec_yv = a->out_dtype == KLA_B200_F32 ? vec2_ok<float>(a->y_var) : vec2_ok<__nv_bfloat16>(a->y_var);
     return dispatch_fwd(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc_for(a->S), prm, *a, st);

@@ -135,6 +135,17 @@ __device__ __forceinline__ void chain_update2(float2 &P, float2 &mean, float2 Pp
     mean = mul2(g, fma2(Pp, r, mul2(a, mean)));
 }
 
+enum Activation { kActSilu = 0, kActGelu = 1, kActRelu = 2, kActNone = 3 };
+
+__device__ __forceinline__ float activate(float x, int act) {
+    switch (act) {
+        case kActSilu: return x / (1.0f + expf(-x));
+        case kActGelu: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+        case kActRelu: return fmaxf(x, 0.0f);
+        default: return x;
+    }
+}
+
 // torch.nn.functional.softplus with its default threshold of 20
 __device__ __forceinline__ float softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 // Value precision from the sensor projection's raw output, as the reference layer forms it

@@ -21,17 +21,6 @@
 
 namespace kla {
 
-enum Activation { kActSilu = 0, kActGelu = 1, kActRelu = 2, kActNone = 3 };
-
-__device__ __forceinline__ float activate(float x, int act) {
-    switch (act) {
-        case kActSilu: return x / (1.0f + expf(-x));
-        case kActGelu: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
-        case kActRelu: return fmaxf(x, 0.0f);
-        default: return x;
-    }
-}
-
 struct ConvStepParams {
     int B, D, K;           // K taps, window of K-1 past inputs
     const void *x;         // [B, D] with batch stride

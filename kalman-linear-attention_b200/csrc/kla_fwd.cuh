@@ -49,6 +49,12 @@ struct alignas(64) FwdParams {
     // each for the channels it owns, when a tile arrives
     int lv_log_sigma;
     float obs_var_min, obs_var_max;
+    // Forward-only epilogue of the layer (src/kla/layers/kla_layer.py:329-338), applied by the drainer warps at the
+    // store: y += skip * z, then y *= g and y_var *= g^2 with g = act(gate). z / gate: [B, L, M] in the activation
+    // type, ptr == nullptr when absent; skip: one value or one per channel.
+    Tensor3 z, gate;
+    const float *skip;
+    int skip_len, gate_act, epilogue;
 };
 
 // Shared-memory carve-up, shared by the kernel and the launcher.
@@ -390,10 +396,33 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             for (int jt = 0; jt < NT; ++jt) {
                 const int o = jt % NO, t0 = jt * TT;
                 if (!mbar_wait(&full_out[o], (jt / NO) & 1, 4, 100)) { ok = false; break; }
-                output_pass<TO, LPC, MC, MCP, TT, kDrainers>(
-                    ystage(o), yb + (long long)t0 * prm.y.st, prm.y.st, prm.vec_y,
-                    yvb + (long long)t0 * prm.yv.st, prm.yv.st, prm.vec_yv, min(TT, L - t0), m_cta, M, dtid,
-                    [](float2 acc, int, int, float &o0, float &o1) { o0 = acc.x; o1 = acc.y; });
+                if (prm.epilogue) {
+                    const T *zb = prm.z.ptr ? static_cast<const T *>(prm.z.ptr) + (long long)b * prm.z.sb : nullptr;
+                    const T *gb = prm.gate.ptr ? static_cast<const T *>(prm.gate.ptr) + (long long)b * prm.gate.sb : nullptr;
+                    output_pass<TO, LPC, MC, MCP, TT, kDrainers>(
+                        ystage(o), yb + (long long)t0 * prm.y.st, prm.y.st, prm.vec_y,
+                        yvb + (long long)t0 * prm.yv.st, prm.yv.st, prm.vec_yv, min(TT, L - t0), m_cta, M, dtid,
+                        [&](float2 acc, int tt, int c, float &o0, float &o1) {
+                            const int m = m_cta + c;
+                            if (m < M) {
+                                if (zb != nullptr)
+                                    acc.x = fmaf(prm.skip[prm.skip_len > 1 ? m : 0],
+                                                 to_f32<T>(zb[(long long)(t0 + tt) * prm.z.st + m]), acc.x);
+                                if (gb != nullptr) {
+                                    const float g = activate(to_f32<T>(gb[(long long)(t0 + tt) * prm.gate.st + m]), prm.gate_act);
+                                    acc.x *= g;
+                                    acc.y *= g * g;
+                                }
+                            }
+                            o0 = acc.x;
+                            o1 = acc.y;
+                        });
+                } else {
+                    output_pass<TO, LPC, MC, MCP, TT, kDrainers>(
+                        ystage(o), yb + (long long)t0 * prm.y.st, prm.y.st, prm.vec_y,
+                        yvb + (long long)t0 * prm.yv.st, prm.yv.st, prm.vec_yv, min(TT, L - t0), m_cta, M, dtid,
+                        [](float2 acc, int, int, float &o0, float &o1) { o0 = acc.x; o1 = acc.y; });
+                }
                 __syncwarp();
                 if (hlane == 0) mbar_arrive(&empty_out[o]);
             }

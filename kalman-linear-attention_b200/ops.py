@@ -108,7 +108,22 @@ def _sensor_fields(sensors):
     return dict(lambda_v_is_log_variance=1, obs_var_min=float(sensors[0]), obs_var_max=float(sensors[1] or 0.0))
 
 
-def _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype, need_ckpt: bool, sensors=None):
+def _epilogue_fields(epilogue):
+    """C-ABI fields of the forward-only layer epilogue: ``epilogue`` is None or a dict with any of
+    ``z`` + ``lambda_skip`` (float32, one value or [M]) and ``gate`` + ``gate_activation``."""
+    if not epilogue:
+        return {}
+    out = {}
+    skip = epilogue.get("lambda_skip")
+    if skip is not None:
+        out.update(z=_t3(epilogue["z"]), lambda_skip=_ptr(skip), lambda_skip_len=skip.numel())
+    if epilogue.get("gate") is not None:
+        out.update(gate=_t3(epilogue["gate"]), gate_activation=_lib.ACT[epilogue.get("gate_activation", "silu")])
+    return out
+
+
+def _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype, need_ckpt: bool, sensors=None,
+                epilogue=None):
     """Allocate outputs (and the checkpoint scratch when a backward will follow)
     and enqueue ``kla_b200_scan_fwd`` on the current stream of the inputs' device."""
     lib = _lib.load()
@@ -128,7 +143,7 @@ def _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype, nee
         v=_t3(v), lambda_v=_t3(lambda_v), k=_t3(k), q=_t3(q),
         a=_ptr(a), p=_ptr(p), lam0=_ptr(lam0), eta0=_ptr(eta0),
         y=_t3(y), y_var=_t3(y_var), lam_fin=_ptr(lam_fin), eta_fin=_ptr(eta_fin),
-        ckpt=_ptr(ckpt), **_sensor_fields(sensors),
+        ckpt=_ptr(ckpt), **_sensor_fields(sensors), **_epilogue_fields(epilogue),
     )
     with torch.cuda.device(dev):
         _lib.check(lib.kla_b200_scan_fwd(ctypes.byref(args), _stream(dev)))
@@ -229,6 +244,7 @@ def kla_scan_b200(
     *,
     out_dtype: Optional[torch.dtype] = None,
     log_variance: Optional[tuple] = None,
+    epilogue: Optional[dict] = None,
 ):
     """B200 KLA scan. Same call and return contract as the reference's
     ``kla_scan_torch`` (src/kla/ops/kla_ops.py:188-290): returns
@@ -246,6 +262,13 @@ def kla_scan_b200(
     sensor projection's raw log-variance output ``x``, the kernels form
     ``1 / min(softplus(x) + obs_var_min, obs_var_max)`` in float32 on the way in,
     and the gradient returned for that argument is the one with respect to ``x``.
+
+    ``epilogue=dict(z=, lambda_skip=, gate=, gate_activation="silu")`` fuses the
+    layer's output path for inference (kla_layer.py:329-338): ``y += lambda_skip * z``
+    (``lambda_skip``: one value or one per channel), then ``y *= g``, ``y_var *= g**2``
+    with ``g = act(gate)``; either half may be left out. Forward only: it raises
+    ``NotImplementedError`` when a gradient would be needed (run it under
+    ``torch.no_grad()``; the training path applies these two steps in torch).
     """
     _require_device(v)
     if a.dim() != 2:
@@ -289,6 +312,33 @@ def kla_scan_b200(
         if len(log_variance) != 2 or not log_variance[0] >= 0.0:
             raise ValueError("log_variance must be (obs_var_min >= 0, obs_var_max or None)")
         log_variance = (float(log_variance[0]), None if log_variance[1] is None else float(log_variance[1]))
+    if epilogue:
+        if torch.is_grad_enabled() and any(t is not None and t.requires_grad
+                                           for t in (v, lambda_v, k, q, a, p, lam0, eta0, *epilogue.values())
+                                           if torch.is_tensor(t)):
+            raise _unsupported("fuses the skip/gate epilogue in the forward only; call it under torch.no_grad()")
+        epi = dict(epilogue)
+        unknown = set(epi) - {"z", "lambda_skip", "gate", "gate_activation"}
+        if unknown:
+            raise ValueError(f"unknown epilogue keys {sorted(unknown)}")
+        if (epi.get("lambda_skip") is None) != (epi.get("z") is None):
+            raise ValueError("epilogue needs z and lambda_skip together")
+        for name in ("z", "gate"):
+            t = epi.get(name)
+            if t is not None:
+                if tuple(t.shape) != (B, L, M):
+                    raise ValueError(f"epilogue {name} must be [B, L, M]")
+                epi[name] = _rowmajor_last(t if t.dtype == act else t.to(act))
+        if epi.get("lambda_skip") is not None:
+            sk = epi["lambda_skip"].detach().float().reshape(-1).contiguous().to(v.device)
+            if sk.numel() not in (1, M):
+                raise ValueError("lambda_skip must hold one value or one per channel")
+            epi["lambda_skip"] = sk
+        if epi.get("gate_activation", "silu") not in ("silu", "gelu", "relu"):
+            raise ValueError("gate_activation must be 'silu', 'gelu' or 'relu'")
+        y, y_var, lam_fin, eta_fin, _ = _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, bool(decode_from_prior),
+                                                    out_dtype, False, log_variance, epi)
+        return y, y_var, _state_cls()(lam=lam_fin, eta=eta_fin)
     y, y_var, lam_fin, eta_fin = _KLAScanB200.apply(
         v, lambda_v, k, q, a, p, lam0, eta0, bool(decode_from_prior), out_dtype, log_variance)
     return y, y_var, _state_cls()(lam=lam_fin, eta=eta_fin)

@@ -365,3 +365,50 @@ def test_log_variance_prologue_bf16_keeps_float32_precision_inside(kb):
     y2, y_var2, _ = kla_b200.kla_scan_b200(v.float(), lam_v, k.float(), q.float(), a, p)
     torch.testing.assert_close(y, y2, rtol=1e-5, atol=1e-5)
     torch.testing.assert_close(y_var, y_var2, rtol=1e-5, atol=1e-5)
+
+
+# ------------------------------------------------------ fused inference epilogue
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["both", "skip_vector", "gate_gelu", "bf16"])
+def test_forward_epilogue_matches_torch_ops(kb, mode):
+    """epilogue=...: y += lambda_skip * z, then y *= act(gate), y_var *= act(gate)^2 at the store
+    (src/kla/layers/kla_layer.py:329-338), forward only."""
+    kla_b200 = kb
+    dev = torch.device("cuda:0")
+    B, L, M, S = 2, 45, 50, 16
+    g = torch.Generator().manual_seed(4)
+    F = torch.nn.functional
+    dt = torch.bfloat16 if mode == "bf16" else torch.float32
+    v = torch.randn(B, L, M, generator=g).to(dev, dt)
+    lv = (1.0 / F.softplus(torch.randn(B, L, M, generator=g))).to(dev, dt)
+    k = F.normalize(torch.randn(B, L, S, generator=g), dim=-1).to(dev, dt)
+    q = F.normalize(torch.randn(B, L, S, generator=g), dim=-1).to(dev, dt)
+    a = torch.sigmoid(torch.randn(M, S, generator=g)).to(dev)
+    p = F.softplus(torch.randn(M, S, generator=g)).to(dev)
+    z = torch.randn(B, L, M, generator=g).to(dev, dt)
+    gate = torch.randn(B, L, M, generator=g).to(dev, dt)
+    skip = torch.randn(M, generator=g).to(dev) if mode == "skip_vector" else torch.tensor(-0.7, device=dev)
+    act = "gelu" if mode == "gate_gelu" else "silu"
+    epi = {}
+    if mode != "gate_gelu":
+        epi.update(z=z, lambda_skip=skip)
+    if mode != "skip_vector":
+        epi.update(gate=gate, gate_activation=act)
+    with torch.no_grad():
+        y, y_var, st = kla_b200.kla_scan_b200(v, lv, k, q, a, p, epilogue=epi)
+        y0, yv0, st0 = kla_b200.kla_scan_b200(v, lv, k, q, a, p)
+    ref, refv = y0.clone(), yv0.clone()
+    if "z" in epi:
+        ref = ref + skip * z.float()
+    if "gate" in epi:
+        gg = getattr(F, act)(gate.float())
+        ref, refv = ref * gg, refv * gg * gg
+    torch.testing.assert_close(y, ref, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(y_var, refv, rtol=1e-5, atol=1e-5)
+    assert torch.equal(st.lam, st0.lam) and torch.equal(st.eta, st0.eta)
+    with pytest.raises(NotImplementedError, match="no_grad"):
+        kla_b200.kla_scan_b200(v.requires_grad_(True), lv, k, q, a, p, epilogue=epi)
+    with pytest.raises(ValueError, match="together"):
+        with torch.no_grad():
+            kla_b200.kla_scan_b200(v.detach(), lv, k, q, a, p, epilogue=dict(z=z))
