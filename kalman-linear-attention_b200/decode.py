@@ -20,6 +20,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _lib
+from .ops import kla_scan_b200
 
 CONFIG_KEYS = (
     "d_state", "discretization", "zero_process_noise", "clip_value", "obs_var_min", "obs_var_max",
@@ -101,6 +102,70 @@ class LayerDecoder:
     def _linear(self, x, name):
         return F.linear(x, self.w[name + ".weight"], self.w.get(name + ".bias"))
 
+    def _sensors(self, z, sens):
+        """Split the sensor projection as ``KLALayer._project_sensors`` does (kla_layer.py:199-216), raw."""
+        cfg, M, S = self.cfg, self.M, self.S
+        o = 0
+        if cfg["value_rank"] == "conv":
+            v = z
+        else:
+            v = sens[..., o:o + self.w_value]
+            o += self.w_value
+            if "value_expand.weight" in self.w:
+                v = self._linear(v, "value_expand")
+        ls = sens[..., o:o + self.w_var]
+        o += self.w_var
+        if "var_expand.weight" in self.w:
+            ls = self._linear(ls, "var_expand")
+        return v, ls, sens[..., o:o + S], sens[..., o + S:o + 2 * S]
+
+    @torch.no_grad()
+    def prefill(self, x: torch.Tensor, state=None):
+        """A whole prompt: the layer's ``forward(x, state)`` for ``L > 1`` in inference
+        (kla_layer.py:295-345). ``x``: [B, L, d_model]. The projections and the causal convolution are
+        library calls; the scan runs with the sensor prologue and the skip/gate epilogue inside
+        (``kla_scan_b200(log_variance=, epilogue=)``). Returns ``(out, state)`` -- or ``((out, out_var),
+        state)`` -- with ``state`` ready for ``step``."""
+        if not x.is_cuda:
+            raise NotImplementedError("The b200 kernels need CUDA tensors; use the reference layer on this device.")
+        cfg, M = self.cfg, self.M
+        B, L, _ = x.shape
+        if state is None:
+            state = self.init_state(B, x.device, x.dtype)
+        conv_state, lam, eta = state
+        projected = self._linear(x, "in_proj")
+        z, gate = (projected[..., :M], projected[..., M:]) if cfg["use_gating"] else (projected, None)
+        if cfg["use_conv"]:
+            K = cfg["conv_kernel_size"]
+            x_pad = torch.cat((conv_state.to(x.dtype), z.transpose(1, 2)), dim=-1)
+            y = F.conv1d(x_pad, self.w["conv.weight"].to(x.dtype),
+                         None if self.conv_b is None else self.conv_b.to(x.dtype), groups=M)
+            conv_state.copy_(x_pad[..., x_pad.shape[-1] - (K - 1):])
+            act = {"silu": F.silu, "gelu": F.gelu, "relu": F.relu}[cfg["conv_activation"]]
+            z = act(y).transpose(1, 2)
+        v, ls, k, q = self._sensors(z, self._linear(z, "sensor_proj"))
+        if cfg["qk_norm"]:  # [B, L, S]: small next to the [B, L, M] tensors, left to torch
+            k = k / k.norm(dim=-1, keepdim=True).clamp_min(1e-12)
+            q = q / q.norm(dim=-1, keepdim=True).clamp_min(1e-12)
+        if cfg["clip_value"] is not None:
+            k, q = k.clamp(-cfg["clip_value"], cfg["clip_value"]), q.clamp(-cfg["clip_value"], cfg["clip_value"])
+        epi = {}
+        if self.skip is not None:
+            epi.update(z=z, lambda_skip=self.skip)
+        if gate is not None:
+            epi.update(gate=gate, gate_activation=cfg["gating_activation"])
+        y, y_var, st = kla_scan_b200(
+            v, ls, k, q, self.a_bar, self.p_bar, initial_state=(lam, eta), decode_from_prior=cfg["decode_from_prior"],
+            out_dtype=x.dtype if x.dtype == torch.bfloat16 else None,
+            log_variance=(cfg["obs_var_min"], cfg["obs_var_max"]), epilogue=epi or None)
+        lam.copy_(st.lam)
+        eta.copy_(st.eta)
+        y, y_var = y.to(x.dtype), y_var.to(x.dtype)
+        out = self._linear(y, "out_proj")
+        if cfg["return_variance"]:
+            return (out, F.linear(y_var, self.w["out_proj.weight"].pow(2))), state
+        return out, state
+
     def step(self, x: torch.Tensor, state):
         """One token. ``x``: [B, d_model]; ``state``: the tuple of ``init_state``, updated in place.
         Returns ``out`` [B, d_model], or ``(out, out_var)`` when the config returns variances."""
@@ -126,19 +191,7 @@ class LayerDecoder:
                 _lib.check(lib.kla_b200_conv_step(ctypes.byref(ca), stream))
                 z = zc
             sens = self._linear(z, "sensor_proj")
-            o = 0
-            if cfg["value_rank"] == "conv":
-                v = z
-            else:
-                v = sens[:, o:o + self.w_value]
-                o += self.w_value
-                if "value_expand.weight" in self.w:
-                    v = self._linear(v, "value_expand")
-            ls = sens[:, o:o + self.w_var]
-            o += self.w_var
-            if "var_expand.weight" in self.w:
-                ls = self._linear(ls, "var_expand")
-            k, q = sens[:, o:o + S], sens[:, o + S:o + 2 * S]
+            v, ls, k, q = self._sensors(z, sens)
             y = torch.empty(B, M, device=x.device, dtype=x.dtype)
             y_var = torch.empty_like(y)
             sa = _lib.StepLayerArgs(

@@ -6,8 +6,8 @@ Each case builds a reference ``kla.KLALayer`` on CPU in float32 (backend="torch"
 few tokens, then decodes three tokens one at a time through the layer's own decode route
 (``layer(x_t, state=state)``, src/kla/layers/kla_layer.py:295-345). Stored: the layer's
 state_dict, the config fields the decode path reads, the discretised (a_bar, p_bar) of
-``_compute_aq``, the state after the prefill, the three inputs, and after every decoded
-token the layer output(s) and the full state.
+``_compute_aq``, the prefill input and output, the state after the prefill, the three inputs,
+and after every decoded token the layer output(s) and the full state.
 """
 
 import os
@@ -33,8 +33,12 @@ def case(name, d_model, batch, seed, **cfg):
             p.add_(0.05 * torch.randn_like(p))
         x0 = torch.randn(batch, 5, d_model)
         xs = torch.randn(3, batch, 1, d_model)
-        _, state = layer(x0, return_state=True)
-        out = {"x": xs[:, :, 0].numpy()}
+        pre, state = layer(x0, return_state=True)
+        out = {"x": xs[:, :, 0].numpy(), "x0": x0.numpy()}
+        if layer.config.return_variance:
+            out["pre_out"], out["pre_outvar"] = pre[0].numpy(), pre[1].numpy()
+        else:
+            out["pre_out"] = pre.numpy()
         for k_, v_ in layer.state_dict().items():
             out["w:" + k_] = v_.numpy()
         for k_ in CONFIG_KEYS:

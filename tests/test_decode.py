@@ -142,3 +142,27 @@ def test_decode_step_is_graph_capturable():
     torch.cuda.synchronize()
     torch.testing.assert_close(out.cpu(), torch.from_numpy(z["out0"]), rtol=1e-4, atol=1e-5)
     torch.testing.assert_close(state[1].cpu(), torch.from_numpy(z["lam1"]), rtol=2e-5, atol=1e-6)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", CASES)
+def test_prefill_then_decode_matches_reference_layer(name):
+    """The whole inference route: prefill through the scan kernels (sensor prologue and skip/gate
+    epilogue inside), then token-by-token decode from the state the prefill left."""
+    dev = torch.device("cuda:0")
+    z, weights, config = load(name)
+    dec = kla_b200.LayerDecoder(weights, config).to(dev)
+    pre, state = dec.prefill(torch.from_numpy(z["x0"]).to(dev))
+    outs = pre if isinstance(pre, tuple) else (pre,)
+    torch.testing.assert_close(outs[0].cpu(), torch.from_numpy(z["pre_out"]), rtol=1e-4, atol=2e-5)
+    if config["return_variance"]:
+        torch.testing.assert_close(outs[1].cpu(), torch.from_numpy(z["pre_outvar"]), rtol=1e-4, atol=2e-5)
+    if "conv0" in z:
+        torch.testing.assert_close(state[0].cpu(), torch.from_numpy(z["conv0"]), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(state[1].cpu(), torch.from_numpy(z["lam0"]), rtol=5e-5, atol=1e-5)
+    torch.testing.assert_close(state[2].cpu(), torch.from_numpy(z["eta0"]), rtol=5e-5, atol=1e-5)
+    for t in range(3):
+        res = dec.step(torch.from_numpy(z["x"][t]).to(dev), state)
+        out = res[0] if isinstance(res, tuple) else res
+        torch.testing.assert_close(out.cpu(), torch.from_numpy(z[f"out{t}"]), rtol=2e-4, atol=3e-5)
+    torch.testing.assert_close(state[1].cpu(), torch.from_numpy(z["lam3"]), rtol=1e-4, atol=1e-5)
