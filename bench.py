@@ -773,6 +773,95 @@ def run_prologue(args):
     }), flush=True)
 
 
+def run_inference(args):
+    """Secondary line: the inference route of one layer at the decode configuration (batch 32,
+    d_model 1024 -> M = 2048, S = 16, bf16): a prompt of 8192 tokens through LayerDecoder.prefill
+    (projections and conv as library calls, the scan with sensor prologue and skip/gate epilogue
+    inside), then 256 tokens decoded one by one from the state it leaves (CUDA graph of 64 tokens)."""
+    import torch
+
+    dec_mod = __import__("importlib").import_module("kalman-linear-attention_b200.decode")
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, DM, S, K, LP, NTOK = (args.batch or 32), 1024, 16, 4, 8192, 64
+    M = 2 * DM
+    dt = torch.bfloat16
+    g = torch.Generator(device="cpu").manual_seed(0)
+    rn = lambda *sh, scale=1.0: (torch.randn(*sh, generator=g) * scale)
+    weights = {
+        "in_proj.weight": rn(2 * M, DM, scale=DM ** -0.5).to(dt), "sensor_proj.weight": rn(2 * M + 2 * S, M, scale=M ** -0.5).to(dt),
+        "out_proj.weight": rn(DM, M, scale=M ** -0.5).to(dt), "conv.weight": rn(M, 1, K, scale=0.5), "conv.bias": torch.zeros(M),
+        "delta": rn(M, S) - 4.0, "lambda_log": rn(M, S, scale=0.1), "process_noise": torch.full((M, S), 0.01),
+        "lambda_skip": torch.tensor(-1.0),
+    }
+    config = dict(d_state=S, discretization="ou", zero_process_noise=False, clip_value=None, obs_var_min=1e-4,
+                  obs_var_max=None, value_rank="full", qk_norm=True, use_conv=True, conv_kernel_size=K,
+                  conv_activation="silu", use_gating=True, gating_activation="silu", use_lambda_skip=True,
+                  return_variance=False, decode_from_prior=False)
+    dec = dec_mod.LayerDecoder(weights, config).to(dev)
+    prompt = torch.randn(B, LP, DM, device=dev, dtype=dt)
+    xs = torch.randn(NTOK, B, DM, device=dev, dtype=dt)
+    lib = __import__("importlib").import_module("kalman-linear-attention_b200._lib")
+
+    def timed(fn, n):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    n_pre = max(1, min(args.steps, 10))
+    state_box = {}
+
+    def prefill():
+        state_box["out"], state_box["state"] = dec.prefill(prompt)
+
+    ms_pre = timed(prefill, n_pre)
+    # the scan alone, on tensors of the same shapes and types
+    v = torch.randn(B, LP, M, device=dev, dtype=dt)
+    k = torch.nn.functional.normalize(torch.randn(B, LP, S, device=dev), dim=-1).to(dt)
+    import kla_b200
+    with torch.no_grad():
+        ms_scan = timed(lambda: kla_b200.kla_scan_b200(
+            v, v, k, k, dec.a_bar, dec.p_bar, out_dtype=dt, log_variance=(1e-4, None),
+            epilogue=dict(z=v, lambda_skip=dec.skip, gate=v, gate_activation="silu")), n_pre)
+    state = state_box["state"]
+    dec.step(xs[0], state)
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for t in range(NTOK):
+                out = dec.step(xs[t], state)
+    torch.cuda.current_stream().wait_stream(s)
+    us_tok = timed(gr.replay, max(args.steps, 4)) * 1e3 / NTOK
+    total_ms = ms_pre + 256 * us_tok * 1e-3
+    esz = 2
+    scan_bytes = B * LP * esz * (6 * M + 2 * S)  # v, log-variance, z, gate in; y, y_var out; k, q
+    peak, src = peaks()
+    print(json.dumps({
+        "metric": "KLA layer inference tokens/s (prefill 8192 + 256 decoded, one layer)",
+        "value": B * (LP + 256) / (total_ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": n_pre,
+        "warmup": max(args.warmup, 3), "ms_per_step": total_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 activations and projections, f32 filter state", "data": "synthetic",
+        "config": {"workload": f"one KLA layer, B={B} d_model={DM} M={M} S={S}: prefill of {LP} tokens, then 256 tokens "
+                               "decoded one at a time (64-token CUDA graph)",
+                   "prefill_ms": ms_pre, "prefill_tokens_per_s": B * LP / (ms_pre * 1e-3),
+                   "scan_only_ms": ms_scan, "decode_us_per_token": us_tok, "finite": bool(torch.isfinite(out.float()).all())},
+        "roofline": {"bound": "hbm", "kernel": "kla_fwd_kernel<bf16, bf16> with prologue and epilogue (prefill)",
+                     "achieved": scan_bytes / (ms_scan * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": scan_bytes / (ms_scan * 1e-3) / 1e9 / peak, "traffic": None, "peak_source": src,
+                     "algorithmic_bytes": scan_bytes, "ms": ms_scan},
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -786,7 +875,7 @@ def main():
     ap.add_argument("--batch", type=int, default=0,
                     help="raw workload only: batch size per GPU instead of 8, for the occupancy sweep "
                          "(B=4 leaves one CTA per SM, B=16 fills every SM); the headline stays B=8")
-    ap.add_argument("--workload", default="raw", choices=["raw", "seqshard", "decode", "rawpair", "decode_layer", "prologue"],
+    ap.add_argument("--workload", default="raw", choices=["raw", "seqshard", "decode", "rawpair", "decode_layer", "prologue", "inference"],
                     help="raw = the headline raw-op workload (default); seqshard = the long-sequence, "
                          "time-sharded workload (secondary line)")
     args = ap.parse_args()
@@ -802,6 +891,8 @@ def main():
         return run_decode_layer(args)
     if args.workload == "prologue" and args.impl != "reference":
         return run_prologue(args)
+    if args.workload == "inference" and args.impl != "reference":
+        return run_inference(args)
     if args.impl == "reference":
         run_reference(args)
     else:
