@@ -165,7 +165,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         //   update(t)    the serial part: P -> denominator -> reciprocal -> P, mean
         //   readout(t)   this thread's share of y, y_var to shared memory
         //   prep(t+1)    everything of the next step that does not depend on the
-        //                state (phi, r, the two denominator coefficients)
+        //                state (phi, r)
         // so the loads and the state-independent arithmetic of step t+1 sit
         // between the dependent instructions of step t.
         struct StepIn {
@@ -173,7 +173,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             float2 k[HP], q[HP];  // this thread's states, in pairs
         };
         struct StepPre {
-            float2 r[CH][HP], c0[CH][HP], c1[CH][HP], q[HP];
+            float2 r[CH][HP], phi[CH][HP], q[HP];
         };
         auto fetch = [&](StepIn &in, const T *lrow, const float *lfrow, const T *vrow, const float *kqrow, int tt) {
 #pragma unroll
@@ -204,9 +204,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                 pr.q[h] = in.q[h];
 #pragma unroll
                 for (int ci = 0; ci < CH; ++ci) {
-                    float2 phi;
-                    chain_inputs2(dup2(in.lv[ci]), dup2(in.vv[ci]), in.k[h], phi, pr.r[ci][h]);
-                    chain_denominator_coeffs2(phi, ca2[ci][h], cp[ci][h], pr.c1[ci][h], pr.c0[ci][h]);
+                    chain_inputs2(dup2(in.lv[ci]), dup2(in.vv[ci]), in.k[h], pr.phi[ci][h], pr.r[ci][h]);
                 }
             }
         };
@@ -216,8 +214,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             for (int h = 0; h < HP; ++h)
 #pragma unroll
                 for (int ci = 0; ci < CH; ++ci) {
-                    Pp[ci][h] = fma2(ca2[ci][h], P[ci][h], cp[ci][h]);
-                    g[ci][h] = fma2(pr.c1[ci][h], P[ci][h], pr.c0[ci][h]);
+                    g[ci][h] = chain_denominator2(P[ci][h], pr.phi[ci][h], ca2[ci][h], cp[ci][h], Pp[ci][h]);
                 }
 #pragma unroll
             for (int h = 0; h < HP; ++h)
