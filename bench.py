@@ -51,7 +51,7 @@ def algorithmic_bytes_per_token(M, S, esz=4):
 # from profiles/kla_scan_fwd_bwd_B8_T4096_M1024_S16_f32.md; the raw-scan figure is per batch
 # entry (captured at B=1, T=4096, M*S=16384; traffic is proportional to B), from
 # profiles/kla_rawscan_T4096_N16384_f32.md.
-NCU_TRAFFIC = {"kla_bwd_kernel": 1075.5e6, "kla_fwd_kernel": 760.4e6, "rawscan_mobius_bwd_per_batch": 2651.5e6}
+NCU_TRAFFIC = {"kla_bwd_kernel": 1076.2e6, "kla_fwd_kernel": 760.8e6, "rawscan_mobius_bwd_per_batch": 2651.5e6}
 
 
 def make_inputs(seed=0, **w):
@@ -345,7 +345,7 @@ def run_b200(args):
                          "unit": "GB/s", "frac": ach_bwd / peak, "traffic": NCU_TRAFFIC["kla_bwd_kernel"] * B / 8,
                          "peak_source": peak_src, "algorithmic_bytes": bwd_bytes, "ms": bwd_ms,
                          "nominal_peak_gbs": 8000.0, "frac_of_nominal": ach_bwd / 8000.0,
-                         "note": "not HBM-bound at d_state=16: 66 warp-instructions per 32 lane-steps against 24.8 KB per "
+                         "note": "not HBM-bound at d_state=16: 62 warp-instructions per 32 lane-steps against 24.8 KB per "
                                  "token; ncu shows the FP32 pipe ~50 % and issue slots ~68 % busy with two compute warps "
                                  "per scheduler (dependent-instruction latency, shared-memory pipe)"},
             "roofline_fwd": {"bound": "hbm", "kernel": "kla_fwd_kernel", "achieved": ach_fwd, "peak": peak,
