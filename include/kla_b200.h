@@ -250,6 +250,27 @@ typedef struct kla_b200_conv_step_args {
 int kla_b200_conv_step(const kla_b200_conv_step_args *args, void *stream);
 
 /*
+ * The same convolution over a whole prompt: CausalConv1d.forward for L > 1
+ * (src/kla/layers/common.py:87-96), in the layer's [B, L, D] layout (the
+ * reference transposes to [B, D, L] and back around conv1d). state holds the
+ * K-1 inputs before the prompt; the last K-1 inputs are written to state_out,
+ * which must be a different buffer (blocks working on other parts of the prompt
+ * still read state).
+ */
+typedef struct kla_b200_conv_seq_args {
+    int64_t B, L, D, K;
+    int32_t dtype, activation;
+    kla_b200_tensor3 x;   /* in  [B, L, D] */
+    const float *weight;  /* in  [D, K] */
+    const float *bias;    /* in  [D] or NULL */
+    const void *state;    /* in  [B, D, K-1] contiguous */
+    void *state_out;      /* out [B, D, K-1] contiguous, not aliasing state */
+    kla_b200_tensor3 z;   /* out [B, L, D] */
+} kla_b200_conv_seq_args;
+
+int kla_b200_conv_seq(const kla_b200_conv_seq_args *args, void *stream);
+
+/*
  * kla_b200_step_layer is kla_b200_step with the layer's prologue and epilogue
  * folded in (src/kla/layers/kla_layer.py:199-231, 277-293, 329-338): it takes
  * the sensor projection's raw outputs and produces the input of out_proj.

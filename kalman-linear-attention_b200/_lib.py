@@ -24,6 +24,7 @@ SYMBOLS = (
     "kla_b200_step",
     "kla_b200_slab_aggregate",
     "kla_b200_conv_step",
+    "kla_b200_conv_seq",
     "kla_b200_step_layer",
     "kla_b200_mobius_scan_fwd",
     "kla_b200_mobius_scan_bwd",
@@ -50,6 +51,15 @@ class ConvStepArgs(Structure):
         ("dtype", c_int32), ("activation", c_int32),
         ("x", c_void_p), ("x_stride_b", c_int64),
         ("weight", c_void_p), ("bias", c_void_p), ("state", c_void_p), ("z", c_void_p),
+    ]
+
+
+class ConvSeqArgs(Structure):
+    _fields_ = [
+        ("B", c_int64), ("L", c_int64), ("D", c_int64), ("K", c_int64),
+        ("dtype", c_int32), ("activation", c_int32),
+        ("x", Tensor3), ("weight", c_void_p), ("bias", c_void_p), ("state", c_void_p), ("state_out", c_void_p),
+        ("z", Tensor3),
     ]
 
 
@@ -164,6 +174,8 @@ def load() -> ctypes.CDLL:
         fn.argtypes = [POINTER(RawScanArgs), c_void_p]
     lib.kla_b200_conv_step.restype = c_int
     lib.kla_b200_conv_step.argtypes = [POINTER(ConvStepArgs), c_void_p]
+    lib.kla_b200_conv_seq.restype = c_int
+    lib.kla_b200_conv_seq.argtypes = [POINTER(ConvSeqArgs), c_void_p]
     lib.kla_b200_step_layer.restype = c_int
     lib.kla_b200_step_layer.argtypes = [POINTER(StepLayerArgs), c_void_p]
     lib.kla_b200_step.restype = c_int

@@ -455,6 +455,34 @@ int kla_b200_conv_step(const kla_b200_conv_step_args *a, void *stream) {
     return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
 }
 
+int kla_b200_conv_seq(const kla_b200_conv_seq_args *a, void *stream) {
+    if (a == nullptr || a->B < 0 || a->L < 0 || a->D < 0) return KLA_B200_EINVAL;
+    if (a->K < 1 || a->K > KLA_B200_MAX_CONV_TAPS) return KLA_B200_EUNSUPPORTED;
+    if (a->dtype != KLA_B200_F32 && a->dtype != KLA_B200_BF16) return KLA_B200_EUNSUPPORTED;
+    if (a->activation < KLA_B200_ACT_SILU || a->activation > KLA_B200_ACT_NONE) return KLA_B200_EINVAL;
+    if (a->B > 65535 || a->L > (1 << 30) || a->D > (1 << 30)) return KLA_B200_EUNSUPPORTED;
+    if (a->B == 0 || a->D == 0 || a->L == 0) return KLA_B200_OK;
+    if (!a->weight || (a->K > 1 && (!a->state || !a->state_out || a->state == a->state_out))) return KLA_B200_EINVAL;
+    const size_t esz = a->dtype == KLA_B200_F32 ? 4 : 2;
+    int rc;
+    if ((rc = check_t3(a->x, esz, true))) return rc;
+    if ((rc = check_t3(a->z, esz, true))) return rc;
+    if ((a->state && !aligned(a->state, esz)) || (a->state_out && !aligned(a->state_out, esz))) return KLA_B200_EALIGN;
+    const int64_t chunks = (a->L + kConvChunk - 1) / kConvChunk;
+    if (chunks > 65535) return KLA_B200_EUNSUPPORTED;
+    ConvSeqParams prm{};
+    prm.B = (int)a->B; prm.L = (int)a->L; prm.D = (int)a->D; prm.K = (int)a->K;
+    prm.x = t3(a->x); prm.z = t3(a->z); prm.w = a->weight; prm.bias = a->bias; prm.state = a->state;
+    prm.state_out = a->state_out; prm.act = a->activation;
+    dim3 grid((unsigned)((a->D + 127) / 128), (unsigned)chunks, (unsigned)a->B);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (a->dtype == KLA_B200_F32) kla_conv_seq_kernel<float><<<grid, 128, 0, st>>>(prm);
+    else kla_conv_seq_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(prm);
+    g_launches++;
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
+}
+
 int kla_b200_step_layer(const kla_b200_step_layer_args *a, void *stream) {
     if (a == nullptr) return KLA_B200_EINVAL;
     int rc = check_common(a->B, 1, a->M, a->S, a->in_dtype, a->out_dtype);

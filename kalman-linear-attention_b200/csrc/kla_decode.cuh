@@ -56,6 +56,76 @@ __global__ void __launch_bounds__(128) kla_conv_step_kernel(const ConvStepParams
     static_cast<T *>(prm.z)[gid] = from_f32<T>(activate(acc, prm.act));
 }
 
+// The same convolution over a whole prompt (CausalConv1d.forward for L > 1): one thread per channel
+// and chunk of kConvChunk consecutive tokens keeps the K-1 previous inputs in registers, so every input
+// is read once; lanes run over channels, so rows are read and written coalesced in the layer's own
+// [B, L, D] layout (the reference transposes to [B, D, L] and back around its conv1d call). The block that
+// owns the last chunk also writes the new window (the last K-1 inputs) to state_out.
+struct ConvSeqParams {
+    int B, L, D, K;
+    Tensor3 x, z;          // [B, L, D]
+    const float *w, *bias; // [D, K], [D] or nullptr
+    const void *state;     // [B, D, K-1]: the window before the prompt
+    void *state_out;       // [B, D, K-1]: the window after it (another buffer: blocks of other chunks still read state)
+    int act;
+};
+
+constexpr int kConvChunk = 32;
+
+template <typename T>
+__global__ void __launch_bounds__(128) kla_conv_seq_kernel(const ConvSeqParams prm) {
+    const int d = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.z;
+    const int t0 = blockIdx.y * kConvChunk;
+    if (d >= prm.D) return;
+    const int K = prm.K, L = prm.L;
+    const T *xb = static_cast<const T *>(prm.x.ptr) + (long long)b * prm.x.sb + d;
+    T *zb = static_cast<T *>(prm.z.ptr) + (long long)b * prm.z.sb + d;
+    const T *st = static_cast<const T *>(prm.state) + ((long long)b * prm.D + d) * (K - 1);
+    T *sto = static_cast<T *>(prm.state_out) + ((long long)b * prm.D + d) * (K - 1);
+    float w[kConvMaxTaps], win[kConvMaxTaps];  // win[jj]: input at time t - (K-1) + jj, jj < K-1
+#pragma unroll
+    for (int jj = 0; jj < kConvMaxTaps; ++jj) {
+        w[jj] = jj < K ? prm.w[(long long)d * K + jj] : 0.0f;
+        win[jj] = 0.0f;
+        if (jj < K - 1) {
+            const int t = t0 - (K - 1) + jj;  // before the prompt: the carried window
+            win[jj] = t >= 0 ? to_f32<T>(xb[(long long)t * prm.x.st]) : to_f32<T>(st[t + (K - 1)]);
+        }
+    }
+    const float bias = prm.bias != nullptr ? prm.bias[d] : 0.0f;
+    const int t1 = min(L, t0 + kConvChunk);
+    const bool last = t1 == L;
+    // the window after the prompt is made of the last K-1 inputs; those older than the prompt come from the
+    // carried window
+    float keep[kConvMaxTaps];
+    if (last) {
+#pragma unroll
+        for (int jj = 0; jj < kConvMaxTaps; ++jj)
+            if (jj < K - 1) {
+                const int t = L - (K - 1) + jj;
+                keep[jj] = t >= 0 ? to_f32<T>(xb[(long long)t * prm.x.st]) : to_f32<T>(st[t + (K - 1)]);
+            }
+    }
+    for (int t = t0; t < t1; ++t) {
+        const float xin = to_f32<T>(xb[(long long)t * prm.x.st]);
+        float acc = bias;
+#pragma unroll
+        for (int jj = 0; jj < kConvMaxTaps; ++jj)
+            if (jj < K - 1) acc = fmaf(w[jj], win[jj], acc);
+        acc = fmaf(w[K - 1], xin, acc);
+#pragma unroll
+        for (int jj = 0; jj < kConvMaxTaps - 1; ++jj)
+            if (jj + 1 < K - 1) win[jj] = win[jj + 1];
+        if (K > 1) win[K - 2] = xin;
+        zb[(long long)t * prm.z.st] = from_f32<T>(activate(acc, prm.act));
+    }
+    if (last) {
+#pragma unroll
+        for (int jj = 0; jj < kConvMaxTaps; ++jj)
+            if (jj < K - 1) sto[jj] = from_f32<T>(keep[jj]);
+    }
+}
+
 struct StepLayerParams {
     int B, M, S;
     const void *v, *ls, *k, *q, *z, *gate;  // z, gate may be nullptr

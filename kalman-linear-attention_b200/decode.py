@@ -122,8 +122,8 @@ class LayerDecoder:
     @torch.no_grad()
     def prefill(self, x: torch.Tensor, state=None):
         """A whole prompt: the layer's ``forward(x, state)`` for ``L > 1`` in inference
-        (kla_layer.py:295-345). ``x``: [B, L, d_model]. The projections and the causal convolution are
-        library calls; the scan runs with the sensor prologue and the skip/gate epilogue inside
+        (kla_layer.py:295-345). ``x``: [B, L, d_model]. The projections are library GEMMs; the causal
+        convolution runs in ``kla_b200_conv_seq``; the scan runs with the sensor prologue and the skip/gate epilogue inside
         (``kla_scan_b200(log_variance=, epilogue=)``). Returns ``(out, state)`` -- or ``((out, out_var),
         state)`` -- with ``state`` ready for ``step``."""
         if not x.is_cuda:
@@ -136,13 +136,20 @@ class LayerDecoder:
         projected = self._linear(x, "in_proj")
         z, gate = (projected[..., :M], projected[..., M:]) if cfg["use_gating"] else (projected, None)
         if cfg["use_conv"]:
-            K = cfg["conv_kernel_size"]
-            x_pad = torch.cat((conv_state.to(x.dtype), z.transpose(1, 2)), dim=-1)
-            y = F.conv1d(x_pad, self.w["conv.weight"].to(x.dtype),
-                         None if self.conv_b is None else self.conv_b.to(x.dtype), groups=M)
-            conv_state.copy_(x_pad[..., x_pad.shape[-1] - (K - 1):])
-            act = {"silu": F.silu, "gelu": F.gelu, "relu": F.relu}[cfg["conv_activation"]]
-            z = act(y).transpose(1, 2)
+            # the causal convolution over the prompt, in place of cat + transpose + conv1d + activation + transpose
+            zc = torch.empty(B, L, M, device=x.device, dtype=x.dtype)
+            new_window = torch.empty_like(conv_state)
+            dt = _lib.F32 if x.dtype == torch.float32 else _lib.BF16
+            P = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())
+            ca = _lib.ConvSeqArgs(B=B, L=L, D=M, K=cfg["conv_kernel_size"], dtype=dt,
+                                  activation=_lib.ACT[cfg["conv_activation"]],
+                                  x=_lib.Tensor3(z.data_ptr(), z.stride(0), z.stride(1)), weight=P(self.conv_w),
+                                  bias=P(self.conv_b), state=P(conv_state), state_out=P(new_window),
+                                  z=_lib.Tensor3(zc.data_ptr(), zc.stride(0), zc.stride(1)))
+            with torch.cuda.device(x.device):
+                _lib.check(_lib.load().kla_b200_conv_seq(ctypes.byref(ca), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+            conv_state.copy_(new_window)
+            z = zc
         v, ls, k, q = self._sensors(z, self._linear(z, "sensor_proj"))
         if cfg["qk_norm"]:  # [B, L, S]: small next to the [B, L, M] tensors, left to torch
             k = k / k.norm(dim=-1, keepdim=True).clamp_min(1e-12)
