@@ -124,13 +124,18 @@ template <typename T, typename TO, int LPC, bool PRIOR>
 int launch_fwd(FwdParams &prm, const kla_b200_fwd_args &a, cudaStream_t st) {
     using Sh = ScanShape<kSPT, LPC, kCH, kNW, kNH, kTT>;
     using Sm = FwdSmem<T, kSPT, LPC, kCH, kNW, kNH, kTT>;
-    auto kern = kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR>;
+    auto kern = prm.epilogue ? kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, true>
+                             : kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, false>;
     prm.use_tma = !g_no_tma && make_tile_map<T>(&prm.tm_v, a.v, a.B, a.L, a.M, Sh::kMC, kTT) &&
                   make_tile_map<T>(&prm.tm_lv, a.lambda_v, a.B, a.L, a.M, Sh::kMC, kTT);
+    if (prm.epilogue)  // z and gate tiles travel like v and lambda_v when they meet the tensor-map rules
+        prm.epi_tma = !g_no_tma && (a.z.ptr == nullptr || make_tile_map<T>(&prm.tm_z, a.z, a.B, a.L, a.M, Sh::kMC, kTT)) &&
+                      (a.gate.ptr == nullptr || make_tile_map<T>(&prm.tm_gate, a.gate, a.B, a.L, a.M, Sh::kMC, kTT));
+    const size_t smem = prm.epilogue ? Sm::kTotal : Sm::kPlain;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sm::kTotal);
     if (e != cudaSuccess) return cuda_fail(e);
     dim3 grid((unsigned)((prm.M + Sh::kMC - 1) / Sh::kMC), (unsigned)prm.B);
-    kern<<<grid, Sh::kThreads, Sm::kTotal, st>>>(prm);
+    kern<<<grid, Sh::kThreads, smem, st>>>(prm);
     g_launches++;
     e = cudaGetLastError();
     return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);

@@ -141,6 +141,13 @@ __device__ __forceinline__ float activate(float x, int act) {
     }
 }
 
+// The same for the scan's drainer warps, which have a tile time to finish a tile's outputs: hardware
+// exp2 and reciprocal approximations (relative error ~1e-6) for the sigmoid of silu.
+__device__ __forceinline__ float activate_fast(float x, int act) {
+    if (act == kActSilu) return x * rcp_approx(1.0f + __expf(-x));
+    return activate(x, act);
+}
+
 // torch.nn.functional.softplus with its default threshold of 20
 __device__ __forceinline__ float softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 // Value precision from the sensor projection's raw output, as the reference layer forms it

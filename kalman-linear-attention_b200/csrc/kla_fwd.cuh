@@ -30,6 +30,7 @@ namespace kla {
 
 constexpr int kInStages = 3;   // input stages in flight
 constexpr int kOutStages = 2;  // read-out partial buffers
+constexpr int kEpiStages = 3;  // tiles of the epilogue operands (z, gate) in flight, as deep as the inputs
 #ifndef KLA_FWD_UNROLL
 #define KLA_FWD_UNROLL 16
 #endif
@@ -54,7 +55,8 @@ struct alignas(64) FwdParams {
     // type, ptr == nullptr when absent; skip: one value or one per channel.
     Tensor3 z, gate;
     const float *skip;
-    int skip_len, gate_act, epilogue;
+    int skip_len, gate_act, epilogue, epi_tma;
+    alignas(64) CUtensorMap tm_z, tm_gate;  // maps of the epilogue operands, like tm_v; valid when epi_tma
 };
 
 // Shared-memory carve-up, shared by the kernel and the launcher.
@@ -69,10 +71,14 @@ struct FwdSmem {
     static constexpr size_t kLamF = sizeof(T) == 4 ? 0 : ((sizeof(float) * TT * Sh::kMC + 127) / 128) * 128;
     static constexpr size_t kIn = 2 * kTile + kKq + kLamF;
     static constexpr size_t kOut = ((sizeof(float2) * TT * LPC * Sh::kMCP + 127) / 128) * 128;
-    static constexpr size_t kTotal = kBars + kInStages * kIn + kOutStages * kOut;
+    static constexpr size_t kPlain = kBars + kInStages * kIn + kOutStages * kOut;  // without an epilogue
+    static constexpr size_t kEpi = 2 * kTile;                                      // one z and one gate tile
+    static constexpr size_t kTotal = kPlain + kEpiStages * kEpi;                   // epilogue stages sit at the end
 };
 
-template <typename T, typename TO, int SPT, int LPC, int CH, int NW, int NH, int TT, bool PRIOR>
+// EPI: the forward-only layer epilogue (FwdParams::epilogue). A separate instantiation, so that the plain
+// kernel does not carry that code: even untaken it costs the plain path a few per cent.
+template <typename T, typename TO, int SPT, int LPC, int CH, int NW, int NH, int TT, bool PRIOR, bool EPI>
 __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_constant__ FwdParams prm) {
     using Sh = ScanShape<SPT, LPC, CH, NW, NH, TT>;
     using Sm = FwdSmem<T, SPT, LPC, CH, NW, NH, TT>;
@@ -92,8 +98,15 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
     uint64_t *empty_in = full_in + NS;                       // [NS]
     uint64_t *full_out = empty_in + NS;                      // [NO]
     uint64_t *empty_out = full_out + NO;                     // [NO]
+    constexpr int NE = kEpiStages;
+    uint64_t *epi_full = empty_out + NO;                     // [NE]  loaders -> drainers: z, gate tiles loaded
+    uint64_t *epi_empty = epi_full + NE;                     // [NE]  drainers -> loaders: tiles consumed
+    static_assert((2 * NS + 2 * NO + 2 * NE) * sizeof(uint64_t) <= Sm::kBars, "barriers fit their slot");
     unsigned char *in_base = smem + Sm::kBars;
     unsigned char *out_base = in_base + NS * Sm::kIn;
+    unsigned char *epi_base = smem + Sm::kPlain;  // only there when the kernel was launched with an epilogue
+    auto zstage = [&](int e) { return reinterpret_cast<T *>(epi_base + e * Sm::kEpi); };
+    auto gstage = [&](int e) { return reinterpret_cast<T *>(epi_base + e * Sm::kEpi + Sm::kTile); };
     auto vstage = [&](int s) { return reinterpret_cast<T *>(in_base + s * Sm::kIn); };
     auto lstage = [&](int s) { return reinterpret_cast<T *>(in_base + s * Sm::kIn + Sm::kTile); };
     // (k, q) of a step, grouped by owning lane: [TT][LPC][2][SPT] floats, state s = i * LPC + j at [j][.][i]
@@ -117,6 +130,12 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         for (int o = 0; o < NO; ++o) {
             mbar_init(&full_out[o], NW);
             mbar_init(&empty_out[o], kDrainers / 32);
+        }
+        if constexpr (EPI) {
+            for (int e = 0; e < NE; ++e) {
+                mbar_init(&epi_full[e], kProducers);
+                mbar_init(&epi_empty[e], kDrainers / 32);
+            }
         }
         mbar_fence_init();
     }
@@ -384,6 +403,26 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                 if (it + 1 < NT) load_kq(t0 + TT);
                 if (!(prm.use_tma && htid == 0)) mbar_arrive(&full_in[s]);
                 produced = it + 1;
+                if constexpr (EPI) {  // this tile's z and gate, for the drainers
+                    const int e = it % NE;
+                    if (it >= NE && !mbar_wait(&epi_empty[e], (it / NE - 1) & 1, 6, 100)) { ok = false; break; }
+                    const bool has_z = prm.z.ptr != nullptr, has_g = prm.gate.ptr != nullptr;
+                    if (prm.epi_tma) {
+                        if (htid == 0) {
+                            mbar_arrive_expect_tx(&epi_full[e], ((has_z ? 1 : 0) + (has_g ? 1 : 0)) * kTileBytes);
+                            if (has_z) tma_load_3d(zstage(e), &prm.tm_z, m_cta, t0, b, &epi_full[e]);
+                            if (has_g) tma_load_3d(gstage(e), &prm.tm_gate, m_cta, t0, b, &epi_full[e]);
+                        }
+                    } else {
+                        if (has_z)
+                            stage_tile_plain<T, TT, MC, kProducers>(
+                                zstage(e), static_cast<const T *>(prm.z.ptr) + (long long)b * prm.z.sb, prm.z.st, t0, L, m_cta, M, htid);
+                        if (has_g)
+                            stage_tile_plain<T, TT, MC, kProducers>(
+                                gstage(e), static_cast<const T *>(prm.gate.ptr) + (long long)b * prm.gate.sb, prm.gate.st, t0, L, m_cta, M, htid);
+                    }
+                    if (!(prm.epi_tma && htid == 0)) mbar_arrive(&epi_full[e]);
+                }
             }
         } else {
             // ---- drainers: per finished tile, sum the LPC partial read-outs and store y, y_var
@@ -393,20 +432,20 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             for (int jt = 0; jt < NT; ++jt) {
                 const int o = jt % NO, t0 = jt * TT;
                 if (!mbar_wait(&full_out[o], (jt / NO) & 1, 4, 100)) { ok = false; break; }
-                if (prm.epilogue) {
-                    const T *zb = prm.z.ptr ? static_cast<const T *>(prm.z.ptr) + (long long)b * prm.z.sb : nullptr;
-                    const T *gb = prm.gate.ptr ? static_cast<const T *>(prm.gate.ptr) + (long long)b * prm.gate.sb : nullptr;
+                if constexpr (EPI) {
+                    const int e = jt % NE;
+                    if (!mbar_wait(&epi_full[e], (jt / NE) & 1, 7, 100)) { ok = false; break; }
+                    const T *zs = prm.z.ptr ? zstage(e) : nullptr, *gs = prm.gate.ptr ? gstage(e) : nullptr;
                     output_pass<TO, LPC, MC, MCP, TT, kDrainers>(
                         ystage(o), yb + (long long)t0 * prm.y.st, prm.y.st, prm.vec_y,
                         yvb + (long long)t0 * prm.yv.st, prm.yv.st, prm.vec_yv, min(TT, L - t0), m_cta, M, dtid,
                         [&](float2 acc, int tt, int c, float &o0, float &o1) {
                             const int m = m_cta + c;
                             if (m < M) {
-                                if (zb != nullptr)
-                                    acc.x = fmaf(prm.skip[prm.skip_len > 1 ? m : 0],
-                                                 to_f32<T>(zb[(long long)(t0 + tt) * prm.z.st + m]), acc.x);
-                                if (gb != nullptr) {
-                                    const float g = activate(to_f32<T>(gb[(long long)(t0 + tt) * prm.gate.st + m]), prm.gate_act);
+                                if (zs != nullptr)
+                                    acc.x = fmaf(prm.skip[prm.skip_len > 1 ? m : 0], to_f32<T>(zs[tt * MC + c]), acc.x);
+                                if (gs != nullptr) {
+                                    const float g = activate_fast(to_f32<T>(gs[tt * MC + c]), prm.gate_act);
                                     acc.x *= g;
                                     acc.y *= g * g;
                                 }
@@ -414,6 +453,8 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                             o0 = acc.x;
                             o1 = acc.y;
                         });
+                    __syncwarp();
+                    if (hlane == 0) mbar_arrive(&epi_empty[e]);
                 } else {
                     output_pass<TO, LPC, MC, MCP, TT, kDrainers>(
                         ystage(o), yb + (long long)t0 * prm.y.st, prm.y.st, prm.vec_y,
@@ -428,6 +469,8 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         // still in flight into its shared memory.
         if (!ok && prm.use_tma && htid == 0) {
             for (int t = max(0, produced - NS); t < produced; ++t) mbar_wait(&full_in[t % NS], (t / NS) & 1, 5);
+            if (EPI && prm.epi_tma)
+                for (int t = max(0, produced - NE); t < produced; ++t) mbar_wait(&epi_full[t % NE], (t / NE) & 1, 8);
         }
     }
 }
