@@ -8,7 +8,9 @@
  * element strides; none takes or returns a torch type; none allocates device
  * memory (the caller owns outputs and scratch); none throws. All work is
  * enqueued on the CUDA stream passed in (`stream` is a `cudaStream_t` cast to
- * `void*`; NULL is the default stream) on the current device.
+ * `void*`; NULL is the default stream) on the current device. The first scan
+ * call on a device looks up the address of the library's status word on that
+ * device; make that first call outside any stream capture.
  *
  * Notation follows the reference (src/kla/ops/kla_ops.py:1-32):
  *   B batch, L sequence length, M channels, S states per channel
@@ -358,6 +360,19 @@ int64_t kla_b200_launch_count(void);
  * outputs of that launch are then invalid. Reading a non-zero status clears it.
  */
 int kla_b200_device_status(int *status);
+
+/*
+ * Test hooks for the bounded waits; not for production use. The reference has
+ * no counterpart (its kernels use block-wide barriers, which cannot run out).
+ * wait_limit_ns: how long a warp polls a hand-over barrier before it gives up
+ *   (0 restores the default of one second).
+ * skip_tile: the scan kernels' loader leaves the hand-over of this tile
+ *   incomplete, so that the wait for it runs out after wait_limit_ns, the kernel
+ *   returns and kla_b200_device_status reports 0x100 | site; -1 switches it off.
+ * The settings are process-wide and are read when a scan is launched. A tile that
+ * is skipped is loaded all the same: nothing is left in flight and nothing faults.
+ */
+int kla_b200_test_hooks(int64_t wait_limit_ns, int32_t skip_tile);
 
 #ifdef __cplusplus
 }

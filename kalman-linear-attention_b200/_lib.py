@@ -34,6 +34,7 @@ SYMBOLS = (
     "kla_b200_version",
     "kla_b200_launch_count",
     "kla_b200_device_status",
+    "kla_b200_test_hooks",
 )
 
 
@@ -186,6 +187,8 @@ def load() -> ctypes.CDLL:
     lib.kla_b200_launch_count.restype = c_int64
     lib.kla_b200_device_status.restype = c_int
     lib.kla_b200_device_status.argtypes = [POINTER(c_int)]
+    lib.kla_b200_test_hooks.restype = c_int
+    lib.kla_b200_test_hooks.argtypes = [c_int64, c_int32]
     _lib = lib
     return lib
 
@@ -196,6 +199,14 @@ def device_status() -> int:
     st = c_int(0)
     check(load().kla_b200_device_status(ctypes.byref(st)))
     return st.value
+
+
+def check_status(what: str = "kla_b200") -> None:
+    """Raise ``RuntimeError`` if a kernel launched so far on the current device gave up on a bounded wait
+    (its outputs are then invalid). Synchronises, so call it where the caller synchronises anyway."""
+    st = device_status()
+    if st != 0:
+        raise RuntimeError(f"{what}: a kernel gave up on a bounded wait (device status {st:#x}); its outputs are invalid")
 
 
 def check(code: int) -> None:

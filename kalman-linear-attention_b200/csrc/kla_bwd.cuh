@@ -59,6 +59,7 @@ struct alignas(64) BwdParams {
     // lv holds log-variances (see FwdParams); dlv then receives the gradient with respect to them
     int lv_log_sigma;
     float obs_var_min, obs_var_max;
+    WaitCtl wait;
 };
 
 template <typename T, typename TO, int SPT, int LPC, int CH, int NW, int NH, int TT>
@@ -185,7 +186,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
             const int t0 = tile * TT;
             const int n = min(TT, L - t0);
             const bool flip = ti & 1;
-            if (!mbar_wait(&full_in[s], (ti / NS) & 1, 11)) break;
+            if (!mbar_wait(prm.wait, &full_in[s], (ti / NS) & 1, 11)) break;
             if (pro) {  // this warp's channels of the tile: log-variance -> precision, float32
                 const T *raw = lstage(s) + warp * Sh::kCPW;
                 float *lf = lfstage(s) + warp * Sh::kCPW;
@@ -253,7 +254,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
 #pragma unroll 1
             for (int qd = 0; qd < NQ; ++qd) {
                 const int prq = flip ? NQ - 1 - qd : qd;  // physical segment written by steps kSeg*qd .. kSeg*qd + kSeg - 1
-                if (ti > 0 && !mbar_wait(&part_empty[prq], (ti - 1) & 1, 12)) { ok = false; break; }
+                if (ti > 0 && !mbar_wait(prm.wait, &part_empty[prq], (ti - 1) & 1, 12)) { ok = false; break; }
                 if (n == TT) {
 #pragma unroll 1
                     for (int h = 0; h < kSeg; h += kRepUnroll) {
@@ -456,8 +457,8 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
             for (int it = 0; it < NT; ++it) {
                 const int tile = NT - 1 - it, s = it % NS, t0 = tile * TT;
                 if (it >= NS) {  // the stage is free once the compute warps and the summing helpers are done with it
-                    if (!mbar_wait(&empty_in[s], (it / NS - 1) & 1, 13, 100)) { ok = false; break; }
-                    if (!mbar_wait(&stage_done[s], (it / NS - 1) & 1, 16, 100)) { ok = false; break; }
+                    if (!mbar_wait(prm.wait, &empty_in[s], (it / NS - 1) & 1, 13, 100)) { ok = false; break; }
+                    if (!mbar_wait(prm.wait, &stage_done[s], (it / NS - 1) & 1, 16, 100)) { ok = false; break; }
                 }
                 if (prm.use_tma) {
                     if (htid == 0) {
@@ -481,7 +482,8 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                     if (idx < TT * SPAD) kq[idx] = make_float4(kr[e] * kr[e], kr[e], qr[e], qr[e] * qr[e]);
                 }
                 if (tile > 0) load_kq(t0 - TT);
-                if (!(prm.use_tma && htid == 0)) mbar_arrive(&full_in[s]);
+                // (test hook, as in the forward: the wait for tile skip_tile runs out)
+                if (!(prm.use_tma && htid == 0) && !(it == prm.wait.skip_tile && htid == 1)) mbar_arrive(&full_in[s]);
                 produced = it + 1;
             }
         } else {
@@ -499,7 +501,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
                     // the compute warps finish the segments of a tile from its last steps to its first
                     const int qd = NQ - 1 - step;                 // segment in time order
                     const int prq = flip ? NQ - 1 - qd : qd;      // its physical rows
-                    if (!mbar_wait(&part_full[prq], jt & 1, 14, 100)) { ok = false; break; }
+                    if (!mbar_wait(prm.wait, &part_full[prq], jt & 1, 14, 100)) { ok = false; break; }
                     // dk, dq: add the CTA's channels. Compute thread t holds lane
                     // group j = t % LPC, so the partials of state s = i*LPC + jj
                     // sit at columns jj, jj + LPC, ... of row (u, i).
@@ -577,7 +579,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_bwd_kernel(const __grid_co
             }
         }
         if (!ok && prm.use_tma && htid == 0) {
-            for (int t = max(0, produced - NS); t < produced; ++t) mbar_wait(&full_in[t % NS], (t / NS) & 1, 15);
+            for (int t = max(0, produced - NS); t < produced; ++t) mbar_wait(prm.wait, &full_in[t % NS], (t / NS) & 1, 15);
         }
     }
 }

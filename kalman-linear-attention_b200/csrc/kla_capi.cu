@@ -7,34 +7,19 @@
 #include <mutex>
 
 #include "../../include/kla_b200.h"
-#include "kla_bwd.cuh"
 #include "kla_decode.cuh"
-#include "kla_fwd.cuh"
+#include "kla_launch.cuh"
 #include "kla_rawscan.cuh"
 #include "kla_slab.cuh"
 #include "kla_step.cuh"
 
+// The device's status word (kla_b200_device_status). Kernels get its device address in their
+// parameters (WaitCtl::status): in host code the name below is only a handle.
+static __device__ int g_kla_status = 0;
+
 namespace {
 
 using namespace kla;
-
-#ifndef KLA_NW
-#define KLA_NW 4
-#endif
-constexpr int kNW = KLA_NW;            // compute warps per CTA
-#ifndef KLA_NH
-#define KLA_NH 4
-#endif
-constexpr int kNH = KLA_NH;            // helper warps per CTA
-constexpr int kTT = kCkptInterval;     // steps per tile
-#ifndef KLA_SPT
-#define KLA_SPT 4
-#endif
-constexpr int kSPT = KLA_SPT;          // states per thread
-#ifndef KLA_CH
-#define KLA_CH 1
-#endif
-constexpr int kCH = KLA_CH;            // channels per thread
 
 std::atomic<long long> g_launches{0};
 thread_local cudaError_t g_last_cuda = cudaSuccess;
@@ -120,49 +105,65 @@ int check_t3(const kla_b200_tensor3 &t, size_t esz, bool required) {
     return KLA_B200_OK;
 }
 
-template <typename T, typename TO, int LPC, bool PRIOR>
-int launch_fwd(FwdParams &prm, const kla_b200_fwd_args &a, cudaStream_t st) {
-    using Sh = ScanShape<kSPT, LPC, kCH, kNW, kNH, kTT>;
-    using Sm = FwdSmem<T, kSPT, LPC, kCH, kNW, kNH, kTT>;
-    auto kern = prm.epilogue ? kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, true>
-                             : kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, false>;
-    prm.use_tma = !g_no_tma && make_tile_map<T>(&prm.tm_v, a.v, a.B, a.L, a.M, Sh::kMC, kTT) &&
-                  make_tile_map<T>(&prm.tm_lv, a.lambda_v, a.B, a.L, a.M, Sh::kMC, kTT);
-    if (prm.epilogue)  // z and gate tiles travel like v and lambda_v when they meet the tensor-map rules
-        prm.epi_tma = !g_no_tma && (a.z.ptr == nullptr || make_tile_map<T>(&prm.tm_z, a.z, a.B, a.L, a.M, Sh::kMC, kTT)) &&
-                      (a.gate.ptr == nullptr || make_tile_map<T>(&prm.tm_gate, a.gate, a.B, a.L, a.M, Sh::kMC, kTT));
-    const size_t smem = prm.epilogue ? Sm::kTotal : Sm::kPlain;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sm::kTotal);
+constexpr int kMaxDevices = 64;
+std::mutex g_symbol_mu;
+int *g_status_ptr[kMaxDevices] = {};
+// test hooks (kla_b200_test_hooks): wait limit and the tile whose hand-over the loader leaves incomplete
+std::atomic<unsigned> g_wait_limit_ns{1000000000u};
+std::atomic<int> g_skip_tile{-1};
+
+// Device address of the status word on the current device (looked up on first use), with the current
+// wait settings. Returns a C-ABI status.
+int wait_ctl(WaitCtl *w) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e);
-    dim3 grid((unsigned)((prm.M + Sh::kMC - 1) / Sh::kMC), (unsigned)prm.B);
-    kern<<<grid, Sh::kThreads, smem, st>>>(prm);
+    if (dev < 0 || dev >= kMaxDevices) return KLA_B200_EUNSUPPORTED;
+    {
+        std::lock_guard<std::mutex> lock(g_symbol_mu);
+        if (g_status_ptr[dev] == nullptr) {
+            void *ptr = nullptr;
+            e = cudaGetSymbolAddress(&ptr, g_kla_status);
+            if (e != cudaSuccess) return cuda_fail(e);
+            g_status_ptr[dev] = static_cast<int *>(ptr);
+        }
+        w->status = g_status_ptr[dev];
+    }
+    w->limit_ns = g_wait_limit_ns.load();
+    w->skip_tile = g_skip_tile.load();
+    return KLA_B200_OK;
+}
+
+// Tensor maps of the forward's tiles (box: the CTA's channels x one tile of steps), then the launch.
+template <typename T, typename TO, int LPC, bool PRIOR>
+int prep_fwd(FwdParams &prm, const kla_b200_fwd_args &a, cudaStream_t st) {
+    const int mc = scan_channels_per_cta(LPC);
+    prm.use_tma = !g_no_tma && make_tile_map<T>(&prm.tm_v, a.v, a.B, a.L, a.M, mc, kTT) &&
+                  make_tile_map<T>(&prm.tm_lv, a.lambda_v, a.B, a.L, a.M, mc, kTT);
+    if (prm.epilogue)  // z and gate tiles travel like v and lambda_v when they meet the tensor-map rules
+        prm.epi_tma = !g_no_tma && (a.z.ptr == nullptr || make_tile_map<T>(&prm.tm_z, a.z, a.B, a.L, a.M, mc, kTT)) &&
+                      (a.gate.ptr == nullptr || make_tile_map<T>(&prm.tm_gate, a.gate, a.B, a.L, a.M, mc, kTT));
+    const cudaError_t e = launch_fwd<T, TO, LPC, PRIOR>(prm, st);
     g_launches++;
-    e = cudaGetLastError();
     return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
 }
 
 template <typename T, typename TO, int LPC, bool PRIOR>
-int launch_bwd(BwdParams &prm, const kla_b200_bwd_args &a, cudaStream_t st) {
-    using Sh = ScanShape<kSPT, LPC, kCH, kNW, kNH, kTT>;
-    using Sm = BwdSmem<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT>;
-    auto kern = prm.lv_log_sigma ? kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, true>
-                                 : kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, false>;
-    prm.use_tma = !g_no_tma && make_tile_map<T>(&prm.tm_v, a.v, a.B, a.L, a.M, Sh::kMC, kTT) &&
-                  make_tile_map<T>(&prm.tm_lv, a.lambda_v, a.B, a.L, a.M, Sh::kMC, kTT) &&
-                  make_tile_map<TO>(&prm.tm_dy, a.dy, a.B, a.L, a.M, Sh::kMC, kTT) &&
-                  (a.dy_var.ptr == nullptr || make_tile_map<TO>(&prm.tm_dyv, a.dy_var, a.B, a.L, a.M, Sh::kMC, kTT));
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sm::kTotal);
-    if (e != cudaSuccess) return cuda_fail(e);
-    dim3 grid((unsigned)((prm.M + Sh::kMC - 1) / Sh::kMC), (unsigned)prm.B);
-    kern<<<grid, Sh::kThreads, Sm::kTotal, st>>>(prm);
+int prep_bwd(BwdParams &prm, const kla_b200_bwd_args &a, cudaStream_t st) {
+    const int mc = scan_channels_per_cta(LPC);
+    prm.use_tma = !g_no_tma && make_tile_map<T>(&prm.tm_v, a.v, a.B, a.L, a.M, mc, kTT) &&
+                  make_tile_map<T>(&prm.tm_lv, a.lambda_v, a.B, a.L, a.M, mc, kTT) &&
+                  make_tile_map<TO>(&prm.tm_dy, a.dy, a.B, a.L, a.M, mc, kTT) &&
+                  (a.dy_var.ptr == nullptr || make_tile_map<TO>(&prm.tm_dyv, a.dy_var, a.B, a.L, a.M, mc, kTT));
+    const cudaError_t e = launch_bwd<T, TO, LPC, PRIOR>(prm, st);
     g_launches++;
-    e = cudaGetLastError();
     return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
 }
 
 template <typename T, typename TO, int LPC, bool PRIOR>
 int launch_step(const StepParams &prm, cudaStream_t st) {
     const long long threads = (long long)prm.B * prm.M * LPC;
+    if ((threads + 127) / 128 > 0x7fffffffll) return KLA_B200_EUNSUPPORTED;  // grid.x limit
     const unsigned blocks = (unsigned)((threads + 127) / 128);
     kla_step_kernel<T, TO, LPC, PRIOR><<<blocks, 128, 0, st>>>(prm);
     g_launches++;
@@ -198,10 +199,10 @@ int launch_step(const StepParams &prm, cudaStream_t st) {
     } while (0)
 
 int dispatch_fwd(int din, int dout, bool prior, int lpc, FwdParams &prm, const kla_b200_fwd_args &a, cudaStream_t st) {
-    KLA_DISPATCH(launch_fwd, din, dout, prior, lpc, prm, a, st);
+    KLA_DISPATCH(prep_fwd, din, dout, prior, lpc, prm, a, st);
 }
 int dispatch_bwd(int din, int dout, bool prior, int lpc, BwdParams &prm, const kla_b200_bwd_args &a, cudaStream_t st) {
-    KLA_DISPATCH(launch_bwd, din, dout, prior, lpc, prm, a, st);
+    KLA_DISPATCH(prep_bwd, din, dout, prior, lpc, prm, a, st);
 }
 template <typename T, typename TO, int LPC, bool PRIOR>
 int launch_slab(const SlabParams &prm, bool adjoint, cudaStream_t st) {
@@ -222,6 +223,7 @@ int dispatch_step(int din, int dout, bool prior, int lpc, const StepParams &prm,
 template <typename T, typename TO, int LPC, bool PRIOR>
 int launch_step_layer(const StepLayerParams &prm, cudaStream_t st) {
     const long long threads = (long long)prm.B * prm.M * LPC;
+    if ((threads + 127) / 128 > 0x7fffffffll) return KLA_B200_EUNSUPPORTED;  // grid.x limit
     const unsigned blocks = (unsigned)((threads + 127) / 128);
     kla_step_layer_kernel<T, TO, LPC, PRIOR><<<blocks, 128, 0, st>>>(prm);
     g_launches++;
@@ -266,6 +268,8 @@ int launch_rawscan(const kla_b200_rawscan_args *a, void *stream, bool takes_stat
         tma = tma && make_tile_map<float>(&prm.tm_out[k], t, a->B, a->L, a->N, kRawLC, kRawTT);
     }
     prm.use_tma = tma;
+    if (int rc = wait_ctl(&prm.wait)) return rc;
+    prm.wait.skip_tile = -1;  // the hook is for the fused scan kernels
     auto kern = kla_rawscan_kernel<Op>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RawSmem<Op>::kTotal);
     if (e != cudaSuccess) return cuda_fail(e);
@@ -285,7 +289,13 @@ int64_t kla_b200_ckpt_interval(void) { return kCkptInterval; }
 size_t kla_b200_ckpt_bytes(int64_t B, int64_t L, int64_t M, int64_t S) {
     if (B <= 0 || L <= 0 || M <= 0 || S <= 0) return 0;
     const int64_t nt = (L + kCkptInterval - 1) / kCkptInterval;
-    return (size_t)B * (size_t)nt * (size_t)M * (size_t)S * sizeof(float2);
+    // saturating product: a size that does not fit size_t reads as SIZE_MAX, never as a small number
+    size_t n = sizeof(float2);
+    for (const int64_t f : {B, nt, M, S}) {
+        if (n > SIZE_MAX / (size_t)f) return SIZE_MAX;
+        n *= (size_t)f;
+    }
+    return n;
 }
 
 int kla_b200_scan_fwd(const kla_b200_fwd_args *a, void *stream) {
@@ -329,6 +339,7 @@ int kla_b200_scan_fwd(const kla_b200_fwd_args *a, void *stream) {
             if (has_gate) { prm.gate = t3(a->gate); prm.gate_act = a->gate_activation; }
         }
     }
+    if ((rc = wait_ctl(&prm.wait))) return rc;
     prm.vec_y = a->out_dtype == KLA_B200_F32 ? vec2_ok<float>(a->y) : vec2_ok<__nv_bfloat16>(a->y);
     prm.vec_yv = a->out_dtype == KLA_B200_F32 ? vec2_ok<float>(a->y_var) : vec2_ok<__nv_bfloat16>(a->y_var);
     return dispatch_fwd(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc_for(a->S), prm, *a, st);
@@ -385,6 +396,7 @@ int kla_b200_scan_bwd(const kla_b200_bwd_args *a, void *stream) {
     prm.dlam_fin = a->dlam_fin; prm.deta_fin = a->deta_fin;
     prm.dk = a->dk; prm.dq = a->dq; prm.da = a->da; prm.dp = a->dp;
     prm.dlam0 = a->dlam0; prm.deta0 = a->deta0;
+    if ((rc = wait_ctl(&prm.wait))) return rc;
     prm.vec_dv = a->in_dtype == KLA_B200_F32 ? vec2_ok<float>(a->dv) : vec2_ok<__nv_bfloat16>(a->dv);
     prm.vec_dlv = a->in_dtype == KLA_B200_F32 ? vec2_ok<float>(a->dlambda_v) : vec2_ok<__nv_bfloat16>(a->dlambda_v);
     return dispatch_bwd(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc_for(a->S), prm, *a, st);
@@ -432,6 +444,8 @@ int kla_b200_step(const kla_b200_step_args *a, void *stream) {
     prm.v_sb = a->v_stride_b; prm.lv_sb = a->lambda_v_stride_b; prm.k_sb = a->k_stride_b; prm.q_sb = a->q_stride_b;
     prm.a = a->a; prm.p = a->p; prm.lam = a->lam; prm.eta = a->eta;
     prm.y = a->y; prm.yv = a->y_var; prm.lam_out = a->lam_out; prm.eta_out = a->eta_out;
+    prm.vec = a->S % 4 == 0 && aligned(a->lam, 16) && aligned(a->eta, 16) && aligned(a->a, 16) && aligned(a->p, 16) &&
+              aligned(a->lam_out, 16) && aligned(a->eta_out, 16);
     int lpc = 1;
     while (lpc * 4 < a->S) lpc *= 2;
     return dispatch_step(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc, prm, static_cast<cudaStream_t>(stream));
@@ -514,6 +528,8 @@ int kla_b200_step_layer(const kla_b200_step_layer_args *a, void *stream) {
     prm.skip = a->lambda_skip_len != 0 ? a->lambda_skip : nullptr; prm.skip_len = a->lambda_skip_len;
     prm.obs_var_min = a->obs_var_min; prm.obs_var_max = a->obs_var_max; prm.clip = a->clip_value;
     prm.qk_norm = a->qk_norm; prm.gate_act = a->gate_activation;
+    prm.vec = a->S % 4 == 0 && aligned(a->lam, 16) && aligned(a->eta, 16) && aligned(a->a, 16) && aligned(a->p, 16) &&
+              aligned(a->lam_out, 16) && aligned(a->eta_out, 16);
     int lpc = 1;
     while (lpc * 4 < a->S) lpc *= 2;
     return dispatch_step_layer(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc, prm, static_cast<cudaStream_t>(stream));
@@ -548,7 +564,6 @@ int64_t kla_b200_launch_count(void) { return g_launches.load(); }
 static __device__ __align__(256) unsigned char g_static_ckpt[KLA_B200_STATIC_CKPT_BYTES];
 
 namespace {
-constexpr int kMaxDevices = 64;
 std::mutex g_static_mu;
 void *g_static_ckpt_ptr[kMaxDevices] = {};
 
@@ -608,6 +623,13 @@ int kla_b200_device_status(int *status) {
         e = cudaMemcpyToSymbol(g_kla_status, &zero, sizeof(int));
         if (e != cudaSuccess) return cuda_fail(e);
     }
+    return KLA_B200_OK;
+}
+
+int kla_b200_test_hooks(int64_t wait_limit_ns, int32_t skip_tile) {
+    if (wait_limit_ns < 0 || wait_limit_ns > 4000000000ll) return KLA_B200_EINVAL;
+    g_wait_limit_ns.store(wait_limit_ns == 0 ? 1000000000u : (unsigned)wait_limit_ns);
+    g_skip_tile.store(skip_tile < 0 ? -1 : skip_tile);
     return KLA_B200_OK;
 }
 

@@ -45,6 +45,14 @@ constexpr int kCkptInterval = 16;   // steps between checkpoints of the filter s
 // that ran out (kStatusWait | site). Read back by kla_b200_device_status().
 constexpr int kStatusWait = 0x100;
 
+// What a kernel needs for its bounded waits; part of every kernel's parameters.
+struct WaitCtl {
+    int *status;        // the device's status word (one per device, owned by the library)
+    unsigned limit_ns;  // a wait gives up after about this long (1e9 in normal operation)
+    int skip_tile;      // test hook: the loader leaves out one arrive for this tile, so that the wait
+                        // for it runs out; -1 in normal operation
+};
+
 struct Tensor3 {
     void *ptr;
     long long sb, st;  // batch and time strides, in elements
@@ -204,8 +212,6 @@ __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { retu
 // objects in shared memory; tile loads use the tensor-map form of the bulk
 // async copy (TMA), which signals the same mbarrier with its byte count.
 
-__device__ int g_kla_status = 0;
-
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -237,17 +243,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 }
 // Bounded wait. A waiting warp sleeps between polls (sleep_ns each) so that it
 // does not take issue slots from the warps that are computing on the same
-// scheduler. After about a second of polling it gives up, records where in
-// g_kla_status and returns false; the caller then leaves its loop so that the
-// CTA ends instead of hanging the device.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int site, unsigned sleep_ns = 100) {
+// scheduler. After about WaitCtl::limit_ns of polling (a second) it gives up,
+// records where in the device's status word and returns false; the caller then
+// leaves its loop so that the CTA ends instead of hanging the device.
+__device__ __forceinline__ bool mbar_wait(const WaitCtl &w, uint64_t *bar, uint32_t parity, int site,
+                                          unsigned sleep_ns = 100) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint32_t limit = 1000000000u / (sleep_ns + 100);
+    const uint32_t limit = w.limit_ns / (sleep_ns + 100);
     for (uint32_t i = 0; i < limit; ++i) {
         __nanosleep(sleep_ns);
         if (mbar_try_wait(bar, parity)) return true;
     }
-    atomicCAS(&g_kla_status, 0, kStatusWait | site);
+    atomicCAS(w.status, 0, kStatusWait | site);
     return false;
 }
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA)

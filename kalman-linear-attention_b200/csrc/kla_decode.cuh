@@ -137,6 +137,7 @@ struct StepLayerParams {
     int skip_len;
     float obs_var_min, obs_var_max, clip;  // obs_var_max <= 0: none; clip <= 0: none
     int qk_norm, gate_act;
+    int vec;  // as StepParams::vec
 };
 
 // One thread per (b, m, group of 4 consecutive states), LPC adjacent lanes per channel, as in kla_step_kernel.
@@ -190,9 +191,13 @@ __global__ void __launch_bounds__(128) kla_step_layer_kernel(const StepLayerPara
             to_f32<T>(static_cast<const T *>(prm.ls)[(long long)b * prm.ls_sb + m]), prm.obs_var_min, prm.obs_var_max);
         const float vl = to_f32<T>(static_cast<const T *>(prm.v)[(long long)b * prm.v_sb + m]) * lv;
         const long long ms0 = (long long)m * S + j * 4, bms0 = ((long long)b * M + m) * S + j * 4;
-        const bool vec = (S % 4) == 0;
+        // lanes wholly past the row (j * 4 >= S, e.g. S = 12 with LPC = 4) hold padding chains and touch no memory
+        const bool vec = prm.vec != 0, lane_live = j * 4 < S;
         float lamv[4], etav[4], av[4], pv[4], lo[4], eo[4];
-        if (vec) {
+        if (!lane_live) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { lamv[i] = 1.0f; etav[i] = 0.0f; av[i] = 0.0f; pv[i] = 1.0f; }
+        } else if (vec) {
             const float4 l4 = *reinterpret_cast<const float4 *>(prm.lam + bms0);
             const float4 e4 = *reinterpret_cast<const float4 *>(prm.eta + bms0);
             const float4 a4 = *reinterpret_cast<const float4 *>(prm.a + ms0);
@@ -234,7 +239,9 @@ __global__ void __launch_bounds__(128) kla_step_layer_kernel(const StepLayerPara
             lo[i] = lam;
             eo[i] = eta;
         }
-        if (vec) {
+        if (!lane_live) {
+            // padding lane: nothing to store
+        } else if (vec) {
             *reinterpret_cast<float4 *>(prm.lam_out + bms0) = make_float4(lo[0], lo[1], lo[2], lo[3]);
             *reinterpret_cast<float4 *>(prm.eta_out + bms0) = make_float4(eo[0], eo[1], eo[2], eo[3]);
         } else {

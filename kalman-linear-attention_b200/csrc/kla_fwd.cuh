@@ -56,6 +56,7 @@ struct alignas(64) FwdParams {
     Tensor3 z, gate;
     const float *skip;
     int skip_len, gate_act, epilogue, epi_tma;
+    WaitCtl wait;
     alignas(64) CUtensorMap tm_z, tm_gate;  // maps of the epilogue operands, like tm_v; valid when epi_tma
 };
 
@@ -276,7 +277,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         for (int tile = 0; tile < NT; ++tile) {
             const int s = tile % NS, o = tile % NO;
             const int t0 = tile * TT;
-            if (!mbar_wait(&full_in[s], (tile / NS) & 1, 1)) break;
+            if (!mbar_wait(prm.wait, &full_in[s], (tile / NS) & 1, 1)) break;
             if (pro) {  // this warp's channels of the tile: log-variance -> precision, float32
                 const T *raw = lstage(s) + warp * Sh::kCPW;
                 float *lf = lfstage(s) + warp * Sh::kCPW;
@@ -287,7 +288,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                 fence_proxy_async();  // these plain stores are ordered before the bulk copy that refills the stage
                 __syncwarp();
             }
-            if (tile >= NO && !mbar_wait(&empty_out[o], (tile / NO - 1) & 1, 2)) break;
+            if (tile >= NO && !mbar_wait(prm.wait, &empty_out[o], (tile / NO - 1) & 1, 2)) break;
             if (ck != nullptr) {
 #pragma unroll
                 for (int ci = 0; ci < CH; ++ci)
@@ -355,7 +356,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         const int htid = tid - Sh::kCompute;
         const int hlane = htid & 31;
         constexpr uint32_t kTileBytes = sizeof(T) * TT * MC;
-        int produced = 0;
+        int produced = 0, epi_issued = 0;  // tiles whose input / epilogue copies have been issued
         bool ok = true;
         if (htid < kProducers) {
             // ---- loaders: TMA tiles of v, lambda_v and the (k, q) pairs, NS tiles ahead
@@ -379,7 +380,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             load_kq(0);
             for (int it = 0; it < NT; ++it) {
                 const int s = it % NS, t0 = it * TT;
-                if (it >= NS && !mbar_wait(&empty_in[s], (it / NS - 1) & 1, 3, 100)) { ok = false; break; }
+                if (it >= NS && !mbar_wait(prm.wait, &empty_in[s], (it / NS - 1) & 1, 3, 100)) { ok = false; break; }
                 if (prm.use_tma) {
                     if (htid == 0) {
                         mbar_arrive_expect_tx(&full_in[s], 2 * kTileBytes);
@@ -401,11 +402,12 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                     }
                 }
                 if (it + 1 < NT) load_kq(t0 + TT);
-                if (!(prm.use_tma && htid == 0)) mbar_arrive(&full_in[s]);
+                // (test hook: one loader thread leaves out its arrive for tile skip_tile, so the wait for that tile runs out)
+                if (!(prm.use_tma && htid == 0) && !(it == prm.wait.skip_tile && htid == 1)) mbar_arrive(&full_in[s]);
                 produced = it + 1;
                 if constexpr (EPI) {  // this tile's z and gate, for the drainers
                     const int e = it % NE;
-                    if (it >= NE && !mbar_wait(&epi_empty[e], (it / NE - 1) & 1, 6, 100)) { ok = false; break; }
+                    if (it >= NE && !mbar_wait(prm.wait, &epi_empty[e], (it / NE - 1) & 1, 6, 100)) { ok = false; break; }
                     const bool has_z = prm.z.ptr != nullptr, has_g = prm.gate.ptr != nullptr;
                     if (prm.epi_tma) {
                         if (htid == 0) {
@@ -422,6 +424,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                                 gstage(e), static_cast<const T *>(prm.gate.ptr) + (long long)b * prm.gate.sb, prm.gate.st, t0, L, m_cta, M, htid);
                     }
                     if (!(prm.epi_tma && htid == 0)) mbar_arrive(&epi_full[e]);
+                    epi_issued = it + 1;
                 }
             }
         } else {
@@ -431,10 +434,10 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             TO *yvb = static_cast<TO *>(prm.yv.ptr) + (long long)b * prm.yv.sb;
             for (int jt = 0; jt < NT; ++jt) {
                 const int o = jt % NO, t0 = jt * TT;
-                if (!mbar_wait(&full_out[o], (jt / NO) & 1, 4, 100)) { ok = false; break; }
+                if (!mbar_wait(prm.wait, &full_out[o], (jt / NO) & 1, 4, 100)) { ok = false; break; }
                 if constexpr (EPI) {
                     const int e = jt % NE;
-                    if (!mbar_wait(&epi_full[e], (jt / NE) & 1, 7, 100)) { ok = false; break; }
+                    if (!mbar_wait(prm.wait, &epi_full[e], (jt / NE) & 1, 7, 100)) { ok = false; break; }
                     const T *zs = prm.z.ptr ? zstage(e) : nullptr, *gs = prm.gate.ptr ? gstage(e) : nullptr;
                     output_pass<TO, LPC, MC, MCP, TT, kDrainers>(
                         ystage(o), yb + (long long)t0 * prm.y.st, prm.y.st, prm.vec_y,
@@ -467,10 +470,11 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         }
         // Leaving early (a wait ran out): do not end the CTA with bulk copies
         // still in flight into its shared memory.
-        if (!ok && prm.use_tma && htid == 0) {
-            for (int t = max(0, produced - NS); t < produced; ++t) mbar_wait(&full_in[t % NS], (t / NS) & 1, 5);
-            if (EPI && prm.epi_tma)
-                for (int t = max(0, produced - NE); t < produced; ++t) mbar_wait(&epi_full[t % NE], (t / NE) & 1, 8);
+        if (!ok && htid == 0) {
+            if (prm.use_tma)
+                for (int t = max(0, produced - NS); t < produced; ++t) mbar_wait(prm.wait, &full_in[t % NS], (t / NS) & 1, 5);
+            if (EPI && prm.epi_tma)  // the epilogue tiles travel by TMA whether or not v and lambda_v do
+                for (int t = max(0, epi_issued - NE); t < epi_issued; ++t) mbar_wait(prm.wait, &epi_full[t % NE], (t / NE) & 1, 8);
         }
     }
 }

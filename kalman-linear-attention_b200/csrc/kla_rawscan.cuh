@@ -38,6 +38,7 @@ struct alignas(64) RawParams {
     float *dstate0;       // [B, N] or nullptr
     int B, L, N, NT;
     int use_tma;
+    WaitCtl wait;
 };
 
 // TMA store of a shared-memory tile into a rank-3 tensor map, tracked by the bulk-group mechanism
@@ -169,7 +170,7 @@ __global__ void __launch_bounds__(kRawLC + 32) kla_rawscan_kernel(const __grid_c
             const int tile = Op::REV ? NT - 1 - ti : ti;
             const int t0 = tile * TT, n = min(TT, L - t0);
             const int s = ti % NSI, o = ti % NSO;
-            if (!mbar_wait(&full_in[s], (ti / NSI) & 1, 21)) break;
+            if (!mbar_wait(prm.wait, &full_in[s], (ti / NSI) & 1, 21)) break;
             auto one_step = [&](int u) {
                 float x[NIN], y[NOUT];
 #pragma unroll
@@ -216,7 +217,7 @@ __global__ void __launch_bounds__(kRawLC + 32) kla_rawscan_kernel(const __grid_c
         for (int ti = 0; ti < NT; ++ti) {
             const int tile = Op::REV ? NT - 1 - ti : ti;
             const int t0 = tile * TT, s = ti % NSI;
-            if (ti >= NSI && !mbar_wait(&empty_in[s], (ti / NSI - 1) & 1, 22, 50)) { ok = false; break; }
+            if (ti >= NSI && !mbar_wait(prm.wait, &empty_in[s], (ti / NSI - 1) & 1, 22, 50)) { ok = false; break; }
             if (tma) {
                 if (lane == 0) {
                     constexpr uint32_t kBytes = sizeof(float) * LC * (NIN * TT + (Op::HALO >= 0 ? 1 : 0));
@@ -242,7 +243,7 @@ __global__ void __launch_bounds__(kRawLC + 32) kla_rawscan_kernel(const __grid_c
         }
         // Leaving early (a wait ran out): do not end the CTA with bulk copies in flight into its shared memory.
         if (!ok && tma && lane == 0)
-            for (int t = max(0, produced - NSI); t < produced; ++t) mbar_wait(&full_in[t % NSI], (t / NSI) & 1, 23);
+            for (int t = max(0, produced - NSI); t < produced; ++t) mbar_wait(prm.wait, &full_in[t % NSI], (t / NSI) & 1, 23);
     }
 }
 

@@ -1,0 +1,82 @@
+// Definitions and explicit instantiations of the scan kernels' launchers
+// (kla_launch.cuh). The build compiles this file once per slice:
+//   KLA_INST_KIND   0 forward, 1 backward
+//   KLA_INST_DT     0 (float, float), 1 (bfloat16, float), 2 (bfloat16, bfloat16)
+//   KLA_INST_LPCS   0 lanes per channel 1, 2, 4;  1 lanes per channel 8, 16, 32
+// Without those macros it holds every instantiation.
+#include "kla_launch.cuh"
+
+namespace kla {
+
+template <typename T, typename TO, int LPC, bool PRIOR>
+cudaError_t launch_fwd(const FwdParams &prm, cudaStream_t st) {
+    using Sh = ScanShape<kSPT, LPC, kCH, kNW, kNH, kTT>;
+    using Sm = FwdSmem<T, kSPT, LPC, kCH, kNW, kNH, kTT>;
+    auto kern = prm.epilogue ? kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, true>
+                             : kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, false>;
+    const size_t smem = prm.epilogue ? Sm::kTotal : Sm::kPlain;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sm::kTotal);
+    if (e != cudaSuccess) return e;
+    dim3 grid((unsigned)((prm.M + Sh::kMC - 1) / Sh::kMC), (unsigned)prm.B);
+    kern<<<grid, Sh::kThreads, smem, st>>>(prm);
+    return cudaGetLastError();
+}
+
+template <typename T, typename TO, int LPC, bool PRIOR>
+cudaError_t launch_bwd(const BwdParams &prm, cudaStream_t st) {
+    using Sh = ScanShape<kSPT, LPC, kCH, kNW, kNH, kTT>;
+    using Sm = BwdSmem<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT>;
+    auto kern = prm.lv_log_sigma ? kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, true>
+                                 : kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, false>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sm::kTotal);
+    if (e != cudaSuccess) return e;
+    dim3 grid((unsigned)((prm.M + Sh::kMC - 1) / Sh::kMC), (unsigned)prm.B);
+    kern<<<grid, Sh::kThreads, Sm::kTotal, st>>>(prm);
+    return cudaGetLastError();
+}
+
+#define KLA_INST_ONE(FN, PARAMS, T, TO, LPC)                                         \
+    template cudaError_t FN<T, TO, LPC, false>(const PARAMS &, cudaStream_t);        \
+    template cudaError_t FN<T, TO, LPC, true>(const PARAMS &, cudaStream_t);
+#define KLA_INST_LOW(FN, PARAMS, T, TO) \
+    KLA_INST_ONE(FN, PARAMS, T, TO, 1) KLA_INST_ONE(FN, PARAMS, T, TO, 2) KLA_INST_ONE(FN, PARAMS, T, TO, 4)
+#define KLA_INST_HIGH(FN, PARAMS, T, TO) \
+    KLA_INST_ONE(FN, PARAMS, T, TO, 8) KLA_INST_ONE(FN, PARAMS, T, TO, 16) KLA_INST_ONE(FN, PARAMS, T, TO, 32)
+
+#if !defined(KLA_INST_LPCS) || KLA_INST_LPCS == 0
+#define KLA_INST_L(FN, PARAMS, T, TO) KLA_INST_LOW(FN, PARAMS, T, TO)
+#else
+#define KLA_INST_L(FN, PARAMS, T, TO)
+#endif
+#if !defined(KLA_INST_LPCS) || KLA_INST_LPCS == 1
+#define KLA_INST_H(FN, PARAMS, T, TO) KLA_INST_HIGH(FN, PARAMS, T, TO)
+#else
+#define KLA_INST_H(FN, PARAMS, T, TO)
+#endif
+#define KLA_INST_DTYPE(FN, PARAMS, T, TO) KLA_INST_L(FN, PARAMS, T, TO) KLA_INST_H(FN, PARAMS, T, TO)
+
+#if !defined(KLA_INST_DT) || KLA_INST_DT == 0
+#define KLA_INST_D0(FN, PARAMS) KLA_INST_DTYPE(FN, PARAMS, float, float)
+#else
+#define KLA_INST_D0(FN, PARAMS)
+#endif
+#if !defined(KLA_INST_DT) || KLA_INST_DT == 1
+#define KLA_INST_D1(FN, PARAMS) KLA_INST_DTYPE(FN, PARAMS, __nv_bfloat16, float)
+#else
+#define KLA_INST_D1(FN, PARAMS)
+#endif
+#if !defined(KLA_INST_DT) || KLA_INST_DT == 2
+#define KLA_INST_D2(FN, PARAMS) KLA_INST_DTYPE(FN, PARAMS, __nv_bfloat16, __nv_bfloat16)
+#else
+#define KLA_INST_D2(FN, PARAMS)
+#endif
+#define KLA_INST_ALL(FN, PARAMS) KLA_INST_D0(FN, PARAMS) KLA_INST_D1(FN, PARAMS) KLA_INST_D2(FN, PARAMS)
+
+#if !defined(KLA_INST_KIND) || KLA_INST_KIND == 0
+KLA_INST_ALL(launch_fwd, FwdParams)
+#endif
+#if !defined(KLA_INST_KIND) || KLA_INST_KIND == 1
+KLA_INST_ALL(launch_bwd, BwdParams)
+#endif
+
+}  // namespace kla

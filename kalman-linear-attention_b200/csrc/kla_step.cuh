@@ -19,6 +19,7 @@ struct StepParams {
     const float *a, *p, *lam, *eta;
     void *y, *yv;
     float *lam_out, *eta_out;
+    int vec;  // S % 4 == 0 and lam, eta, a, p, lam_out, eta_out 16-byte aligned: a lane's four states move as one vector
 };
 
 template <typename T, typename TO, int LPC, bool PRIOR>
@@ -37,10 +38,15 @@ __global__ void __launch_bounds__(128) kla_step_kernel(const StepParams prm) {
         const T *kb = static_cast<const T *>(prm.k) + (long long)b * prm.k_sb;
         const T *qb = static_cast<const T *>(prm.q) + (long long)b * prm.q_sb;
         const long long ms0 = (long long)m * S + j * 4, bms0 = ((long long)b * M + m) * S + j * 4;
-        // one lane's four states as 16-byte vectors when the row length allows it
-        const bool vec = (S % 4) == 0;
+        // One lane's four states as 16-byte vectors when the row length and the pointers allow it.
+        // LPC is a power of two, so for S = 12, 20, 24, ... some lanes of a channel lie wholly past
+        // the row (j * 4 >= S): they hold padding chains and touch no memory.
+        const bool vec = prm.vec != 0, lane_live = j * 4 < S;
         float lamv[4], etav[4], av[4], pv[4], lo[4], eo[4];
-        if (vec) {
+        if (!lane_live) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { lamv[i] = 1.0f; etav[i] = 0.0f; av[i] = 0.0f; pv[i] = 1.0f; }
+        } else if (vec) {
             const float4 l4 = *reinterpret_cast<const float4 *>(prm.lam + bms0);
             const float4 e4 = *reinterpret_cast<const float4 *>(prm.eta + bms0);
             const float4 a4 = *reinterpret_cast<const float4 *>(prm.a + ms0);
@@ -84,7 +90,9 @@ __global__ void __launch_bounds__(128) kla_step_kernel(const StepParams prm) {
             lo[i] = lam;
             eo[i] = eta;
         }
-        if (vec) {
+        if (!lane_live) {
+            // padding lane: nothing to store
+        } else if (vec) {
             *reinterpret_cast<float4 *>(prm.lam_out + bms0) = make_float4(lo[0], lo[1], lo[2], lo[3]);
             *reinterpret_cast<float4 *>(prm.eta_out + bms0) = make_float4(eo[0], eo[1], eo[2], eo[3]);
         } else {

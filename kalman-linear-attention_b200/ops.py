@@ -198,6 +198,7 @@ class _KLAScanB200(torch.autograd.Function):
         return y, y_var, lam_fin, eta_fin
 
     @staticmethod
+    @torch.autograd.function.once_differentiable  # the hand-written gradients have no graph: a double backward raises
     def backward(ctx, dy, dy_var, dlam_fin, deta_fin):
         v, lambda_v, k, q, a, p, lam0, eta0, ckpt = ctx.saved_tensors
         B, L, M = v.shape
@@ -362,7 +363,11 @@ def kla_step_b200(
 
     ``inplace=True`` updates the state tensors where they are (they must be
     float32 and contiguous) instead of allocating new ones. When a gradient is
-    required the step is run as a length-1 scan, which has a backward.
+    required the step is run as a length-1 scan, which has a backward. The two
+    routes differ where the reference's own ``kla_step`` and ``kla_scan`` differ:
+    the step kernel floors ``phi`` at 1e-12 and clamps the variance
+    (kla_ops.py:310-312, 323), the scan leaves ``phi`` unfloored (kla_ops.py:238);
+    the values agree except for keys that are zero to within 1e-6.
     """
     _require_device(v)
     if v.dim() != 2 or k.dim() != 2:

@@ -61,6 +61,7 @@ class _MobiusScanB200(torch.autograd.Function):
         return lam
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, dlam):
         A, B, C, D, lam, *rest = ctx.saved_tensors
         lam0 = rest[0] if ctx.has_lam0 else None
@@ -81,6 +82,7 @@ class _AffineScanB200(torch.autograd.Function):
         return eta
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, deta):
         alpha, eta = ctx.saved_tensors
         deta = deta.contiguous()

@@ -154,6 +154,7 @@ class _SeqShardedScan(torch.autograd.Function):
         return y, y_var, lam_out, eta_out
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, dy, dy_var, dlam_fin, deta_fin):
         v, lambda_v, k, q, a, p, lam_in, eta_in, ckpt, lam_out, eta_out = ctx.saved_tensors
         group, od = ctx.group, ctx.out_dtype

@@ -18,6 +18,13 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu)")
 
 
+def reference_src() -> str:
+    """Directory that holds the reference package ``kla``: ``$KLA_REFERENCE_SRC`` when set, else the copy
+    ``baseline/install_reference.py`` leaves under ``baseline/_ref``; "" when neither exists (tests then skip)."""
+    cand = os.environ.get("KLA_REFERENCE_SRC") or os.path.join(ROOT, "baseline", "_ref")
+    return cand if os.path.isfile(os.path.join(cand, "kla", "__init__.py")) else ""
+
+
 def golden_names():
     return sorted(
         os.path.splitext(os.path.basename(p))[0]

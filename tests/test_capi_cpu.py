@@ -107,6 +107,31 @@ def test_new_entry_points_reject_bad_arguments_without_cuda(L):
     assert lib.kla_b200_launch_count() == 0
 
 
+def test_sizes_that_overflow_are_refused_not_wrapped(L):
+    lib = L.load()
+    size_max = ctypes.c_size_t(-1).value
+    # 2^66 bytes: the product must saturate, not wrap to a small number
+    assert lib.kla_b200_ckpt_bytes(1, 1 << 30, 1 << 30, 128) == size_max
+    assert lib.kla_b200_ckpt_bytes(65535, 1 << 30, 1 << 30, 128) == size_max
+    buf = (ctypes.c_float * 64)()
+    ptr = ctypes.addressof(buf)
+    a = L.FwdArgs(B=1, L=1 << 30, M=1 << 30, S=128)
+    out = ctypes.c_void_p()
+    assert lib.kla_b200_scan_fwd_static(ctypes.byref(a), None, ctypes.byref(out)) == 5  # too big for the built-in scratch
+    assert out.value is None
+    # a decode step whose grid would not fit 31 bits is refused instead of running a truncated grid
+    big = dict(B=65535, M=1 << 30, S=128, in_dtype=0, out_dtype=0)
+    s_args = L.StepArgs(v=ptr, lambda_v=ptr, k=ptr, q=ptr, a=ptr, p=ptr, lam=ptr, eta=ptr, y=ptr, y_var=ptr,
+                        lam_out=ptr, eta_out=ptr, **big)
+    assert lib.kla_b200_step(ctypes.byref(s_args), None) == 2
+    l_args = L.StepLayerArgs(v=ptr, log_sigma_v=ptr, k=ptr, q=ptr, a=ptr, p=ptr, lam=ptr, eta=ptr, y=ptr, y_var=ptr,
+                             lam_out=ptr, eta_out=ptr, **big)
+    assert lib.kla_b200_step_layer(ctypes.byref(l_args), None) == 2
+    assert lib.kla_b200_test_hooks(-1, 0) == 1
+    assert lib.kla_b200_test_hooks(0, -1) == 0
+    assert lib.kla_b200_launch_count() == 0
+
+
 def test_error_text_and_exception_mapping(L):
     lib = L.load()
     assert lib.kla_b200_strerror(0) == b"ok"

@@ -12,11 +12,12 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(HERE))
 import kla_b200  # noqa: E402
+from conftest import reference_src  # noqa: E402
 from importlib import import_module  # noqa: E402
 
 decode = import_module("kalman-linear-attention_b200.decode")
 CASES = sorted(os.path.basename(p)[7:-4] for p in glob.glob(os.path.join(HERE, "golden", "decode_*.npz")))
-REF_SRC = os.environ.get("KLA_REFERENCE_SRC", "/root/reference/src")  # the reference package, when it is on this machine
+REF_SRC = reference_src()  # the directory holding the reference package `kla`, or "" when there is none here
 needs_ref = pytest.mark.skipif(not os.path.isdir(REF_SRC), reason="reference package not present")
 
 

@@ -10,13 +10,13 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import load_golden
+from conftest import load_golden, reference_src
 from oracle import kla_oracle as O
 
 import kla_b200
 
 ops = importlib.import_module("kalman-linear-attention_b200.ops")
-REF_SRC = os.environ.get("KLA_REFERENCE_SRC", "/root/reference/src")  # the reference package, when it is on this machine
+REF_SRC = reference_src()  # the directory holding the reference package `kla`, or "" when there is none here
 INPUTS = ("v", "lambda_v", "k", "q", "a", "p")
 
 

@@ -227,12 +227,17 @@ def test_bf16_io(kb, out_dtype):
     y, y_var, st, grads = run_gpu(kb, g, state=True, dtype=torch.bfloat16, out_dtype=out_dtype)
     assert y.dtype == (out_dtype or torch.float32)
     assert grads[0].dtype == torch.bfloat16 and grads[2].dtype == torch.bfloat16
-    tol = dict(rtol=2e-2, atol=2e-2)
-    torch.testing.assert_close(y.double().cpu(), torch.tensor(f.y), **tol)
-    torch.testing.assert_close(y_var.double().cpu(), torch.tensor(f.y_var), **tol)
+    # rtol 2e-2 as stated for bfloat16 I/O; the absolute term is only the float32 noise of a sum whose terms
+    # cancel (1e-5 of the tensor's scale), not a bfloat16 allowance
+    def within(got, ref, what):
+        r = ratio(got, ref, rtol=2e-2, atol=1e-5 * max(1.0, float(np.abs(ref).max())))
+        assert r <= 1.0, f"{what}: {r:.2f}x of rtol 2e-2"
+
+    within(y, f.y, "y")
+    within(y_var, f.y_var, "y_var")
     torch.testing.assert_close(st.lam.double().cpu(), torch.tensor(f.lam), rtol=1e-4, atol=1e-5)
     for n, gr, ref in zip(b._fields, grads, b):
-        assert rel_err(gr, ref) < 2e-2, f"{n}: {rel_err(gr, ref):.2e}"
+        within(gr, ref, n)
 
 
 def test_step_kernel_matches_golden(kb):
@@ -244,6 +249,47 @@ def test_step_kernel_matches_golden(kb):
                                         kb.KLAState(t("lam"), t("eta")), decode_from_prior=prior)
         assert ratio(y, g["y" + tag]) <= 1 and ratio(y_var, g["y_var" + tag]) <= 1
         assert ratio(st.lam, g["lam_out" + tag]) <= 1 and ratio(st.eta, g["eta_out" + tag]) <= 1
+
+
+@pytest.mark.parametrize("S", [12, 20, 24, 40, 48, 96])
+@pytest.mark.parametrize("inplace", [False, True])
+def test_step_kernel_rows_that_do_not_fill_their_lanes(kb, S, inplace):
+    """d_state a multiple of 4 that is not 4 x a power of two: some lanes of a channel own no state at all. They
+    must neither read nor write: the state sits between guard rows that have to come back untouched, and every
+    row must match the oracle (a stray predict-only write would land on the next (b, m) row)."""
+    B, M = 3, 5
+    rng = np.random.default_rng(S)
+    f32 = lambda x: np.asarray(x, np.float32)
+    v, lv = f32(rng.standard_normal((B, M))), f32(0.5 + rng.random((B, M)))
+    k, q = f32(rng.standard_normal((B, S)) * 0.3), f32(rng.standard_normal((B, S)) * 0.3)
+    a, p = f32(0.4 + 0.5 * rng.random((M, S))), f32(0.01 + 0.05 * rng.random((M, S)))
+    lam, eta = f32(0.5 + rng.random((B, M, S))), f32(rng.standard_normal((B, M, S)))
+    guard = 64
+    def padded(x):
+        buf = torch.full((x.size + 2 * guard,), 777.0, device="cuda")
+        buf[guard:guard + x.size] = torch.tensor(x, device="cuda").reshape(-1)
+        return buf, buf[guard:guard + x.size].view(*x.shape)
+    lam_buf, lam_t = padded(lam)
+    eta_buf, eta_t = padded(eta)
+    a_buf, a_t = padded(a)
+    p_buf, p_t = padded(p)
+    t = lambda x: torch.tensor(x, device="cuda")
+    for prior in (False, True):
+        ref = O.step(v, lv, k, q, a, p, lam, eta, prior=prior)
+        lam_in, eta_in = lam_t.clone(), eta_t.clone()
+        if inplace:
+            lam_buf[guard:guard + lam.size] = t(lam).reshape(-1)
+            eta_buf[guard:guard + eta.size] = t(eta).reshape(-1)
+            lam_in, eta_in = lam_t, eta_t
+        y, y_var, st = kb.kla_step_b200(t(v), t(lv), t(k), t(q), a_t, p_t, (lam_in, eta_in),
+                                        decode_from_prior=prior, inplace=inplace)
+        torch.cuda.synchronize()
+        assert ratio(y, ref.y, 2e-5, 2e-6) <= 1 and ratio(y_var, ref.y_var, 2e-5, 2e-6) <= 1
+        assert ratio(st.lam, ref.lam, 2e-5, 2e-6) <= 1 and ratio(st.eta, ref.eta, 2e-5, 2e-6) <= 1
+        for buf in (lam_buf, eta_buf, a_buf, p_buf):
+            assert (buf[:guard] == 777.0).all() and (buf[-guard:] == 777.0).all(), "a lane wrote outside its rows"
+        if not inplace:
+            assert torch.equal(lam_t, t(lam)) and torch.equal(eta_t, t(eta)), "the input state was modified"
 
 
 def test_prefill_then_decode_equals_one_scan(kb):
@@ -267,10 +313,13 @@ def test_prefill_then_decode_equals_one_scan(kb):
 
 
 def test_full_size_slice_against_oracle(kb):
-    """The headline raw-op shape (B=8, T=4096, M=1024, S=16) on the GPU; the
-    oracle checks random (batch, channel-block) slices, which is exact because
-    lanes are independent over (b, m); dk, dq are checked as sums of blocks on a
-    smaller channel count elsewhere."""
+    """The headline raw-op shape (B=8, T=4096, M=1024, S=16) on the GPU against the float64 oracle.
+
+    Lanes are independent over (b, m), so y, y_var, the state, dv, dlambda_v are checked exactly on random
+    (batch, channel-block) slices. The four reduced gradients are checked at the full length of their sums:
+    da, dp (sums over all 8 x 4096 (b, t)) on channel blocks over ALL batch elements, and dk, dq (sums over
+    all 1024 channels) on one whole batch element. Next to each ratio the same ratio for the oracle run in
+    float32 (the reference's sequential algorithm in float32) is printed: the float32 noise of sums this long."""
     B, L, M, S = 8, 4096, 1024, 16
     gen = torch.Generator(device="cpu").manual_seed(0)
     v = torch.randn(B, L, M, generator=gen)
@@ -285,19 +334,42 @@ def test_full_size_slice_against_oracle(kb):
     ins = [t.cuda().requires_grad_(True) for t in (v, lv, k, q, a, p)]
     y, y_var, st = kb.kla_scan_b200(*ins)
     grads = torch.autograd.grad((y * dy.cuda()).sum() + (y_var * dyv.cuda()).sum(), ins)
+    n_ = lambda t: t.numpy()
     for b_, m0 in ((0, 0), (3, 512), (7, 1016)):
-        sl = slice(m0, m0 + 8)
-        f = O.scan_fwd(v[b_:b_ + 1, :, sl].numpy(), lv[b_:b_ + 1, :, sl].numpy(), k[b_:b_ + 1].numpy(),
-                       q[b_:b_ + 1].numpy(), a[sl].numpy(), p[sl].numpy())
-        bw = O.scan_bwd(v[b_:b_ + 1, :, sl].numpy(), lv[b_:b_ + 1, :, sl].numpy(), k[b_:b_ + 1].numpy(),
-                        q[b_:b_ + 1].numpy(), a[sl].numpy(), p[sl].numpy(),
-                        dy[b_:b_ + 1, :, sl].numpy(), dyv[b_:b_ + 1, :, sl].numpy())
-        r = {"y": ratio(y[b_:b_ + 1, :, sl], f.y), "y_var": ratio(y_var[b_:b_ + 1, :, sl], f.y_var),
-             "lam": ratio(st.lam[b_:b_ + 1, sl], f.lam), "eta": ratio(st.eta[b_:b_ + 1, sl], f.eta),
-             "dv": ratio(grads[0][b_:b_ + 1, :, sl], bw.dv), "dlambda_v": ratio(grads[1][b_:b_ + 1, :, sl], bw.dlambda_v)}
-        print(f"\n  full-size slice b={b_} m={m0}: " + " ".join(f"{n} {x:.2f}" for n, x in r.items()))
+        sl, bs = slice(m0, m0 + 8), slice(b_, b_ + 1)
+        f = O.scan_fwd(n_(v[bs, :, sl]), n_(lv[bs, :, sl]), n_(k[bs]), n_(q[bs]), n_(a[sl]), n_(p[sl]))
+        bw = O.scan_bwd(n_(v[bs, :, sl]), n_(lv[bs, :, sl]), n_(k[bs]), n_(q[bs]), n_(a[sl]), n_(p[sl]),
+                        n_(dy[bs, :, sl]), n_(dyv[bs, :, sl]))
+        r = {"y": ratio(y[bs, :, sl], f.y), "y_var": ratio(y_var[bs, :, sl], f.y_var),
+             "lam": ratio(st.lam[bs, sl], f.lam), "eta": ratio(st.eta[bs, sl], f.eta),
+             "dv": ratio(grads[0][bs, :, sl], bw.dv), "dlambda_v": ratio(grads[1][bs, :, sl], bw.dlambda_v)}
+        print(f"\n  full-size slice b={b_} m={m0}: " + " ".join(f"{n}={x:.2f}" for n, x in r.items()))
         assert max(r.values()) <= 1.0, r
     assert all(torch.isfinite(t).all() for t in grads)
+
+    rows = []
+    # da, dp: channel blocks, all batch elements and time steps
+    for m0 in (0, 504, 1016):
+        sl = slice(m0, m0 + 8)
+        args = (n_(v[:, :, sl]), n_(lv[:, :, sl]), n_(k), n_(q), n_(a[sl]), n_(p[sl]), n_(dy[:, :, sl]), n_(dyv[:, :, sl]))
+        b64 = O.scan_bwd(*args)
+        b32 = O.scan_bwd(*args, dtype=np.float32)
+        for name, got, r64, r32 in (("da", grads[4][sl], b64.da, b32.da), ("dp", grads[5][sl], b64.dp, b32.dp)):
+            rows.append((f"{name}[{m0}:{m0 + 8}]", ratio(got, r64), ratio(r32, r64), rel_err(got, r64)))
+    # dk, dq: one batch element, all channels
+    b_ = 5
+    bs = slice(b_, b_ + 1)
+    args = (n_(v[bs]), n_(lv[bs]), n_(k[bs]), n_(q[bs]), n_(a), n_(p), n_(dy[bs]), n_(dyv[bs]))
+    b64 = O.scan_bwd(*args)
+    b32 = O.scan_bwd(*args, dtype=np.float32)
+    for name, got, r64, r32 in (("dk", grads[2][bs], b64.dk, b32.dk), ("dq", grads[3][bs], b64.dq, b32.dq)):
+        rows.append((f"{name}[b={b_}]", ratio(got, r64), ratio(r32, r64), rel_err(got, r64)))
+    print("\n  full-size reduced gradients, |err|/(1e-6 + 1e-5|ref|) against the float64 oracle:")
+    for name, r, r32, re_ in rows:
+        print(f"    {name:14s} b200 {r:8.2f}   float32 oracle {r32:8.2f}   rel_err {re_:.1e}")
+    for name, r, r32, re_ in rows:
+        assert re_ < 2e-3, (name, re_)  # the reference's own gradient contract, tests/test_backends.py:54
+        assert r <= REDUCED_SLACK, (name, r)
 
 
 # ------------------------------------------------------------ fused sensor prologue
