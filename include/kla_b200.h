@@ -203,6 +203,40 @@ typedef struct kla_b200_slab_args {
 int kla_b200_slab_aggregate(const kla_b200_slab_args *args, void *stream);
 
 /*
+ * Fold of per-chunk aggregates for the time-parallel scan on one GPU. The
+ * reference parallelises its scan over time with associative scans of
+ * trace-normalised Moebius matrices and affine pairs
+ * (src/kla/ops/kla_ops.py:76-123, 248, 274-280) and folds a carried state onto a
+ * scanned chunk (src/kla/ops/kernels/triton/tiled_mobius_scan.py:86-102); this
+ * is the carry pass of the same idea at chunk granularity.
+ *
+ * A [B, L, ...] problem whose (b, m) grid is too small to fill the GPU is cut
+ * into C chunks of L/C steps that are scanned as B*C batch entries (entry
+ * b*C + c is chunk c of batch element b; for tensors whose batch stride is
+ * L times their time stride this is the same memory with other strides):
+ *   1. kla_b200_slab_aggregate (adjoint = 0) over the B*C entries;
+ *   2. kla_b200_chunk_fold (adjoint = 0): the state before each chunk,
+ *      lam_in / eta_in [B*C, M, S], from the aggregates and the initial state;
+ *   3. kla_b200_scan_fwd over the B*C entries with lam0 = lam_in, eta0 = eta_in;
+ *      the state after the sequence is entry b*C + C-1 of lam_fin / eta_fin.
+ * Backward: kla_b200_slab_aggregate (adjoint = 1, lam0 = lam_in, eta0 = eta_in),
+ * kla_b200_chunk_fold (adjoint = 1) from the gradient of the returned state
+ * (in_a = dlam_fin, in_b = deta_fin, [B, M, S], or both NULL), then
+ * kla_b200_scan_bwd over the B*C entries with dlam_fin / deta_fin = the seeds
+ * out_a / out_b; the gradient of the initial state is entry b*C of dlam0 / deta0.
+ * The folds run in float64, one thread per (b, m, s).
+ */
+typedef struct kla_b200_chunk_fold_args {
+    int64_t B, C, M, S;
+    int32_t adjoint;
+    const float *agg;         /* [B*C, M, S, 8] from kla_b200_slab_aggregate */
+    const float *in_a, *in_b; /* [B, M, S] or both NULL: (lam0, eta0) / (dlam_fin, deta_fin) */
+    float *out_a, *out_b;     /* [B*C, M, S]: (lam_in, eta_in) / (dlam_seed, deta_seed) */
+} kla_b200_chunk_fold_args;
+
+int kla_b200_chunk_fold(const kla_b200_chunk_fold_args *args, void *stream);
+
+/*
  * One decode step. Replaces kla_step (src/kla/ops/kla_ops.py:293-331), which
  * the reference layer calls directly for single-token decode
  * (src/kla/layers/kla_layer.py:277-293). phi is floored at 1e-12 as there

@@ -23,6 +23,7 @@ SYMBOLS = (
     "kla_b200_scan_bwd",
     "kla_b200_step",
     "kla_b200_slab_aggregate",
+    "kla_b200_chunk_fold",
     "kla_b200_conv_step",
     "kla_b200_conv_seq",
     "kla_b200_step_layer",
@@ -126,6 +127,13 @@ class SlabArgs(Structure):
     ]
 
 
+class ChunkFoldArgs(Structure):
+    _fields_ = [
+        ("B", c_int64), ("C", c_int64), ("M", c_int64), ("S", c_int64), ("adjoint", c_int32),
+        ("agg", c_void_p), ("in_a", c_void_p), ("in_b", c_void_p), ("out_a", c_void_p), ("out_b", c_void_p),
+    ]
+
+
 class StepArgs(Structure):
     _fields_ = [
         ("B", c_int64), ("M", c_int64), ("S", c_int64),
@@ -169,6 +177,8 @@ def load() -> ctypes.CDLL:
     lib.kla_b200_scan_bwd.argtypes = [POINTER(BwdArgs), c_void_p]
     lib.kla_b200_slab_aggregate.restype = c_int
     lib.kla_b200_slab_aggregate.argtypes = [POINTER(SlabArgs), c_void_p]
+    lib.kla_b200_chunk_fold.restype = c_int
+    lib.kla_b200_chunk_fold.argtypes = [POINTER(ChunkFoldArgs), c_void_p]
     for name in ("mobius_scan_fwd", "mobius_scan_bwd", "affine_scan_fwd", "affine_scan_bwd"):
         fn = getattr(lib, "kla_b200_" + name)
         fn.restype = c_int

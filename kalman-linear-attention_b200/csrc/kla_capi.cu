@@ -426,6 +426,25 @@ int kla_b200_slab_aggregate(const kla_b200_slab_args *a, void *stream) {
                          static_cast<cudaStream_t>(stream));
 }
 
+int kla_b200_chunk_fold(const kla_b200_chunk_fold_args *a, void *stream) {
+    if (a == nullptr || a->B < 0 || a->C < 1 || a->M < 0 || a->S < 0) return KLA_B200_EINVAL;
+    if (a->S > KLA_B200_MAX_DSTATE || a->B * a->C > 65535 || a->M > (1 << 30)) return KLA_B200_EUNSUPPORTED;
+    if (a->B == 0 || a->M == 0 || a->S == 0) return KLA_B200_OK;
+    if (!a->agg || !a->out_a || !a->out_b || (a->in_a == nullptr) != (a->in_b == nullptr)) return KLA_B200_EINVAL;
+    if (!aligned(a->agg, 16)) return KLA_B200_EALIGN;
+    ChunkFoldParams prm{};
+    prm.B = (int)a->B; prm.C = (int)a->C; prm.M = (int)a->M; prm.S = (int)a->S;
+    prm.agg = a->agg; prm.in_a = a->in_a; prm.in_b = a->in_b; prm.out_a = a->out_a; prm.out_b = a->out_b;
+    const long long lanes = a->B * a->M * a->S;
+    const unsigned blocks = (unsigned)((lanes + 127) / 128);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (a->adjoint) kla_chunk_fold_kernel<true><<<blocks, 128, 0, st>>>(prm);
+    else kla_chunk_fold_kernel<false><<<blocks, 128, 0, st>>>(prm);
+    g_launches++;
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
+}
+
 int kla_b200_step(const kla_b200_step_args *a, void *stream) {
     if (a == nullptr) return KLA_B200_EINVAL;
     int rc = check_common(a->B, 1, a->M, a->S, a->in_dtype, a->out_dtype);

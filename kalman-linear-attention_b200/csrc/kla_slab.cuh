@@ -189,4 +189,77 @@ __global__ void __launch_bounds__(128) kla_slab_aggregate_kernel(const SlabParam
     }
 }
 
+// ---------------------------------------------------------------------------
+// Folds over the chunks of one sequence held on ONE GPU (time-parallel scan).
+//
+// The time axis of a [B, L, ...] problem is cut into C chunks that are scanned
+// as B*C independent batch entries (entry b*C + c = chunk c of batch element b),
+// which fills the GPU when B*M alone does not. Each chunk needs the state it
+// starts from (forward) and the carry it ends with (backward); both follow from
+// the per-chunk aggregates above by a short serial fold over c, done here with
+// one thread per (b, m, s) lane in float64.
+//
+//   forward  in:  agg [B*C, M, S, 8] (MODE 0 records), lam0/eta0 [B, M, S] or nullptr
+//            out: lam_in, eta_in [B*C, M, S], the state before each chunk's first step
+//   adjoint  in:  agg [B*C, M, S, 8] (MODE 1 records), dlam_fin/deta_fin [B, M, S] or nullptr
+//            out: dlam_seed, deta_seed [B*C, M, S]: passed to the backward kernel as the gradient
+//                 of each chunk's returned state, they make it start from the right carry
+struct ChunkFoldParams {
+    int B, C, M, S;
+    const float *agg;
+    const float *in_a, *in_b;
+    float *out_a, *out_b;
+};
+
+template <bool ADJ>
+__global__ void __launch_bounds__(128) kla_chunk_fold_kernel(const ChunkFoldParams prm) {
+    const long long lanes = (long long)prm.M * prm.S;
+    const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= (long long)prm.B * lanes) return;
+    const long long b = gid / lanes, ms = gid % lanes;
+    const int C = prm.C;
+    auto rec = [&](int c, double (&A)[7]) {
+        const float4 *src = reinterpret_cast<const float4 *>(prm.agg + (((b * C + c) * lanes) + ms) * 8);
+        const float4 lo = src[0], hi = src[1];
+        A[0] = lo.x; A[1] = lo.y; A[2] = lo.z; A[3] = lo.w; A[4] = hi.x; A[5] = hi.y; A[6] = hi.z;
+    };
+    double A[7];
+    if (!ADJ) {
+        double P = 1.0, mean = 0.0;
+        if (prm.in_a != nullptr) {
+            P = 1.0 / fmax((double)prm.in_a[gid], (double)kLamMin);
+            mean = (double)prm.in_b[gid] * P;
+        }
+        for (int c = 0; c < C; ++c) {
+            const long long o = (b * C + c) * lanes + ms;
+            const double lam = 1.0 / P;
+            prm.out_a[o] = (float)lam;
+            prm.out_b[o] = (float)(mean * lam);
+            if (c + 1 < C) {
+                rec(c, A);
+                const double x = A[0] + A[1] * P, w = A[2] + A[3] * P, z = A[4] + A[5] * P + A[6] * mean;
+                P = w / x;
+                mean = z / x;
+            }
+        }
+    } else {
+        rec(C - 1, A);
+        const double dl = prm.in_a ? (double)prm.in_a[gid] : 0.0, de = prm.in_b ? (double)prm.in_b[gid] : 0.0;
+        // (dL/dP, dL/dmean) at the end of the sequence from the gradient of (lam, eta) = (1/P, mean/P)
+        const double lam = 1.0 / A[5], eta = A[6] * lam;
+        double cP = -lam * (lam * dl + eta * de), cm = de * lam;
+        for (int c = C - 1; c >= 0; --c) {
+            if (c != C - 1) rec(c, A);
+            const long long o = (b * C + c) * lanes + ms;
+            const double P_end = A[5], mean_end = A[6];
+            const double deta = cm * P_end;
+            prm.out_b[o] = (float)deta;
+            prm.out_a[o] = (float)(-(cP * P_end * P_end + mean_end * deta));
+            const double nP = A[0] * cP + A[1] * cm + A[3];
+            cm = A[2] * cm + A[4];
+            cP = nP;
+        }
+    }
+}
+
 }  // namespace kla

@@ -23,7 +23,7 @@ from typing import NamedTuple, Optional
 import torch
 
 from . import _lib
-from ._lib import BF16, F32, MAX_DSTATE, BwdArgs, FwdArgs, StepArgs, Tensor3
+from ._lib import BF16, F32, MAX_DSTATE, BwdArgs, ChunkFoldArgs, FwdArgs, SlabArgs, StepArgs, Tensor3
 
 
 class KLAState(NamedTuple):
@@ -179,6 +179,93 @@ def _launch_bwd(v, lambda_v, k, q, a, p, lam0, eta0, ckpt, dy, dy_var, dlam_fin,
     return dv, dlv, dk, dq, da, dp, dlam0, deta0
 
 
+def slab_aggregate(v, lambda_v, k, a, p, *, q=None, dy=None, dy_var=None, lam0=None, eta0=None,
+                   prior: bool = False) -> torch.Tensor:
+    """Launch ``kla_b200_slab_aggregate``: one record per lane that describes how a whole time slab acts on
+    the filter state (``dy`` None) or on the backward carry (``dy`` given). Returns [B, M, S, 8] float32."""
+    lib = _lib.load()
+    B, L, M = v.shape
+    S = k.shape[2]
+    out = torch.empty((B, M, S, 8), device=v.device, dtype=torch.float32)
+    adjoint = dy is not None
+    od = dy.dtype if adjoint else torch.float32
+    args = SlabArgs(
+        B=B, L=L, M=M, S=S, in_dtype=_dt(v.dtype), out_dtype=_dt(od),
+        decode_from_prior=int(prior), adjoint=int(adjoint),
+        v=_t3(v), lambda_v=_t3(lambda_v), k=_t3(k), q=_t3(q),
+        a=_ptr(a), p=_ptr(p), lam0=_ptr(lam0), eta0=_ptr(eta0),
+        dy=_t3(dy), dy_var=_t3(dy_var), out=_ptr(out),
+    )
+    with torch.cuda.device(v.device):
+        _lib.check(lib.kla_b200_slab_aggregate(ctypes.byref(args), _stream(v.device)))
+    return out
+
+
+def chunk_fold(agg: torch.Tensor, C: int, in_a, in_b, adjoint: bool):
+    """Launch ``kla_b200_chunk_fold`` over aggregates [B*C, M, S, 8]; returns two [B*C, M, S] float32 tensors:
+    the state before each chunk (forward) or the state-gradient seeds of each chunk (adjoint)."""
+    lib = _lib.load()
+    BC, M, S, _ = agg.shape
+    out_a = torch.empty((BC, M, S), device=agg.device, dtype=torch.float32)
+    out_b = torch.empty((BC, M, S), device=agg.device, dtype=torch.float32)
+    args = ChunkFoldArgs(B=BC // C, C=C, M=M, S=S, adjoint=int(adjoint), agg=_ptr(agg),
+                         in_a=_ptr(in_a), in_b=_ptr(in_b), out_a=_ptr(out_a), out_b=_ptr(out_b))
+    with torch.cuda.device(agg.device):
+        _lib.check(lib.kla_b200_chunk_fold(ctypes.byref(args), _stream(agg.device)))
+    return out_a, out_b
+
+
+# CTAs the backward kernel keeps resident on a B200: 148 SMs x 2
+_RESIDENT_CTAS = 296
+_MIN_CHUNK_STEPS = 64
+
+
+def _chunkable(t: Optional[torch.Tensor], B: int, L: int) -> bool:
+    """[B, L, X] can be read as [B*C, L/C, X] without a copy."""
+    return t is None or B == 1 or t.stride(0) == L * t.stride(1)
+
+
+def pick_time_chunks(B: int, L: int, M: int, S: int, requested: Optional[int] = None) -> int:
+    """Number of time chunks for the time-parallel scan. 1 = the plain lane-serial kernels.
+
+    The kernels put one CTA on every 32 / 16 / 8 ... channels (d_state 16 / 32 / 64 ...) of every batch element.
+    When that grid leaves most of the GPU empty, the sequence is cut into C chunks that run as B*C batch entries;
+    building the chunks' start states costs about 0.7x of a forward + backward pass on top, so chunking is only
+    chosen when the plain grid fills less than a third of the resident CTA slots. C divides L, chunks keep at
+    least 64 steps. ``requested`` (or the environment variable KLA_B200_TIME_CHUNKS) overrides the choice; it is
+    lowered to the nearest usable divisor of L."""
+    import os
+
+    if requested is None and os.environ.get("KLA_B200_TIME_CHUNKS"):
+        requested = int(os.environ["KLA_B200_TIME_CHUNKS"])
+    lpc = 1
+    while 4 * lpc < S:
+        lpc *= 2
+    mc = 4 * (32 // lpc)
+    ctas = B * ((M + mc - 1) // mc)
+    if requested is None:
+        if ctas == 0 or 3 * ctas > _RESIDENT_CTAS:
+            return 1
+        want = _RESIDENT_CTAS // ctas
+    else:
+        want = max(1, int(requested))
+    want = min(want, max(1, L // _MIN_CHUNK_STEPS), max(1, 65535 // max(B, 1)))
+    for c in range(want, 0, -1):
+        if L % c == 0:
+            return c
+    return 1
+
+
+def _as_chunks(t: Optional[torch.Tensor], C: int) -> Optional[torch.Tensor]:
+    """View [B, L, X] as [B*C, L/C, X] (same memory)."""
+    if t is None or C == 1:
+        return t
+    B, L, X = t.shape
+    if B == 1:
+        return t.as_strided((C, L // C, X), (t.stride(1) * (L // C), t.stride(1), t.stride(2)), t.storage_offset())
+    return t.as_strided((B * C, L // C, X), (t.stride(1) * (L // C), t.stride(1), t.stride(2)), t.storage_offset())
+
+
 class _KLAScanB200(torch.autograd.Function):
     """Forward and exact backward of the fused scan, both as single kernels.
 
@@ -187,11 +274,28 @@ class _KLAScanB200(torch.autograd.Function):
     float32 contiguous [B, M, S] or None."""
 
     @staticmethod
-    def forward(ctx, v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype: torch.dtype, sensors=None):
+    def forward(ctx, v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype: torch.dtype, sensors=None,
+                chunks: int = 1):
         need_grad = any(ctx.needs_input_grad[:8])
-        y, y_var, lam_fin, eta_fin, ckpt = _launch_fwd(
-            v, lambda_v, k, q, a, p, lam0, eta0, prior, out_dtype, need_grad, sensors)
-        ctx.save_for_backward(v, lambda_v, k, q, a, p, lam0, eta0, ckpt)
+        B, L, M = v.shape
+        C = chunks if (chunks > 1 and sensors is None and all(_chunkable(t, B, L) for t in (v, lambda_v, k, q))) else 1
+        ctx.chunks = C
+        if C > 1:
+            # time-parallel: the chunks of every sequence run as B*C batch entries from exact start states
+            vc, lc, kc, qc = (_as_chunks(t, C) for t in (v, lambda_v, k, q))
+            agg = slab_aggregate(vc, lc, kc, a, p)
+            lam_in, eta_in = chunk_fold(agg, C, lam0, eta0, adjoint=False)
+            y, y_var, lam_all, eta_all, ckpt = _launch_fwd(
+                vc, lc, kc, qc, a, p, lam_in, eta_in, prior, out_dtype, need_grad)
+            S = k.shape[2]
+            lam_fin = lam_all.view(B, C, M, S)[:, C - 1].contiguous()
+            eta_fin = eta_all.view(B, C, M, S)[:, C - 1].contiguous()
+            ctx.save_for_backward(v, lambda_v, k, q, a, p, lam0, eta0, ckpt, lam_in, eta_in)
+            y, y_var = y.view(B, L, M), y_var.view(B, L, M)
+        else:
+            y, y_var, lam_fin, eta_fin, ckpt = _launch_fwd(
+                v, lambda_v, k, q, a, p, lam0, eta0, prior, out_dtype, need_grad, sensors)
+            ctx.save_for_backward(v, lambda_v, k, q, a, p, lam0, eta0, ckpt)
         ctx.prior = prior
         ctx.sensors = sensors
         ctx.out_dtype = out_dtype
@@ -200,7 +304,7 @@ class _KLAScanB200(torch.autograd.Function):
     @staticmethod
     @torch.autograd.function.once_differentiable  # the hand-written gradients have no graph: a double backward raises
     def backward(ctx, dy, dy_var, dlam_fin, deta_fin):
-        v, lambda_v, k, q, a, p, lam0, eta0, ckpt = ctx.saved_tensors
+        v, lambda_v, k, q, a, p, lam0, eta0, ckpt, *chunk_state = ctx.saved_tensors
         B, L, M = v.shape
         S = k.shape[2]
         dev = v.device
@@ -224,13 +328,29 @@ class _KLAScanB200(torch.autograd.Function):
         if dlam_fin is not None:
             dlam_fin = dlam_fin.float().contiguous()
             deta_fin = deta_fin.float().contiguous()
-        dv, dlv, dk, dq, da, dp, dlam0, deta0 = _launch_bwd(
-            v, lambda_v, k, q, a, p, lam0, eta0, ckpt, dy, dy_var, dlam_fin, deta_fin, ctx.prior, od, ctx.sensors)
+        C = ctx.chunks
+        if C > 1:
+            lam_in, eta_in = chunk_state
+            if not (_chunkable(dy, B, L) and _chunkable(dy_var, B, L)):
+                dy = dy.contiguous()
+                dy_var = None if dy_var is None else dy_var.contiguous()
+            vc, lc, kc, qc, dyc, dyvc = (_as_chunks(t, C) for t in (v, lambda_v, k, q, dy, dy_var))
+            adj = slab_aggregate(vc, lc, kc, a, p, q=qc, dy=dyc, dy_var=dyvc, lam0=lam_in, eta0=eta_in, prior=ctx.prior)
+            dlam_seed, deta_seed = chunk_fold(adj, C, dlam_fin, deta_fin, adjoint=True)
+            dv, dlv, dk, dq, da, dp, dlam_all, deta_all = _launch_bwd(
+                vc, lc, kc, qc, a, p, lam_in, eta_in, ckpt, dyc, dyvc, dlam_seed, deta_seed, ctx.prior, od)
+            dv, dlv = dv.view(B, L, M), dlv.view(B, L, M)
+            dk, dq = dk.view(B, L, S), dq.view(B, L, S)
+            dlam0 = dlam_all.view(B, C, M, S)[:, 0]
+            deta0 = deta_all.view(B, C, M, S)[:, 0]
+        else:
+            dv, dlv, dk, dq, da, dp, dlam0, deta0 = _launch_bwd(
+                v, lambda_v, k, q, a, p, lam0, eta0, ckpt, dy, dy_var, dlam_fin, deta_fin, ctx.prior, od, ctx.sensors)
         if k.dtype != torch.float32:
             dk, dq = dk.to(k.dtype), dq.to(k.dtype)
         has_state = lam0 is not None
         return (dv, dlv, dk, dq, da, dp,
-                dlam0 if has_state else None, deta0 if has_state else None, None, None, None)
+                dlam0 if has_state else None, deta0 if has_state else None, None, None, None, None)
 
 
 def kla_scan_b200(
@@ -246,6 +366,7 @@ def kla_scan_b200(
     out_dtype: Optional[torch.dtype] = None,
     log_variance: Optional[tuple] = None,
     epilogue: Optional[dict] = None,
+    time_chunks: Optional[int] = None,
 ):
     """B200 KLA scan. Same call and return contract as the reference's
     ``kla_scan_torch`` (src/kla/ops/kla_ops.py:188-290): returns
@@ -270,6 +391,15 @@ def kla_scan_b200(
     with ``g = act(gate)``; either half may be left out. Forward only: it raises
     ``NotImplementedError`` when a gradient would be needed (run it under
     ``torch.no_grad()``; the training path applies these two steps in torch).
+
+    ``time_chunks``: the time-parallel form of the scan. The reference's parallel
+    path scans trace-normalised Moebius matrices and affine pairs over time
+    (kla_ops.py:76-123, 248, 274-280); here the sequence is cut into C chunks,
+    one pass composes each chunk's map on the filter state, a short fold over the
+    chunks gives every chunk its exact start state, and the chunks then run
+    through the ordinary kernels side by side (the backward does the same with
+    the adjoint carry). ``None`` picks C from the shape (:func:`pick_time_chunks`:
+    1 unless B*M is too small to fill the GPU), ``1`` switches it off.
     """
     _require_device(v)
     if a.dim() != 2:
@@ -340,8 +470,9 @@ def kla_scan_b200(
         y, y_var, lam_fin, eta_fin, _ = _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, bool(decode_from_prior),
                                                     out_dtype, False, log_variance, epi)
         return y, y_var, _state_cls()(lam=lam_fin, eta=eta_fin)
+    chunks = pick_time_chunks(B, L, M, S, time_chunks) if L > 0 else 1
     y, y_var, lam_fin, eta_fin = _KLAScanB200.apply(
-        v, lambda_v, k, q, a, p, lam0, eta0, bool(decode_from_prior), out_dtype, log_variance)
+        v, lambda_v, k, q, a, p, lam0, eta0, bool(decode_from_prior), out_dtype, log_variance, chunks)
     return y, y_var, _state_cls()(lam=lam_fin, eta=eta_fin)
 
 

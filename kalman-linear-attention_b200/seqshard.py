@@ -27,38 +27,17 @@ tests); gathered tensors land in this GPU's memory and are read from there.
 
 from __future__ import annotations
 
-import ctypes
 from typing import List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
 
 from . import _lib, ops
-from ._lib import SlabArgs
 
 
 # ------------------------------------------------------------------ kernels
 
-def slab_aggregate(v, lambda_v, k, a, p, *, q=None, dy=None, dy_var=None, lam0=None, eta0=None,
-                   prior: bool = False) -> torch.Tensor:
-    """Launch ``kla_b200_slab_aggregate``; forward aggregate when ``dy`` is None,
-    adjoint aggregate otherwise. Returns [B, M, S, 8] float32."""
-    lib = _lib.load()
-    B, L, M = v.shape
-    S = k.shape[2]
-    out = torch.empty((B, M, S, 8), device=v.device, dtype=torch.float32)
-    adjoint = dy is not None
-    od = dy.dtype if adjoint else torch.float32
-    args = SlabArgs(
-        B=B, L=L, M=M, S=S, in_dtype=ops._dt(v.dtype), out_dtype=ops._dt(od),
-        decode_from_prior=int(prior), adjoint=int(adjoint),
-        v=ops._t3(v), lambda_v=ops._t3(lambda_v), k=ops._t3(k), q=ops._t3(q),
-        a=ops._ptr(a), p=ops._ptr(p), lam0=ops._ptr(lam0), eta0=ops._ptr(eta0),
-        dy=ops._t3(dy), dy_var=ops._t3(dy_var), out=ops._ptr(out),
-    )
-    with torch.cuda.device(v.device):
-        _lib.check(lib.kla_b200_slab_aggregate(ctypes.byref(args), ops._stream(v.device)))
-    return out
+slab_aggregate = ops.slab_aggregate  # the launch lives with the other kernel launches
 
 
 # -------------------------------------------------------- folds (pure torch)
