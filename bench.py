@@ -8,11 +8,17 @@ One "step" is one forward + one backward pass of the scan over one batch of
 synthetic input. With N > 1 (launched under torch.distributed.run) every rank
 scans its own batch shard of the same size -- lanes are independent over
 (batch, channel), so there is no data-path collective -- and the value is the
-total over ranks divided by the slowest rank's time (weak scaling).
+total over ranks divided by the slowest rank's time (weak scaling). The same
+line carries two more measured blocks: ``strong`` -- the ONE B=8 problem split
+over the N ranks by batch x channel with the gradient all-reduces inside the
+timed region, checked against rank 0's one-GPU result -- and, for N > 1,
+``seqshard`` -- the long sequence split into time slabs over the ranks.
 
-Prints ONE JSON line (rank 0). ``--impl reference`` times the CPU oracle (a
-port of the reference's sequential float32 scan and its adjoint) on the host
-cores instead.
+Prints ONE JSON line (rank 0). ``--impl reference`` times the reference's own
+CPU path instead (``kla.ops.kla_scan(..., backend="torch")`` forward and
+``torch.autograd.grad``, from the unmodified copy under ``baseline/_ref``) on
+the host cores; without that copy it times the CPU oracle (a port of the
+reference's sequential float32 scan and its adjoint) and says so.
 """
 
 from __future__ import annotations
@@ -31,7 +37,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# The workload: BASELINE config 2, "raw op pair, fp32".
+# The workload: the raw op, float32, batch 8 x 4096 steps x 1024 channels x 16 states per channel.
 WORK = dict(B=8, L=4096, M=1024, S=16)
 METRIC = "KLA scan fwd+bwd tokens/s"
 UNIT = "tokens/s"
@@ -47,11 +53,18 @@ def algorithmic_bytes_per_token(M, S, esz=4):
     return fwd, bwd
 
 
-# ncu-measured DRAM traffic per launch at the bench workload (bytes, read + write), copied
-# from profiles/kla_scan_fwd_bwd_B8_T4096_M1024_S16_f32.md; the raw-scan figure is per batch
-# entry (captured at B=1, T=4096, M*S=16384; traffic is proportional to B), from
-# profiles/kla_rawscan_T4096_N16384_f32.md.
-NCU_TRAFFIC = {"kla_bwd_kernel": 1076.2e6, "kla_fwd_kernel": 760.8e6, "rawscan_mobius_bwd_per_batch": 2651.5e6}
+def ncu_traffic():
+    """DRAM traffic per launch (bytes, read + write) from the last ncu captures of the kernels, kept as data
+    beside the capture summaries (profiles/ncu_traffic.json: kernel -> bytes at the stated shape). A kernel
+    that is missing there reports ``traffic: null``."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
+            return {k: float(v["bytes"]) for k, v in json.load(f)["kernels"].items()}
+    except (OSError, ValueError, KeyError):
+        return {}
+
+
+NCU_TRAFFIC = ncu_traffic()
 
 
 def make_inputs(seed=0, **w):
@@ -166,12 +179,93 @@ def cpu_oracle_run(sample, threads=None):
     return tokens / dt, dt, int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
 
 
+def headline_config(B=None):
+    """The `config` object of the headline line; the same for both arms (the CPU arm says what bounded sample
+    of it a step was under cpu_baseline.sample)."""
+    B = WORK["B"] if B is None else B
+    return {"workload": f"raw KLA scan fwd+bwd, B={B} T=4096 M=1024 S=16 per GPU, fp32 I/O and state"
+                        + ("" if B == 8 else " (batch sweep, not the headline workload)"),
+            **WORK, "sharding": "batch shard per rank, no collective",
+            "l2": "inputs+outputs per step (1.1 GB) exceed the 126 MB L2; no explicit flush"}
+
+
+def reference_dir():
+    """Where the unmodified reference package lives (baseline/install_reference.py puts it there), or None."""
+    d = os.path.join(ROOT, "baseline", "_ref")
+    return d if os.path.isfile(os.path.join(d, "kla", "__init__.py")) else None
+
+
+def cpu_reference_run(sample, threads=None):
+    """Time the reference's own CPU path on `sample`: ``kla.ops.kla_scan(..., backend="torch")`` forward plus
+    ``torch.autograd.grad`` with the seeded upstream gradients, float32, all host threads. Returns
+    (tokens_per_s_at_full_width, seconds, threads); the sample may hold fewer channels than the workload (the
+    reference's path needs ~240 B per (b, t, m, s), 128 GB for the whole workload), lanes are independent over
+    channels, so the rate is scaled by M_sample/M."""
+    import torch
+
+    d = reference_dir()
+    if d not in sys.path:
+        sys.path.insert(0, d)
+    from kla.ops import kla_scan
+
+    n = threads or os.cpu_count() or 1
+    torch.set_num_threads(n)
+    ins = make_inputs(**sample)
+    t = [ins[k].clone().requires_grad_(True) for k in ("v", "lambda_v", "k", "q", "a", "p")]
+    t0 = time.perf_counter()
+    y, y_var, _ = kla_scan(*t, backend="torch")
+    torch.autograd.grad([y, y_var], t, [ins["dy"], ins["dyvar"]])
+    dt = time.perf_counter() - t0
+    tokens = sample["B"] * sample["L"] * (sample["M"] / WORK["M"])
+    return tokens / dt, dt, n
+
+
+def run_reference_torch_cpu(args):
+    """The reference arm proper: the reference's own code on the host cores. One step = one channel block of
+    128 channels of `bs` batch elements at full length (the blocks of the workload are independent), sized so
+    that a step takes a few seconds."""
+    cores = os.cpu_count() or 1
+    sample = dict(B=1, L=WORK["L"], M=128, S=WORK["S"])
+    cpu_reference_run(sample)                      # absorbs the compilation of the reference's associative scan
+    _, dt, _ = cpu_reference_run(sample)
+    sample["B"] = int(min(4, WORK["B"], max(1, round(3.0 / max(dt, 1e-3)))))  # memory: ~3 GB per batch element
+    for _ in range(args.warmup):
+        cpu_reference_run(sample)
+    times = []
+    for _ in range(args.steps):
+        _, dt, _ = cpu_reference_run(sample)
+        times.append(dt)
+    tokens = sample["B"] * sample["L"] * (sample["M"] / WORK["M"])
+    value = tokens * args.steps / sum(times)
+    best = tokens / min(times)
+    desc = (f"kla.ops.kla_scan(backend='torch') fwd + autograd.grad, float32: one block of M={sample['M']} of {WORK['M']} "
+            f"channels x B={sample['B']} of {WORK['B']} batch elements x T={sample['L']} per step; rate scaled by the "
+            f"block's share of the workload (blocks are independent; the whole workload does not fit host memory)")
+    port_rate, port_dt, _ = cpu_oracle_run(dict(B=1, L=WORK["L"], M=256, S=WORK["S"]))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": headline_config(),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "reference", "sample": desc,
+                         "best_step": best},
+        "cpu_port": {"value": port_rate, "unit": UNIT, "cores": cores, "kind": "port",
+                     "sample": f"the C/OpenMP restatement of the same algorithm, B=1 x T={WORK['L']} x M=256, {port_dt:.2f} s"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_reference(args):
-    """The reference arm: the reference's CPU algorithm (oracle port, float32,
-    OpenMP over channels) on the host cores, same workload definition."""
+    """The reference arm: the reference's own CPU path when its package is installed under baseline/_ref,
+    otherwise the reference's CPU algorithm as restated by the oracle (float32, OpenMP over channels); on the
+    host cores, same workload definition."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if reference_dir() is not None:
+        return run_reference_torch_cpu(args)
     cores = os.cpu_count() or 1
     # bounded sample: one batch element, all T, a channel block; calibrate its width
     sample = dict(B=1, L=WORK["L"], M=64, S=WORK["S"])
@@ -195,7 +289,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "raw KLA scan fwd+bwd, B=8 T=4096 M=1024 S=16, fp32 (CPU: bounded sample)", **WORK},
+        "config": headline_config(),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -292,6 +386,21 @@ def run_b200(args):
     fwd_ms = sum(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(args.steps)) / args.steps
     bwd_ms = sum(ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(args.steps)) / args.steps
 
+    # ---- two more measured blocks on the same ranks (see their docstrings); a failure there must not cost
+    # the headline, so it is reported in place of the block
+    extra = {}
+    if not args.batch:
+        for name, fn, n in (("strong", strong_block, min(args.steps, 30)), ("seqshard", seqshard_block, min(args.steps, 5))):
+            if name == "seqshard" and world < 2:
+                continue
+            try:
+                extra[name] = fn(dev, rank, world, max(n, 1))
+            except Exception as exc:  # noqa: BLE001
+                if world > 1:
+                    raise  # a rank that skips a collective would leave the others waiting
+                extra[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+            torch.cuda.empty_cache()
+
     # ---- end to end through the public API with HOST buffers: pinned inputs
     # copied in, kla_scan_b200 + autograd, every result copied back out.
     pin = {n: t.pin_memory() for n, t in host.items()}
@@ -337,27 +446,38 @@ def run_b200(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"raw KLA scan fwd+bwd, B={B} T=4096 M=1024 S=16 per GPU, fp32 I/O and state"
-                                   + ("" if B == 8 else " (batch sweep, not the headline workload)"),
-                       **WORK, "sharding": "batch shard per rank, no collective",
-                       "l2": "inputs+outputs per step (1.1 GB) exceed the 126 MB L2; no explicit flush"},
+            "config": headline_config(B),
             "roofline": {"bound": "hbm", "kernel": "kla_bwd_kernel", "achieved": ach_bwd, "peak": peak,
-                         "unit": "GB/s", "frac": ach_bwd / peak, "traffic": NCU_TRAFFIC["kla_bwd_kernel"] * B / 8,
+                         "unit": "GB/s", "frac": ach_bwd / peak, "traffic": NCU_TRAFFIC["kla_bwd_kernel"] * B / 8 if "kla_bwd_kernel" in NCU_TRAFFIC else None,
                          "peak_source": peak_src, "algorithmic_bytes": bwd_bytes, "ms": bwd_ms,
                          "nominal_peak_gbs": 8000.0, "frac_of_nominal": ach_bwd / 8000.0,
                          "note": "not HBM-bound at d_state=16: 62 warp-instructions per 32 lane-steps against 24.8 KB per "
                                  "token; ncu shows the FP32 pipe ~50 % and issue slots ~68 % busy with two compute warps "
                                  "per scheduler (dependent-instruction latency, shared-memory pipe)"},
             "roofline_fwd": {"bound": "hbm", "kernel": "kla_fwd_kernel", "achieved": ach_fwd, "peak": peak,
-                             "unit": "GB/s", "frac": ach_fwd / peak, "traffic": NCU_TRAFFIC["kla_fwd_kernel"] * B / 8,
+                             "unit": "GB/s", "frac": ach_fwd / peak, "traffic": NCU_TRAFFIC["kla_fwd_kernel"] * B / 8 if "kla_fwd_kernel" in NCU_TRAFFIC else None,
                              "algorithmic_bytes": fwd_bytes, "ms": fwd_ms},
             "roofline_step": {"achieved": ach_step, "peak": peak, "unit": "GB/s", "frac": ach_step / peak},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps},
             "gpu_launches": int(launches),
             "clocks": clocks,
+            **extra,
         }
-        if world == 1 and not args.no_cpu:
+        if world == 1 and not args.no_cpu and reference_dir() is not None:
+            sample = dict(B=2, L=T, M=128, S=S)
+            cpu_reference_run(dict(sample, B=1))  # warm-up: the reference's associative scan is compiled on first use
+            runs = [cpu_reference_run(sample) for _ in range(3)]
+            rate, dt, cores = max(runs)
+            line["cpu_baseline"] = {
+                "value": rate, "unit": UNIT, "cores": cores, "kind": "reference",
+                "sample": f"kla.ops.kla_scan(backend='torch') fwd + autograd.grad, float32, one block of B={sample['B']} x T={T} x "
+                          f"M={sample['M']} of {M} channels, best of 3 after a warm-up ({dt:.1f} s); rate scaled by the block's "
+                          f"share of the workload (blocks are independent; the whole workload needs ~128 GB on this path)"}
+            prate, pdt, pcores = cpu_oracle_run(dict(B=1, L=T, M=512, S=S))
+            line["cpu_port"] = {"value": prate, "unit": UNIT, "cores": pcores, "kind": "port",
+                                "sample": f"the C/OpenMP restatement of the same algorithm, B=1 x T={T} x M=512, {pdt:.1f} s"}
+        elif world == 1 and not args.no_cpu:
             sample = dict(B=1, L=T, M=128, S=S)
             rate, dt, cores = cpu_oracle_run(sample)
             # grow the sample towards ~10 s of CPU work: channels first, then batch
@@ -374,8 +494,193 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def _event_time(fn, steps, warm, barrier):
+    """Average milliseconds of fn() over `steps` calls, CUDA events on the current stream, after `warm` calls."""
+    import torch
+
+    for _ in range(warm):
+        fn()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    barrier()
+    return e0.elapsed_time(e1) / steps
+
+
+def _dev_ratio(got, ref, rtol=1e-5, atol=1e-6):
+    """max |got - ref| / (atol + rtol |ref|), on the device."""
+    got, ref = got.double(), ref.double()
+    return float(((got - ref).abs() / (atol + rtol * ref.abs())).max()) if ref.numel() else 0.0
+
+
+def _dev_rel(got, ref):
+    got, ref = got.double(), ref.double()
+    return float((got - ref).abs().max() / (ref.abs().max() + 1.0)) if ref.numel() else 0.0
+
+
+def strong_block(dev, rank, world, steps):
+    """ONE problem of the headline shape split over the ranks by batch x channel (shard.block_of), forward +
+    backward through the public API with the gradient all-reduces (da, dp over the batch group; dk, dq over the
+    channel group) INSIDE the timed region. Every rank also runs the whole problem alone on its GPU: that is the
+    parity reference (max deviation over all outputs and ranks) and the one-GPU time the efficiency is taken
+    against. A rank's block holds few (batch, channel) lanes, so the scan cuts its sequence into time chunks."""
+    import importlib
+
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    import kla_b200
+    shard = kla_b200.shard
+    ops = importlib.import_module("kalman-linear-attention_b200.ops")
+
+    B, T, M, S = 8, WORK["L"], WORK["M"], WORK["S"]
+    g = torch.Generator(device=dev).manual_seed(4321)  # the same problem on every rank
+    r = lambda *sh: torch.randn(*sh, device=dev, generator=g)
+    v, lv = r(B, T, M), 1.0 / F.softplus(r(B, T, M))
+    k, q = F.normalize(r(B, T, S), dim=-1), F.normalize(r(B, T, S), dim=-1)
+    a, p = torch.sigmoid(r(M, S)), F.softplus(r(M, S))
+    dy, dyv = r(B, T, M), r(B, T, M)
+    full = [v, lv, k, q, a, p]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run(ins, groups, gy, gyv, chunks=None):
+        leaves = [t.detach().requires_grad_(True) for t in ins]
+        if groups is None:
+            y, yv, _ = kla_b200.kla_scan_b200(*leaves, time_chunks=chunks)
+        else:
+            y, yv, _ = shard.scan_block(kla_b200.kla_scan_b200, groups, *leaves)
+        return (y, yv) + torch.autograd.grad([y, yv], leaves, [gy, gyv])
+
+    ref = run(full, None, dy, dyv, chunks=1)
+    t1 = _event_time(lambda: run(full, None, dy, dyv, chunks=1), steps, 3, barrier)
+
+    blk = shard.block_of(B, M, world, rank)
+    groups = shard.make_groups(world, blk.batch_parts, blk.channel_parts) if world > 1 else shard.Groups(None, None)
+    bs, ms = slice(blk.b0, blk.b1), slice(blk.m0, blk.m1)
+    mine = [v[bs, :, ms].contiguous(), lv[bs, :, ms].contiguous(), k[bs].contiguous(), q[bs].contiguous(),
+            a[ms].contiguous(), p[ms].contiguous()]
+    dyb, dyvb = dy[bs, :, ms].contiguous(), dyv[bs, :, ms].contiguous()
+    out = run(mine, groups, dyb, dyvb)
+    tn = _event_time(lambda: run(mine, groups, dyb, dyvb), steps, 3, barrier)
+
+    y, yv, dv, dlv, dk, dq, da, dp = out
+    ry, ryv, rdv, rdlv, rdk, rdq, rda, rdp = ref
+    elem = max(_dev_ratio(y, ry[bs, :, ms]), _dev_ratio(yv, ryv[bs, :, ms]), _dev_ratio(dv, rdv[bs, :, ms]),
+               _dev_ratio(dlv, rdlv[bs, :, ms]))
+    red = max(_dev_rel(dk, rdk[bs]), _dev_rel(dq, rdq[bs]), _dev_rel(da, rda[ms]), _dev_rel(dp, rdp[ms]))
+    tm = torch.tensor([tn, t1, elem, red], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+    tn, t1, elem, red = tm.tolist()
+    Bb, Mb = blk.b1 - blk.b0, blk.m1 - blk.m0
+    return {
+        "workload": f"ONE problem B={B} T={T} M={M} S={S} fp32 split over {world} rank(s): {blk.batch_parts} batch x "
+                    f"{blk.channel_parts} channel blocks of B={Bb}, M={Mb}; forward + backward + all-reduces of da, dp "
+                    f"(batch group) and dk, dq (channel group) timed together",
+        "scaling": "strong", "ms_per_step": tn, "tokens_per_s": B * T / (tn * 1e-3),
+        "one_gpu_ms_per_step": t1, "efficiency": t1 / (world * tn),
+        "time_chunks_per_rank": ops.pick_time_chunks(Bb, T, Mb, S),
+        "parity": {"elementwise_max_ratio_of_rtol1e-5_atol1e-6": elem, "reduced_gradients_max_rel_err": red,
+                   "against": "the same problem scanned whole on one GPU by the lane-serial kernels"},
+        "steps": steps,
+    }
+
+
+def seqshard_block(dev, rank, world, steps):
+    """The long sequence (B=2, T=131072, M=4096, S=16, bfloat16 I/O, float32 state) split into `world` time slabs,
+    forward + backward through kla_scan_seq_sharded, with its all-gathers and all-reduces inside the timed region.
+    Parity: the same slabs scanned one after the other by the plain kernels, the state handed from rank to rank
+    (and the state gradient back) with point-to-point copies -- what one GPU would compute sequentially."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    import kla_b200
+
+    B, T, M, S = 2, 131072, 4096, 16
+    Ls = T // world
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    bf = torch.bfloat16
+    r = lambda *sh: torch.randn(*sh, device=dev, generator=g)
+    v, lv = r(B, Ls, M).to(bf), (1.0 / F.softplus(r(B, Ls, M))).to(bf)
+    k, q = F.normalize(r(B, Ls, S), dim=-1).to(bf), F.normalize(r(B, Ls, S), dim=-1).to(bf)
+    g0 = torch.Generator(device=dev).manual_seed(1234)  # a, p are shared by all ranks
+    a = torch.sigmoid(torch.randn(M, S, generator=g0, device=dev))
+    p = F.softplus(torch.randn(M, S, generator=g0, device=dev))
+    dy, dyv = r(B, Ls, M).to(bf), r(B, Ls, M).to(bf)
+    ins = [t.requires_grad_(True) for t in (v, lv, k, q, a, p)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        y, yv, st = kla_b200.kla_scan_seq_sharded(*ins, out_dtype=bf)
+        return (y, yv, st) + torch.autograd.grad([y, yv], ins, [dy, dyv])
+
+    out = step()
+    ms = _event_time(step, steps, 2, barrier)
+
+    # the same slabs, scanned one after the other by the plain kernels
+    f32 = dict(device=dev, dtype=torch.float32)
+    init = None
+    if rank > 0:
+        lam_in, eta_in = torch.empty(B, M, S, **f32), torch.empty(B, M, S, **f32)
+        dist.recv(lam_in, src=rank - 1)
+        dist.recv(eta_in, src=rank - 1)
+        init = (lam_in.requires_grad_(True), eta_in.requires_grad_(True))
+    leaves = [t.detach().requires_grad_(True) for t in ins]
+    y2, yv2, st2 = kla_b200.kla_scan_b200(*leaves, initial_state=init, out_dtype=bf, time_chunks=1)
+    if rank < world - 1:
+        dist.send(st2.lam.detach().contiguous(), dst=rank + 1)
+        dist.send(st2.eta.detach().contiguous(), dst=rank + 1)
+        dl, de = torch.empty(B, M, S, **f32), torch.empty(B, M, S, **f32)
+        dist.recv(dl, src=rank + 1)
+        dist.recv(de, src=rank + 1)
+    else:
+        dl, de = torch.zeros(B, M, S, **f32), torch.zeros(B, M, S, **f32)
+    g2 = torch.autograd.grad([y2, yv2, st2.lam, st2.eta], leaves + (list(init) if init else []), [dy, dyv, dl, de])
+    if rank > 0:
+        dist.send(g2[6].contiguous(), dst=rank - 1)
+        dist.send(g2[7].contiguous(), dst=rank - 1)
+    da2, dp2 = g2[4].clone(), g2[5].clone()
+    if world > 1:
+        dist.all_reduce(da2)
+        dist.all_reduce(dp2)
+    y, yv, st, dv, dlv, dk, dq, da, dp = out
+    dev_out = max(_dev_rel(y, y2), _dev_rel(yv, yv2))
+    dev_grad = max(_dev_rel(dv, g2[0]), _dev_rel(dlv, g2[1]), _dev_rel(dk, g2[2]), _dev_rel(dq, g2[3]),
+                   _dev_rel(da, da2), _dev_rel(dp, dp2))
+    dev_state = max(_dev_rel(st.lam, st2.lam), _dev_rel(st.eta, st2.eta)) if rank == world - 1 else 0.0
+    tm = torch.tensor([ms, dev_out, dev_grad, dev_state], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+    ms, dev_out, dev_grad, dev_state = tm.tolist()
+    fb, bb = algorithmic_bytes_per_token(M, S, esz=2)
+    peak, _ = peaks()
+    return {
+        "workload": f"sequence-sharded KLA scan fwd+bwd, B={B} T={T} M={M} S={S}, bf16 I/O, float32 state, time split "
+                    f"into {world} slabs of {Ls} steps; slab aggregates, NCCL all-gathers and the da, dp all-reduce inside "
+                    f"the timed region",
+        "scaling": "strong", "ms_per_step": ms, "tokens_per_s": B * T / (ms * 1e-3), "steps": steps,
+        "roofline_frac_per_gpu": (fb + bb) * B * T / world / (ms * 1e-3) / 1e9 / peak,
+        "parity": {"outputs_max_rel_err": dev_out, "gradients_max_rel_err": dev_grad, "final_state_max_rel_err": dev_state,
+                   "against": "the slabs scanned one after the other by the plain kernels, state and state gradient "
+                              "handed from rank to rank (bf16 outputs: one rounding step is 4e-3 relative)"},
+    }
+
+
 def run_seqshard(args):
-    """Secondary workload (not the default line): BASELINE config 5, the long
+    """Secondary workload (not the default line): the long
     sequence split into time slabs over the ranks -- B=2, T=131072, M=4096, S=16,
     bfloat16 I/O with float32 state, forward + backward through
     ``kla_scan_seq_sharded`` (slab aggregates, NCCL all-gathers, fused scans).
@@ -451,7 +756,7 @@ def run_seqshard(args):
 
 
 def run_decode(args):
-    """Secondary workload: the single-token decode step of BASELINE config 3
+    """Secondary workload: the single-token decode step of the prefill-then-decode configuration
     (B=32, M=2048, S=16, float32 state updated in place), 256 steps per timed
     pass through the C ABI. State-bound: per step every lane's (lam, eta) is read
     and written (16 B) and a, p are read (8 B per (m, s), shared over the batch)."""
@@ -598,7 +903,7 @@ def run_rawpair(args):
                                "four launches per step (Moebius fwd, bwd, affine fwd, bwd)",
                    "l2": f"each launch streams {5 * 4 * B * T * N / 1e9:.1f}-{10 * 4 * B * T * N / 1e9:.1f} GB, far beyond the 126 MB L2"},
         "roofline": {"bound": "hbm", "kernel": "kla_rawscan_kernel<MobiusBwd>", "achieved": per[top]["achieved"],
-                     "peak": peak, "unit": "GB/s", "frac": per[top]["frac"], "traffic": NCU_TRAFFIC["rawscan_mobius_bwd_per_batch"] * B,
+                     "peak": peak, "unit": "GB/s", "frac": per[top]["frac"], "traffic": NCU_TRAFFIC["rawscan_mobius_bwd_per_batch"] * B if "rawscan_mobius_bwd_per_batch" in NCU_TRAFFIC else None,
                      "peak_source": src, "algorithmic_bytes": per[top]["algorithmic_bytes"], "ms": per[top]["ms"]},
         "roofline_all": per,
         "step_gbs": all_bytes / (total_ms / args.steps * 1e-3) / 1e9,

@@ -21,7 +21,8 @@ def _worker(rank, world, port, mode, q):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        B, L, M, S = 2, 96, 64, 16
+        # "block1": one batch element, so the two ranks split the CHANNELS and dk, dq are all-reduced over NCCL
+        B, L, M, S = (1 if mode == "block1" else 2), 96, 64, 16
         g = _seeded(B, L, M, S, seed=77)
         t = lambda n: torch.tensor(g[n], dtype=torch.float32, device=dev)
         full = [t(n).requires_grad_(True) for n in INPUTS]
@@ -60,15 +61,18 @@ def _worker(rank, world, port, mode, q):
             gr = torch.autograd.grad(loss, full + [lam0, eta0])
             out["y"] = (y - y_ref[bs, :, ms]).abs().max().item()
             out["dv"] = ((gr[0][bs, :, ms] - g_ref[0][bs, :, ms]).abs().max() / (g_ref[0].abs().max() + 1)).item()
+            assert (blk.batch_parts, blk.channel_parts) == ((1, 2) if mode == "block1" else (2, 1))
             out["dk"] = ((gr[2][bs] - g_ref[2][bs]).abs().max() / (g_ref[2].abs().max() + 1)).item()
+            out["dq"] = ((gr[3][bs] - g_ref[3][bs]).abs().max() / (g_ref[3].abs().max() + 1)).item()
             out["da"] = ((gr[4][ms] - g_ref[4][ms]).abs().max() / (g_ref[4].abs().max() + 1)).item()
+            out["dp"] = ((gr[5][ms] - g_ref[5][ms]).abs().max() / (g_ref[5].abs().max() + 1)).item()
         torch.cuda.synchronize()
         q.put((rank, out))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["seq", "block"])
+@pytest.mark.parametrize("mode", ["seq", "block", "block1"])
 def test_two_gpu_sharding_matches_one_shot(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -76,7 +80,7 @@ def test_two_gpu_sharding_matches_one_shot(mode):
 
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 32500 + (os.getpid() % 2000) + (0 if mode == "seq" else 1)
+    port = 32500 + (os.getpid() % 2000) + ["seq", "block", "block1"].index(mode)
     procs = [ctx.Process(target=_worker, args=(r, 2, port, mode, q)) for r in range(2)]
     [p.start() for p in procs]
     res = [q.get(timeout=300) for _ in procs]
