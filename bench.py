@@ -512,12 +512,12 @@ def _event_time(fn, steps, warm, barrier):
 
 def _dev_ratio(got, ref, rtol=1e-5, atol=1e-6):
     """max |got - ref| / (atol + rtol |ref|), on the device."""
-    got, ref = got.double(), ref.double()
+    got, ref = got.detach().double(), ref.detach().double()
     return float(((got - ref).abs() / (atol + rtol * ref.abs())).max()) if ref.numel() else 0.0
 
 
 def _dev_rel(got, ref):
-    got, ref = got.double(), ref.double()
+    got, ref = got.detach().double(), ref.detach().double()
     return float((got - ref).abs().max() / (ref.abs().max() + 1.0)) if ref.numel() else 0.0
 
 
@@ -1078,6 +1078,54 @@ def run_prologue(args):
     }), flush=True)
 
 
+def run_epilogue(args):
+    """Secondary line: the scan with the layer's output path fused in for TRAINING (skip + gate applied at the forward
+    kernel's store, their adjoint as one memory-bound kernel before the scan's backward; kla_layer.py:329-338) beside
+    the same step with that path as the eager torch operations the reference layer issues and torch autograd's
+    backward of them; both through the public autograd API at the headline shape."""
+    import torch
+    import torch.nn.functional as F
+    import kla_b200
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, T, M, S = (args.batch or WORK["B"]), WORK["L"], WORK["M"], WORK["S"]
+    host = make_inputs(seed=0, **{**WORK, "B": B})
+    g = torch.Generator().manual_seed(7)
+    z, gate = torch.randn(B, T, M, generator=g).to(dev), torch.randn(B, T, M, generator=g).to(dev)
+    skip = torch.tensor(-1.0, device=dev)
+    d = {n: t.to(dev) for n, t in host.items()}
+    leaves = [d["v"], d["lambda_v"], d["k"], d["q"], d["a"], d["p"], z, gate, skip]
+
+    def fused():
+        ins = [t.detach().requires_grad_(True) for t in leaves]
+        y, yv, _ = kla_b200.kla_scan_b200(*ins[:6], epilogue=dict(z=ins[6], gate=ins[7], lambda_skip=ins[8]))
+        return torch.autograd.grad([y, yv], ins, [d["dy"], d["dyvar"]])
+
+    def eager():
+        ins = [t.detach().requires_grad_(True) for t in leaves]
+        y, yv, _ = kla_b200.kla_scan_b200(*ins[:6])
+        y = y + ins[8] * ins[6]
+        gg = F.silu(ins[7])
+        y, yv = y * gg, yv * gg.pow(2)
+        return torch.autograd.grad([y, yv], ins, [d["dy"], d["dyvar"]])
+
+    gf, ge = fused(), eager()
+    diff = max(float((a_ - b_).abs().max() / (b_.abs().max() + 1e-12)) for a_, b_ in zip(gf, ge))
+    sync = torch.cuda.synchronize
+    ms_f = _event_time(fused, args.steps, max(args.warmup, 3), sync)
+    ms_e = _event_time(eager, args.steps, max(args.warmup, 3), sync)
+    print(json.dumps({
+        "metric": "KLA scan fwd+bwd with fused skip/gate epilogue, tokens/s", "value": B * T / (ms_f * 1e-3), "unit": UNIT,
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_f, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"raw KLA scan fwd+bwd through autograd, B={B} T={T} M={M} S={S}, with y += skip*z, y *= silu(gate), "
+                               "y_var *= silu(gate)^2 and the gradients of z, gate, skip",
+                   "ms_fused": ms_f, "ms_eager_epilogue": ms_e, "speedup_vs_eager_epilogue": ms_e / ms_f,
+                   "max_rel_diff_of_gradients": diff},
+    }), flush=True)
+
+
 def run_inference(args):
     """Secondary line: the inference route of one layer at the decode configuration (batch 32,
     d_model 1024 -> M = 2048, S = 16, bf16): a prompt of 8192 tokens through LayerDecoder.prefill
@@ -1167,6 +1215,154 @@ def run_inference(args):
     }), flush=True)
 
 
+def run_reference_gpu(args):
+    """Secondary workload: the reference's OWN GPU backends on this GPU, on the headline raw-op shape, forward +
+    backward through ``kla.ops.kla_scan(..., backend=...)`` (unmodified copy under baseline/_ref): ``triton`` (its
+    tiled Moebius and affine scans composed with torch operations, src/kla/ops/triton_backend.py:125-171) and ``cuda``
+    (its fused CUDA kernel, JIT-compiled on first use, src/kla/ops/cuda_backend.py:158-236; its gradients through the
+    precision scan are approximate by design). One JSON line per backend, ``impl: reference-<backend>``; a backend
+    that cannot run here prints ``unavailable`` with the reason. Each runs in a child process with a time limit, so a
+    build or a kernel that goes wrong there ends that child only."""
+    if reference_dir() is None:
+        print(json.dumps({"impl": "reference-gpu", "unavailable": "the reference is not installed under baseline/_ref"}))
+        return
+    for backend in ("triton", "cuda"):
+        cmd = [sys.executable, os.path.abspath(__file__), "--workload", "_reference_gpu_child", "--backend", backend,
+               "--steps", str(min(args.steps, 10)), "--warmup", str(args.warmup)]
+        try:
+            res = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+            lines = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+            if res.returncode == 0 and lines:
+                print(lines[-1], flush=True)
+            else:
+                tail = (res.stderr or res.stdout).strip().splitlines()[-1:] or ["no output"]
+                print(json.dumps({"impl": f"reference-{backend}", "unavailable": f"exit {res.returncode}: {tail[0][:300]}"}), flush=True)
+        except subprocess.TimeoutExpired:
+            print(json.dumps({"impl": f"reference-{backend}", "unavailable": "no result within 900 s"}), flush=True)
+
+
+def run_reference_gpu_child(args):
+    import torch
+
+    sys.path.insert(0, reference_dir())
+    from kla.ops import kla_scan
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    B = WORK["B"]
+    while True:
+        try:
+            host = make_inputs(seed=0, **{**WORK, "B": B})
+            d = {n: t.to(dev) for n, t in host.items()}
+            ins = [d[n].requires_grad_(True) for n in ("v", "lambda_v", "k", "q", "a", "p")]
+
+            def step():
+                y, y_var, _ = kla_scan(*ins, backend=args.backend)
+                return torch.autograd.grad([y, y_var], ins, [d["dy"], d["dyvar"]])
+
+            step()
+            break
+        except torch.OutOfMemoryError:
+            del d, ins
+            torch.cuda.empty_cache()
+            if B == 1:
+                raise
+            B //= 2
+    for _ in range(max(args.warmup, 1)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({
+        "impl": f"reference-{args.backend}", "metric": METRIC, "value": B * WORK["L"] / (ms * 1e-3), "unit": UNIT,
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"raw KLA scan fwd+bwd through the reference's kla_scan(backend='{args.backend}'), B={B} "
+                               f"T=4096 M=1024 S=16, fp32" + ("" if B == WORK["B"] else " (largest batch that fits its temporaries)"),
+                   **{**WORK, "B": B}},
+        "peak_memory_gb": torch.cuda.max_memory_allocated() / 1e9,
+    }), flush=True)
+
+
+def run_train_step(args):
+    """Secondary workload: the reference's ``SequenceModel(ModelConfig(vocab 50304, d_model 768, 12 layers),
+    KLAConfig(d_state=16))`` training step (forward + backward, bf16 autocast, random weights, uniform random token
+    ids, batch 16 x T=2048 split over the ranks, DistributedDataParallel over NCCL) with the scan on the ``b200``
+    backend; the layers, the model and DDP are the reference's and torch's own. ``--backend triton`` runs the same step
+    on the reference's Triton backend for comparison (at the largest per-GPU batch its temporaries fit)."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    if reference_dir() is None:
+        print(json.dumps({"workload": "train_step", "unavailable": "the reference is not installed under baseline/_ref"}))
+        return
+    sys.path.insert(0, reference_dir())
+    import kla_b200
+    from kla import KLAConfig, ModelConfig, SequenceModel
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    backend = args.backend or "b200"
+    if backend == "b200":
+        kla_b200.register()
+    GB, T, V = 16, 2048, 50304
+    Bl = max(1, GB // world)
+    if args.batch:
+        Bl = args.batch
+    torch.manual_seed(0)
+    model = SequenceModel(ModelConfig(vocab_size=V, d_model=768, n_layers=12), KLAConfig(d_state=16, backend=backend)).to(dev)
+    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
+    ids = torch.randint(0, V, (Bl, T + 1), device=dev, generator=torch.Generator(device=dev).manual_seed(1 + rank))
+    lib = __import__("importlib").import_module("kalman-linear-attention_b200._lib")
+
+    def step():
+        net.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            logits = net(ids[:, :-1])
+        loss = F.cross_entropy(logits.reshape(-1, V).float(), ids[:, 1:].reshape(-1))
+        loss.backward()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    loss = step()
+    n0 = lib.load().kla_b200_launch_count()
+    ms = _event_time(step, args.steps, max(args.warmup, 2), barrier)
+    launches = (lib.load().kla_b200_launch_count() - n0) / (args.steps + max(args.warmup, 2))
+    tm = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+    ms = tm.item()
+    if rank == 0:
+        print(json.dumps({
+            "workload": "train_step", "metric": "SequenceModel training step tokens/s", "value": Bl * world * T / (ms * 1e-3),
+            "unit": UNIT, "n_gpus": world, "steps": args.steps, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong" if not args.batch else "weak", "dtype": "bf16 autocast, float32 scan", "data": "synthetic",
+            "config": {"workload": f"SequenceModel(vocab 50304, d_model 768, 12 layers, d_state 16) fwd+bwd, batch {Bl} per GPU x "
+                                   f"T={T}, scan backend '{backend}', DDP over {world} rank(s)",
+                       "global_batch": Bl * world, "seq_len": T, "parallelism": f"dp{world}"},
+            "loss": float(loss), "scan_kernel_launches_per_step": launches,
+            "peak_memory_gb": torch.cuda.max_memory_allocated() / 1e9,
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1180,10 +1376,18 @@ def main():
     ap.add_argument("--batch", type=int, default=0,
                     help="raw workload only: batch size per GPU instead of 8, for the occupancy sweep "
                          "(B=4 leaves one CTA per SM, B=16 fills every SM); the headline stays B=8")
-    ap.add_argument("--workload", default="raw", choices=["raw", "seqshard", "decode", "rawpair", "decode_layer", "prologue", "inference"],
+    ap.add_argument("--backend", default="", help="reference_gpu child / train_step: the scan backend to run")
+    ap.add_argument("--workload", default="raw", choices=["raw", "seqshard", "decode", "rawpair", "decode_layer", "prologue", "epilogue", "inference",
+                                                          "reference_gpu", "_reference_gpu_child", "train_step"],
                     help="raw = the headline raw-op workload (default); seqshard = the long-sequence, "
                          "time-sharded workload (secondary line)")
     args = ap.parse_args()
+    if args.workload == "reference_gpu":
+        return run_reference_gpu(args)
+    if args.workload == "_reference_gpu_child":
+        return run_reference_gpu_child(args)
+    if args.workload == "train_step":
+        return run_train_step(args)
     if args.batch > 0:
         WORK["B"] = args.batch
     if args.workload == "seqshard" and args.impl != "reference":
@@ -1196,6 +1400,8 @@ def main():
         return run_decode_layer(args)
     if args.workload == "prologue" and args.impl != "reference":
         return run_prologue(args)
+    if args.workload == "epilogue" and args.impl != "reference":
+        return run_epilogue(args)
     if args.workload == "inference" and args.impl != "reference":
         return run_inference(args)
     if args.impl == "reference":

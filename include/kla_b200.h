@@ -90,16 +90,19 @@ typedef struct kla_b200_fwd_args {
      * (no ceiling when obs_var_max <= 0), in float32 whatever in_dtype is. */
     int32_t lambda_v_is_log_variance;
     float obs_var_min, obs_var_max;
-    /* Fused layer epilogue, forward only (src/kla/layers/kla_layer.py:329-338):
+    /* Fused layer epilogue (src/kla/layers/kla_layer.py:329-338):
      * y += lambda_skip * z (when lambda_skip_len is 1 or M; z: [B, L, M] in
      * in_dtype), then y *= g, y_var *= g^2 with g = act(gate) (when gate.ptr is
-     * not NULL; KLA_B200_ACT_*). For inference (prefill): refused with
-     * KLA_B200_EUNSUPPORTED together with ckpt != NULL, because the backward
-     * kernel has no counterpart for it. */
+     * not NULL; KLA_B200_ACT_*). When a backward will follow (ckpt != NULL) the
+     * scan's own outputs, before skip and gate, must also be kept for the
+     * epilogue's adjoint (kla_b200_epilogue_bwd): y_raw, y_var_raw, [B, L, M] in
+     * out_dtype; without them the combination is refused with
+     * KLA_B200_EUNSUPPORTED. */
     kla_b200_tensor3 z, gate;
     const float *lambda_skip;
     int32_t lambda_skip_len;
     int32_t gate_activation;
+    kla_b200_tensor3 y_raw, y_var_raw; /* out, or ptr NULL */
 } kla_b200_fwd_args;
 
 /* Bytes of the checkpoint scratch the forward writes for the backward:
@@ -201,6 +204,33 @@ typedef struct kla_b200_slab_args {
 } kla_b200_slab_args;
 
 int kla_b200_slab_aggregate(const kla_b200_slab_args *args, void *stream);
+
+/*
+ * Adjoint of the fused layer epilogue. Replaces what torch autograd does for
+ * the reference layer's output path (src/kla/layers/kla_layer.py:329-338:
+ * y + lambda_skip * z, then the gate on y and its square on y_var). One
+ * memory-bound pass: from the gradients of the gated outputs it forms the
+ * gradients kla_b200_scan_bwd takes as dy, dy_var, plus dz, dgate and
+ * dlambda_skip (accumulated with atomic adds after the library zeroes it).
+ * z/dz and lambda_skip, or gate/dgate, are NULL when that half of the path is
+ * absent. Activation tensors (z, gate, dz, dgate) are in_dtype, the others
+ * out_dtype, as in the forward.
+ */
+typedef struct kla_b200_epilogue_bwd_args {
+    int64_t B, L, M;
+    int32_t in_dtype, out_dtype;
+    int32_t gate_activation;        /* KLA_B200_ACT_* */
+    int32_t lambda_skip_len;        /* 0 (none), 1 or M */
+    kla_b200_tensor3 dout, dout_var; /* in  [B, L, M]; dout_var.ptr may be NULL = zero */
+    kla_b200_tensor3 y_raw, y_var_raw; /* in: what the forward stored */
+    kla_b200_tensor3 z, gate;       /* in, as in the forward */
+    const float *lambda_skip;       /* in  [lambda_skip_len] */
+    kla_b200_tensor3 dy, dy_var;    /* out [B, L, M], out_dtype */
+    kla_b200_tensor3 dz, dgate;     /* out [B, L, M], in_dtype */
+    float *dlambda_skip;            /* out [lambda_skip_len] float32 */
+} kla_b200_epilogue_bwd_args;
+
+int kla_b200_epilogue_bwd(const kla_b200_epilogue_bwd_args *args, void *stream);
 
 /*
  * Fold of per-chunk aggregates for the time-parallel scan on one GPU. The

@@ -24,6 +24,7 @@ SYMBOLS = (
     "kla_b200_step",
     "kla_b200_slab_aggregate",
     "kla_b200_chunk_fold",
+    "kla_b200_epilogue_bwd",
     "kla_b200_conv_step",
     "kla_b200_conv_seq",
     "kla_b200_step_layer",
@@ -98,6 +99,17 @@ class FwdArgs(Structure):
         ("lambda_v_is_log_variance", c_int32), ("obs_var_min", c_float), ("obs_var_max", c_float),
         ("z", Tensor3), ("gate", Tensor3), ("lambda_skip", c_void_p),
         ("lambda_skip_len", c_int32), ("gate_activation", c_int32),
+        ("y_raw", Tensor3), ("y_var_raw", Tensor3),
+    ]
+
+
+class EpilogueBwdArgs(Structure):
+    _fields_ = [
+        ("B", c_int64), ("L", c_int64), ("M", c_int64),
+        ("in_dtype", c_int32), ("out_dtype", c_int32), ("gate_activation", c_int32), ("lambda_skip_len", c_int32),
+        ("dout", Tensor3), ("dout_var", Tensor3), ("y_raw", Tensor3), ("y_var_raw", Tensor3),
+        ("z", Tensor3), ("gate", Tensor3), ("lambda_skip", c_void_p),
+        ("dy", Tensor3), ("dy_var", Tensor3), ("dz", Tensor3), ("dgate", Tensor3), ("dlambda_skip", c_void_p),
     ]
 
 
@@ -177,6 +189,8 @@ def load() -> ctypes.CDLL:
     lib.kla_b200_scan_bwd.argtypes = [POINTER(BwdArgs), c_void_p]
     lib.kla_b200_slab_aggregate.restype = c_int
     lib.kla_b200_slab_aggregate.argtypes = [POINTER(SlabArgs), c_void_p]
+    lib.kla_b200_epilogue_bwd.restype = c_int
+    lib.kla_b200_epilogue_bwd.argtypes = [POINTER(EpilogueBwdArgs), c_void_p]
     lib.kla_b200_chunk_fold.restype = c_int
     lib.kla_b200_chunk_fold.argtypes = [POINTER(ChunkFoldArgs), c_void_p]
     for name in ("mobius_scan_fwd", "mobius_scan_bwd", "affine_scan_fwd", "affine_scan_bwd"):

@@ -34,7 +34,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
 ]  # no --split-compile: with it the optimiser's result (and the kernels' speed) varied from build to build
 
-_SCAN_DEPS = ["kla_common.cuh", "kla_fwd.cuh", "kla_bwd.cuh", "kla_launch.cuh", "kla_scan_inst.cu"]
+_SCAN_DEPS = ["kla_common.cuh", "kla_fwd.cuh", "kla_bwd.cuh", "kla_agg.cuh", "kla_launch.cuh", "kla_scan_inst.cu"]
 
 
 def _units():
@@ -45,6 +45,7 @@ def _units():
             for lp, lname in ((0, "lo"), (1, "hi")):
                 flags = [f"-DKLA_INST_KIND={kind}", f"-DKLA_INST_DT={dt}", f"-DKLA_INST_LPCS={lp}"]
                 units.append((f"scan_{kname}_{dname}_{lname}", "kla_scan_inst.cu", flags, _SCAN_DEPS))
+    units.append(("scan_agg", "kla_scan_inst.cu", ["-DKLA_INST_KIND=2"], _SCAN_DEPS))
     return units
 
 

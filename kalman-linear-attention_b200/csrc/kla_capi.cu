@@ -8,6 +8,7 @@
 
 #include "../../include/kla_b200.h"
 #include "kla_decode.cuh"
+#include "kla_epilogue.cuh"
 #include "kla_launch.cuh"
 #include "kla_rawscan.cuh"
 #include "kla_slab.cuh"
@@ -204,18 +205,21 @@ int dispatch_fwd(int din, int dout, bool prior, int lpc, FwdParams &prm, const k
 int dispatch_bwd(int din, int dout, bool prior, int lpc, BwdParams &prm, const kla_b200_bwd_args &a, cudaStream_t st) {
     KLA_DISPATCH(prep_bwd, din, dout, prior, lpc, prm, a, st);
 }
+// Tensor maps of the aggregate kernel's tiles, then the launch.
 template <typename T, typename TO, int LPC, bool PRIOR>
-int launch_slab(const SlabParams &prm, bool adjoint, cudaStream_t st) {
-    constexpr int MC = 4 * (32 / LPC);
-    dim3 grid((unsigned)((prm.M + MC - 1) / MC), (unsigned)prm.B);
-    if (adjoint) kla_slab_aggregate_kernel<T, TO, kSPT, LPC, true, PRIOR><<<grid, 128, 0, st>>>(prm);
-    else kla_slab_aggregate_kernel<T, TO, kSPT, LPC, false, false><<<grid, 128, 0, st>>>(prm);
+int prep_agg(AggParams &prm, const kla_b200_slab_args &a, cudaStream_t st) {
+    const int mc = agg_channels_per_cta(LPC);
+    const bool adj = a.adjoint != 0;
+    prm.use_tma = !g_no_tma && a.L > 0 && make_tile_map<T>(&prm.tm_v, a.v, a.B, a.L, a.M, mc, kAggTT) &&
+                  make_tile_map<T>(&prm.tm_lv, a.lambda_v, a.B, a.L, a.M, mc, kAggTT) &&
+                  (!adj || (make_tile_map<TO>(&prm.tm_dy, a.dy, a.B, a.L, a.M, mc, kAggTT) &&
+                            (a.dy_var.ptr == nullptr || make_tile_map<TO>(&prm.tm_dyv, a.dy_var, a.B, a.L, a.M, mc, kAggTT))));
+    const cudaError_t e = launch_agg<T, TO, LPC, PRIOR>(prm, adj, st);
     g_launches++;
-    cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
 }
-int dispatch_slab(int din, int dout, bool prior, int lpc, const SlabParams &prm, bool adjoint, cudaStream_t st) {
-    KLA_DISPATCH(launch_slab, din, dout, prior, lpc, prm, adjoint, st);
+int dispatch_slab(int din, int dout, bool prior, int lpc, AggParams &prm, const kla_b200_slab_args &a, cudaStream_t st) {
+    KLA_DISPATCH(prep_agg, din, dout, prior, lpc, prm, a, st);
 }
 int dispatch_step(int din, int dout, bool prior, int lpc, const StepParams &prm, cudaStream_t st) {
     KLA_DISPATCH(launch_step, din, dout, prior, lpc, prm, st);
@@ -328,7 +332,14 @@ int kla_b200_scan_fwd(const kla_b200_fwd_args *a, void *stream) {
     {
         const bool has_skip = a->lambda_skip_len != 0, has_gate = a->gate.ptr != nullptr;
         if (has_skip || has_gate) {
-            if (a->ckpt != nullptr) return KLA_B200_EUNSUPPORTED;  // forward only
+            // with a backward to follow, the scan's own outputs must be kept for the epilogue's adjoint
+            // (the gate's adjoint reads them; the skip path alone does not)
+            if (a->ckpt != nullptr && has_gate && (a->y_raw.ptr == nullptr || a->y_var_raw.ptr == nullptr)) return KLA_B200_EUNSUPPORTED;
+            if ((a->y_raw.ptr == nullptr) != (a->y_var_raw.ptr == nullptr)) return KLA_B200_EINVAL;
+            if (a->y_raw.ptr != nullptr) {
+                if ((rc = check_t3(a->y_raw, osz, true)) || (rc = check_t3(a->y_var_raw, osz, true))) return rc;
+                prm.y_raw = t3(a->y_raw); prm.yv_raw = t3(a->y_var_raw);
+            }
             if (has_skip && ((a->lambda_skip_len != 1 && a->lambda_skip_len != a->M) || !a->lambda_skip || !a->z.ptr))
                 return KLA_B200_EINVAL;
             if (a->gate_activation < KLA_B200_ACT_SILU || a->gate_activation > KLA_B200_ACT_NONE) return KLA_B200_EINVAL;
@@ -417,13 +428,77 @@ int kla_b200_slab_aggregate(const kla_b200_slab_args *a, void *stream) {
                            (rc = check_t3(a->dy_var, osz, false))))
             return rc;
     }
-    SlabParams prm{};
+    AggParams prm{};
     prm.B = (int)a->B; prm.L = (int)a->L; prm.M = (int)a->M; prm.S = (int)a->S;
     prm.v = t3(a->v); prm.lv = t3(a->lambda_v); prm.k = t3(a->k); prm.q = t3(a->q);
     prm.dy = t3(a->dy); prm.dyv = t3(a->dy_var);
     prm.a = a->a; prm.p = a->p; prm.lam0 = a->lam0; prm.eta0 = a->eta0; prm.out = a->out;
-    return dispatch_slab(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc_for(a->S), prm, a->adjoint != 0,
+    if ((rc = wait_ctl(&prm.wait))) return rc;
+    prm.wait.skip_tile = -1;  // the hook is for the scan kernels
+    return dispatch_slab(a->in_dtype, a->out_dtype, a->decode_from_prior != 0, lpc_for(a->S), prm, *a,
                          static_cast<cudaStream_t>(stream));
+}
+
+int kla_b200_epilogue_bwd(const kla_b200_epilogue_bwd_args *a, void *stream) {
+    if (a == nullptr || a->B < 0 || a->L < 0 || a->M < 0) return KLA_B200_EINVAL;
+    if (a->in_dtype != KLA_B200_F32 && a->in_dtype != KLA_B200_BF16) return KLA_B200_EUNSUPPORTED;
+    if (a->out_dtype != KLA_B200_F32 && a->out_dtype != KLA_B200_BF16) return KLA_B200_EUNSUPPORTED;
+    if (a->in_dtype == KLA_B200_F32 && a->out_dtype == KLA_B200_BF16) return KLA_B200_EUNSUPPORTED;
+    if (a->B > 65535 || a->L > (1 << 30) || a->M > (1 << 30)) return KLA_B200_EUNSUPPORTED;
+    if (a->gate_activation < KLA_B200_ACT_SILU || a->gate_activation > KLA_B200_ACT_NONE) return KLA_B200_EINVAL;
+    const bool has_skip = a->lambda_skip_len != 0, has_gate = a->gate.ptr != nullptr;
+    if (has_skip && ((a->lambda_skip_len != 1 && a->lambda_skip_len != a->M) || !a->lambda_skip || !a->dlambda_skip)) return KLA_B200_EINVAL;
+    const size_t esz = a->in_dtype == KLA_B200_F32 ? 4 : 2, osz = a->out_dtype == KLA_B200_F32 ? 4 : 2;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    if (has_skip && (e = cudaMemsetAsync(a->dlambda_skip, 0, sizeof(float) * (size_t)a->lambda_skip_len, st)) != cudaSuccess)
+        return cuda_fail(e);
+    if (a->B == 0 || a->L == 0 || a->M == 0) return KLA_B200_OK;
+    int rc;
+    if ((rc = check_t3(a->dout, osz, true)) || (rc = check_t3(a->dout_var, osz, false)) || (rc = check_t3(a->dy, osz, true)) ||
+        (rc = check_t3(a->dy_var, osz, true)))
+        return rc;
+    if (has_gate && ((rc = check_t3(a->gate, esz, true)) || (rc = check_t3(a->dgate, esz, true)) ||
+                     (rc = check_t3(a->y_raw, osz, true)) || (rc = check_t3(a->y_var_raw, osz, true))))
+        return rc;
+    if (has_skip && ((rc = check_t3(a->z, esz, true)) || (rc = check_t3(a->dz, esz, true)))) return rc;
+    const long long row_blocks = (a->L + kEpiRows - 1) / kEpiRows;
+    if (row_blocks > 65535) return KLA_B200_EUNSUPPORTED;
+    EpilogueBwdParams prm{};
+    prm.B = (int)a->B; prm.L = (int)a->L; prm.M = (int)a->M;
+    prm.dout = t3(a->dout); prm.dout_var = t3(a->dout_var); prm.y_raw = t3(a->y_raw); prm.yv_raw = t3(a->y_var_raw);
+    if (has_skip) { prm.z = t3(a->z); prm.dz = t3(a->dz); prm.skip = a->lambda_skip; prm.skip_len = a->lambda_skip_len; prm.dskip = a->dlambda_skip; }
+    if (has_gate) { prm.gate = t3(a->gate); prm.dgate = t3(a->dgate); prm.gate_act = a->gate_activation; }
+    prm.dy = t3(a->dy); prm.dy_var = t3(a->dy_var);
+    // four channels per thread when every tensor can be read and written as 4-element vectors
+    auto vec_ok = [&](const kla_b200_tensor3 &t, size_t sz) {
+        return t.ptr == nullptr || (aligned(t.ptr, 4 * sz) && t.stride_b % 4 == 0 && t.stride_t % 4 == 0);
+    };
+    const bool vec = a->M % 4 == 0 && vec_ok(a->dout, osz) && vec_ok(a->dout_var, osz) && vec_ok(a->dy, osz) &&
+                     vec_ok(a->dy_var, osz) && (!has_gate || (vec_ok(a->gate, esz) && vec_ok(a->dgate, esz) &&
+                     vec_ok(a->y_raw, osz) && vec_ok(a->y_var_raw, osz))) && (!has_skip || (vec_ok(a->z, esz) && vec_ok(a->dz, esz)));
+    const int per = vec ? 4 : 1;
+    dim3 grid((unsigned)((a->M + 128 * per - 1) / (128 * per)), (unsigned)row_blocks, (unsigned)a->B);
+#define KLA_EPI_LAUNCH(T, TO)                                                                                   \
+    do {                                                                                                        \
+        if (vec) {                                                                                              \
+            if (has_skip && has_gate) kla_epilogue_bwd_kernel<T, TO, 4, true, true><<<grid, 128, 0, st>>>(prm);  \
+            else if (has_skip) kla_epilogue_bwd_kernel<T, TO, 4, true, false><<<grid, 128, 0, st>>>(prm);        \
+            else kla_epilogue_bwd_kernel<T, TO, 4, false, true><<<grid, 128, 0, st>>>(prm);                      \
+        } else {                                                                                                \
+            if (has_skip && has_gate) kla_epilogue_bwd_kernel<T, TO, 1, true, true><<<grid, 128, 0, st>>>(prm);  \
+            else if (has_skip) kla_epilogue_bwd_kernel<T, TO, 1, true, false><<<grid, 128, 0, st>>>(prm);        \
+            else kla_epilogue_bwd_kernel<T, TO, 1, false, true><<<grid, 128, 0, st>>>(prm);                      \
+        }                                                                                                       \
+    } while (0)
+    if (!has_skip && !has_gate) return KLA_B200_EINVAL;  // nothing to differentiate
+    if (a->in_dtype == KLA_B200_F32) KLA_EPI_LAUNCH(float, float);
+    else if (a->out_dtype == KLA_B200_F32) KLA_EPI_LAUNCH(__nv_bfloat16, float);
+    else KLA_EPI_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+#undef KLA_EPI_LAUNCH
+    g_launches++;
+    e = cudaGetLastError();
+    return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
 }
 
 int kla_b200_chunk_fold(const kla_b200_chunk_fold_args *a, void *stream) {

@@ -55,6 +55,9 @@ struct alignas(64) FwdParams {
     // type, ptr == nullptr when absent; skip: one value or one per channel.
     Tensor3 z, gate;
     const float *skip;
+    // Training with the epilogue: the drainers also store the scan's own y, y_var (before skip and gate), which the
+    // epilogue's adjoint needs; ptr == nullptr when no backward will follow.
+    Tensor3 y_raw, yv_raw;
     int skip_len, gate_act, epilogue, epi_tma;
     WaitCtl wait;
     alignas(64) CUtensorMap tm_z, tm_gate;  // maps of the epilogue operands, like tm_v; valid when epi_tma
@@ -432,6 +435,15 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             const int dtid = htid - kProducers;
             TO *yb = static_cast<TO *>(prm.y.ptr) + (long long)b * prm.y.sb;
             TO *yvb = static_cast<TO *>(prm.yv.ptr) + (long long)b * prm.yv.sb;
+            float skip0 = 0.0f, skip1 = 0.0f;
+            if constexpr (EPI) {
+                static_assert(kDrainers % (MC / 2) == 0, "a drainer thread keeps its channel pair from tile to tile");
+                if (prm.skip != nullptr) {
+                    const int c0 = (dtid % (MC / 2)) * 2;
+                    skip0 = prm.skip[prm.skip_len > 1 ? min(m_cta + c0, M - 1) : 0];
+                    skip1 = prm.skip[prm.skip_len > 1 ? min(m_cta + c0 + 1, M - 1) : 0];
+                }
+            }
             for (int jt = 0; jt < NT; ++jt) {
                 const int o = jt % NO, t0 = jt * TT;
                 if (!mbar_wait(prm.wait, &full_out[o], (jt / NO) & 1, 4, 100)) { ok = false; break; }
@@ -439,14 +451,20 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                     const int e = jt % NE;
                     if (!mbar_wait(prm.wait, &epi_full[e], (jt / NE) & 1, 7, 100)) { ok = false; break; }
                     const T *zs = prm.z.ptr ? zstage(e) : nullptr, *gs = prm.gate.ptr ? gstage(e) : nullptr;
+                    TO *yr = prm.y_raw.ptr ? static_cast<TO *>(prm.y_raw.ptr) + (long long)b * prm.y_raw.sb + (long long)t0 * prm.y_raw.st : nullptr;
+                    TO *yvr = prm.y_raw.ptr ? static_cast<TO *>(prm.yv_raw.ptr) + (long long)b * prm.yv_raw.sb + (long long)t0 * prm.yv_raw.st : nullptr;
                     output_pass<TO, LPC, MC, MCP, TT, kDrainers>(
                         ystage(o), yb + (long long)t0 * prm.y.st, prm.y.st, prm.vec_y,
                         yvb + (long long)t0 * prm.yv.st, prm.yv.st, prm.vec_yv, min(TT, L - t0), m_cta, M, dtid,
                         [&](float2 acc, int tt, int c, float &o0, float &o1) {
                             const int m = m_cta + c;
                             if (m < M) {
-                                if (zs != nullptr)
-                                    acc.x = fmaf(prm.skip[prm.skip_len > 1 ? m : 0], to_f32<T>(zs[tt * MC + c]), acc.x);
+                                if (yr != nullptr) {  // the scan's own outputs, for the epilogue's adjoint
+                                    yr[(long long)tt * prm.y_raw.st + m] = from_f32<TO>(acc.x);
+                                    yvr[(long long)tt * prm.yv_raw.st + m] = from_f32<TO>(acc.y);
+                                }
+                                // a drainer thread meets the same pair of channels in every tile: its skip values are in registers
+                                if (zs != nullptr) acc.x = fmaf((c & 1) ? skip1 : skip0, to_f32<T>(zs[tt * MC + c]), acc.x);
                                 if (gs != nullptr) {
                                     const float g = activate_fast(to_f32<T>(gs[tt * MC + c]), prm.gate_act);
                                     acc.x *= g;

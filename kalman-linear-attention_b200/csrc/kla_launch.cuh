@@ -5,6 +5,7 @@
 // slices compile in parallel; kla_capi.cu only calls them.
 #pragma once
 
+#include "kla_agg.cuh"
 #include "kla_bwd.cuh"
 
 namespace kla {
@@ -30,11 +31,17 @@ constexpr int kCH = KLA_CH;            // channels per thread
 // channels per CTA of the scan kernels for a given number of lanes per channel
 inline int scan_channels_per_cta(int lpc) { return kNW * (32 / lpc) * kCH; }
 
+// channels per CTA of the aggregate kernel
+inline int agg_channels_per_cta(int lpc) { return kNW * (32 / lpc); }
+
 // Launch on `st` with the grid and shared memory of the instantiation; prm must be complete
 // (tensor maps included). Returns the launch's CUDA status.
 template <typename T, typename TO, int LPC, bool PRIOR>
 cudaError_t launch_fwd(const FwdParams &prm, cudaStream_t st);
 template <typename T, typename TO, int LPC, bool PRIOR>
 cudaError_t launch_bwd(const BwdParams &prm, cudaStream_t st);
+// adjoint: prm.q, dy, dyv, lam0, eta0 are used and PRIOR matters; otherwise the forward aggregate
+template <typename T, typename TO, int LPC, bool PRIOR>
+cudaError_t launch_agg(const AggParams &prm, bool adjoint, cudaStream_t st);
 
 }  // namespace kla

@@ -1,6 +1,6 @@
 // Definitions and explicit instantiations of the scan kernels' launchers
 // (kla_launch.cuh). The build compiles this file once per slice:
-//   KLA_INST_KIND   0 forward, 1 backward
+//   KLA_INST_KIND   0 forward, 1 backward, 2 aggregates
 //   KLA_INST_DT     0 (float, float), 1 (bfloat16, float), 2 (bfloat16, bfloat16)
 //   KLA_INST_LPCS   0 lanes per channel 1, 2, 4;  1 lanes per channel 8, 16, 32
 // Without those macros it holds every instantiation.
@@ -34,6 +34,32 @@ cudaError_t launch_bwd(const BwdParams &prm, cudaStream_t st) {
     kern<<<grid, Sh::kThreads, Sm::kTotal, st>>>(prm);
     return cudaGetLastError();
 }
+
+template <typename T, typename TO, int LPC, bool PRIOR>
+cudaError_t launch_agg(const AggParams &prm, bool adjoint, cudaStream_t st) {
+    constexpr int MC = kNW * (32 / LPC);
+    dim3 grid((unsigned)((prm.M + MC - 1) / MC), (unsigned)prm.B);
+    cudaError_t e;
+    if (adjoint) {
+        auto kern = kla_agg_kernel<T, TO, kSPT, LPC, kNW, true, PRIOR>;
+        constexpr size_t smem = AggSmem<T, TO, kSPT, LPC, kNW, true>::kTotal;
+        if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+        kern<<<grid, (kNW + 1) * 32, smem, st>>>(prm);
+    } else {
+        auto kern = kla_agg_kernel<T, TO, kSPT, LPC, kNW, false, false>;
+        constexpr size_t smem = AggSmem<T, TO, kSPT, LPC, kNW, false>::kTotal;
+        if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+        kern<<<grid, (kNW + 1) * 32, smem, st>>>(prm);
+    }
+    return cudaGetLastError();
+}
+
+#define KLA_INST_AGG_ONE(T, TO, LPC)                                                       \
+    template cudaError_t launch_agg<T, TO, LPC, false>(const AggParams &, bool, cudaStream_t); \
+    template cudaError_t launch_agg<T, TO, LPC, true>(const AggParams &, bool, cudaStream_t);
+#define KLA_INST_AGG(T, TO)                                                                      \
+    KLA_INST_AGG_ONE(T, TO, 1) KLA_INST_AGG_ONE(T, TO, 2) KLA_INST_AGG_ONE(T, TO, 4) \
+    KLA_INST_AGG_ONE(T, TO, 8) KLA_INST_AGG_ONE(T, TO, 16) KLA_INST_AGG_ONE(T, TO, 32)
 
 #define KLA_INST_ONE(FN, PARAMS, T, TO, LPC)                                         \
     template cudaError_t FN<T, TO, LPC, false>(const PARAMS &, cudaStream_t);        \
@@ -77,6 +103,11 @@ KLA_INST_ALL(launch_fwd, FwdParams)
 #endif
 #if !defined(KLA_INST_KIND) || KLA_INST_KIND == 1
 KLA_INST_ALL(launch_bwd, BwdParams)
+#endif
+#if !defined(KLA_INST_KIND) || KLA_INST_KIND == 2
+KLA_INST_AGG(float, float)
+KLA_INST_AGG(__nv_bfloat16, float)
+KLA_INST_AGG(__nv_bfloat16, __nv_bfloat16)
 #endif
 
 }  // namespace kla

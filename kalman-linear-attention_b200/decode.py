@@ -216,3 +216,151 @@ class LayerDecoder:
             if cfg["return_variance"]:
                 return out, F.linear(y_var, self.w["out_proj.weight"].pow(2))
             return out
+
+
+MODEL_KEYS = ("n_layers", "norm_eps", "mlp", "logit_softcap")
+
+
+class ModelDecoder:
+    """Prompt prefill and token-by-token decode of a whole stack of KLA blocks on the B200 kernels: the
+    reference's ``SequenceModel.forward`` with a state and ``SequenceModel.generate``
+    (src/kla/models/sequence_model.py:150-173, 200-220).
+
+    A block is ``x += mixer(norm(x))`` then ``x += mlp(norm(x))`` (sequence_model.py:47-98). The mixers run
+    through :class:`LayerDecoder` (two fused kernels per layer and token, the scan kernels for the prompt); the
+    norms, the channel MLPs, the embedding and the LM head are a handful of library calls each and stay torch
+    operations. One decoded token is a fixed sequence of launches over state that is updated in place, so
+    ``generate`` captures it once in a CUDA graph and replays it: a token then costs no host work but one replay,
+    where the reference's loop issues several hundred small launches per token from Python.
+
+    Built from plain tensors (``SequenceModel.state_dict()``) and plain config dicts; ``from_model`` reads them
+    off a reference model. The reference package is not needed at run time."""
+
+    def __init__(self, weights: dict, layer_configs, model_config: dict):
+        missing = [k for k in MODEL_KEYS if k not in model_config]
+        if missing:
+            raise ValueError(f"model config lacks {missing}")
+        self.cfg = dict(model_config)
+        self.w = weights
+        n = self.cfg["n_layers"]
+        if len(layer_configs) != n:
+            raise ValueError(f"got {len(layer_configs)} layer configs for {n} layers")
+        self.layers = []
+        for i in range(n):
+            pre = f"blocks.{i}.mixer."
+            lw = {k[len(pre):]: v for k, v in weights.items() if k.startswith(pre)}
+            self.layers.append(LayerDecoder(lw, layer_configs[i]))
+        self._graph = None
+
+    @classmethod
+    def from_model(cls, model) -> "ModelDecoder":
+        """Read weights and configs off a reference ``kla.SequenceModel`` whose mixers are all KLA layers."""
+        weights = {k: v.detach() for k, v in model.state_dict().items()}
+        layer_configs = [{k: getattr(blk.mixer.config, k) for k in CONFIG_KEYS} for blk in model.blocks]
+        model_config = {k: getattr(model.config, k) for k in MODEL_KEYS}
+        dec = cls(weights, layer_configs, model_config)
+        dev = model.embedding.weight.device
+        return dec.to(dev) if dev.type == "cuda" else dec
+
+    def to(self, device) -> "ModelDecoder":
+        out = ModelDecoder.__new__(ModelDecoder)
+        out.__dict__.update(self.__dict__)
+        out.w = {k: v.to(device) for k, v in self.w.items()}
+        out.layers = [layer.to(device) for layer in self.layers]
+        out._graph = None
+        return out
+
+    def init_state(self, batch: int, device, dtype=torch.float32):
+        return [layer.init_state(batch, device, dtype) for layer in self.layers]
+
+    def _norm(self, x, name):  # RMSNorm, src/kla/layers/common.py:45-55
+        xf = x.float()
+        xf = xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + self.cfg["norm_eps"])
+        return (xf * self.w[name + ".weight"].float()).to(x.dtype)
+
+    def _mlp(self, i, x):  # src/kla/layers/common.py:99-122
+        pre = f"blocks.{i}.mlp."
+        if self.cfg["mlp"] == "swiglu":
+            gate, up = F.linear(x, self.w[pre + "w12.weight"], self.w.get(pre + "w12.bias")).chunk(2, dim=-1)
+            return F.linear(F.silu(gate) * up, self.w[pre + "w3.weight"], self.w.get(pre + "w3.bias"))
+        return F.linear(F.gelu(F.linear(x, self.w[pre + "w1.weight"], self.w.get(pre + "w1.bias"))),
+                        self.w[pre + "w2.weight"], self.w.get(pre + "w2.bias"))
+
+    def _head(self, x):
+        logits = F.linear(self._norm(x, "norm_f"), self.w["lm_head.weight"])
+        cap = self.cfg["logit_softcap"]
+        return logits if cap is None else cap * torch.tanh(logits / cap)
+
+    def _blocks(self, x, state, prompt: bool):
+        for i, layer in enumerate(self.layers):
+            h = self._norm(x, f"blocks.{i}.mixer_norm")
+            mixed = layer.prefill(h, state[i])[0] if prompt else layer.step(h, state[i])
+            if isinstance(mixed, tuple):  # a layer that returns variances: the mean path (sequence_model.py:85-86)
+                mixed = mixed[0]
+            x = x + mixed
+            if self.cfg["mlp"] != "none":
+                x = x + self._mlp(i, self._norm(x, f"blocks.{i}.mlp_norm"))
+        return x
+
+    @torch.no_grad()
+    def prefill(self, input_ids: torch.Tensor, state=None):
+        """A prompt: ``input_ids`` [B, L] -> (logits [B, L, vocab], state ready for ``step``)."""
+        x = F.embedding(input_ids, self.w["embedding.weight"])
+        if state is None:
+            state = self.init_state(x.shape[0], x.device, x.dtype)
+        return self._head(self._blocks(x, state, prompt=True)), state
+
+    @torch.no_grad()
+    def step(self, token: torch.Tensor, state):
+        """One token per sequence: ``token`` [B] -> logits [B, vocab]; ``state`` is updated in place."""
+        x = F.embedding(token, self.w["embedding.weight"])
+        return self._head(self._blocks(x, state, prompt=False))
+
+    @torch.no_grad()
+    def generate(self, input_ids: torch.Tensor, max_new_tokens: int, temperature: float = 0.0, top_k=None,
+                 use_graph: bool = True) -> torch.Tensor:
+        """``SequenceModel.generate`` (sequence_model.py:200-220): prefill, then one token at a time from the
+        recurrent state. ``temperature <= 0`` is greedy. With ``use_graph`` the per-token work of all layers is
+        one CUDA graph replay; sampling happens between replays, on the device."""
+        logits, state = self.prefill(input_ids)
+        token = self._sample(logits[:, -1], temperature, top_k)
+        out = [input_ids, token]
+        if max_new_tokens <= 1:
+            return torch.cat(out, dim=1)
+        tok_buf = token[:, 0].clone()
+        graph = None
+        if use_graph:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            snapshot = [[None if t is None else t.clone() for t in st] for st in state]
+            with torch.cuda.stream(side):  # warm-up on a side stream, as graph capture requires
+                for _ in range(2):
+                    self.step(tok_buf, state)
+            torch.cuda.current_stream().wait_stream(side)
+            for st, snap in zip(state, snapshot):  # the warm-up advanced the state: put it back
+                for t, s_ in zip(st, snap):
+                    if t is not None:
+                        t.copy_(s_)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits_buf = self.step(tok_buf, state)
+        for _ in range(max_new_tokens - 1):
+            if graph is not None:
+                graph.replay()
+                logits = logits_buf
+            else:
+                logits = self.step(tok_buf, state)
+            token = self._sample(logits, temperature, top_k)
+            tok_buf.copy_(token[:, 0])
+            out.append(token)
+        return torch.cat(out, dim=1)
+
+    @staticmethod
+    def _sample(logits, temperature, top_k):  # sequence_model.py:222-234
+        if temperature <= 0:
+            return logits.argmax(dim=-1, keepdim=True)
+        logits = logits / temperature
+        if top_k is not None:
+            kth = torch.topk(logits, top_k, dim=-1).values[..., -1, None]
+            logits = logits.masked_fill(logits < kth, float("-inf"))
+        return torch.multinomial(torch.softmax(logits.float(), dim=-1), num_samples=1)

@@ -23,7 +23,7 @@ from typing import NamedTuple, Optional
 import torch
 
 from . import _lib
-from ._lib import BF16, F32, MAX_DSTATE, BwdArgs, ChunkFoldArgs, FwdArgs, SlabArgs, StepArgs, Tensor3
+from ._lib import BF16, F32, MAX_DSTATE, BwdArgs, ChunkFoldArgs, EpilogueBwdArgs, FwdArgs, SlabArgs, StepArgs, Tensor3
 
 
 class KLAState(NamedTuple):
@@ -123,7 +123,7 @@ def _epilogue_fields(epilogue):
 
 
 def _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype, need_ckpt: bool, sensors=None,
-                epilogue=None):
+                epilogue=None, raw=None):
     """Allocate outputs (and the checkpoint scratch when a backward will follow)
     and enqueue ``kla_b200_scan_fwd`` on the current stream of the inputs' device."""
     lib = _lib.load()
@@ -144,6 +144,7 @@ def _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype, nee
         a=_ptr(a), p=_ptr(p), lam0=_ptr(lam0), eta0=_ptr(eta0),
         y=_t3(y), y_var=_t3(y_var), lam_fin=_ptr(lam_fin), eta_fin=_ptr(eta_fin),
         ckpt=_ptr(ckpt), **_sensor_fields(sensors), **_epilogue_fields(epilogue),
+        **({} if raw is None else dict(y_raw=_t3(raw[0]), y_var_raw=_t3(raw[1]))),
     )
     with torch.cuda.device(dev):
         _lib.check(lib.kla_b200_scan_fwd(ctypes.byref(args), _stream(dev)))
@@ -353,6 +354,76 @@ class _KLAScanB200(torch.autograd.Function):
                 dlam0 if has_state else None, deta0 if has_state else None, None, None, None, None)
 
 
+class _KLAScanEpilogueB200(torch.autograd.Function):
+    """The scan with the layer's output path inside (kla_layer.py:329-338), for training: the forward kernel
+    applies skip and gate at its store and also keeps the scan's own y, y_var; the backward runs the path's
+    adjoint (one memory-bound kernel) and then the scan's backward kernel."""
+
+    @staticmethod
+    def forward(ctx, v, lambda_v, k, q, a, p, lam0, eta0, z, gate, skip, prior, out_dtype, sensors, gate_act):
+        need_grad = any(ctx.needs_input_grad[:11])
+        B, L, M = v.shape
+        epi = {}
+        skip_flat = None
+        if skip is not None:
+            skip_flat = skip.detach().float().reshape(-1).contiguous()
+            epi.update(z=z, lambda_skip=skip_flat)
+        if gate is not None:
+            epi.update(gate=gate, gate_activation=gate_act)
+        raw = None
+        if need_grad and gate is not None:
+            raw = (torch.empty((B, L, M), device=v.device, dtype=out_dtype), torch.empty((B, L, M), device=v.device, dtype=out_dtype))
+        y, y_var, lam_fin, eta_fin, ckpt = _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior, out_dtype, need_grad,
+                                                       sensors, epi, raw)
+        ctx.save_for_backward(v, lambda_v, k, q, a, p, lam0, eta0, ckpt, z, gate, skip_flat, *(raw or ()))
+        ctx.prior, ctx.sensors, ctx.out_dtype, ctx.gate_act = prior, sensors, out_dtype, gate_act
+        ctx.skip_shape = None if skip is None else skip.shape
+        return y, y_var, lam_fin, eta_fin
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, dout, dout_var, dlam_fin, deta_fin):
+        v, lambda_v, k, q, a, p, lam0, eta0, ckpt, z, gate, skip_flat, *raw = ctx.saved_tensors
+        B, L, M = v.shape
+        S = k.shape[2]
+        dev, od = v.device, ctx.out_dtype
+        lib = _lib.load()
+
+        def grad_in(g):
+            return None if g is None else _rowmajor_last(g if g.dtype == od else g.to(od))
+
+        dout, dout_var = grad_in(dout), grad_in(dout_var)
+        if dout is None:
+            dout = torch.zeros((B, L, M), device=dev, dtype=od)
+        dy = torch.empty((B, L, M), device=dev, dtype=od)
+        dy_var = torch.empty((B, L, M), device=dev, dtype=od)
+        dz = None if z is None else torch.empty((B, L, M), device=dev, dtype=v.dtype)
+        dgate = None if gate is None else torch.empty((B, L, M), device=dev, dtype=v.dtype)
+        dskip = None if skip_flat is None else torch.empty_like(skip_flat)
+        args = EpilogueBwdArgs(
+            B=B, L=L, M=M, in_dtype=_dt(v.dtype), out_dtype=_dt(od),
+            gate_activation=_lib.ACT[ctx.gate_act if gate is not None else None],
+            lambda_skip_len=0 if skip_flat is None else skip_flat.numel(),
+            dout=_t3(dout), dout_var=_t3(dout_var), y_raw=_t3(raw[0] if raw else None), y_var_raw=_t3(raw[1] if raw else None),
+            z=_t3(z), gate=_t3(gate), lambda_skip=_ptr(skip_flat),
+            dy=_t3(dy), dy_var=_t3(dy_var), dz=_t3(dz), dgate=_t3(dgate), dlambda_skip=_ptr(dskip))
+        with torch.cuda.device(dev):
+            _lib.check(lib.kla_b200_epilogue_bwd(ctypes.byref(args), _stream(dev)))
+        if (dlam_fin is None) != (deta_fin is None):
+            zero = torch.zeros((B, M, S), device=dev, dtype=torch.float32)
+            dlam_fin = zero if dlam_fin is None else dlam_fin
+            deta_fin = zero if deta_fin is None else deta_fin
+        if dlam_fin is not None:
+            dlam_fin, deta_fin = dlam_fin.float().contiguous(), deta_fin.float().contiguous()
+        dv, dlv, dk, dq, da, dp, dlam0, deta0 = _launch_bwd(
+            v, lambda_v, k, q, a, p, lam0, eta0, ckpt, dy, dy_var, dlam_fin, deta_fin, ctx.prior, od, ctx.sensors)
+        if k.dtype != torch.float32:
+            dk, dq = dk.to(k.dtype), dq.to(k.dtype)
+        has_state = lam0 is not None
+        return (dv, dlv, dk, dq, da, dp, dlam0 if has_state else None, deta0 if has_state else None,
+                dz, dgate, None if dskip is None else dskip.reshape(ctx.skip_shape), None, None, None, None)
+
+
 def kla_scan_b200(
     v: torch.Tensor,
     lambda_v: torch.Tensor,
@@ -386,11 +457,12 @@ def kla_scan_b200(
     and the gradient returned for that argument is the one with respect to ``x``.
 
     ``epilogue=dict(z=, lambda_skip=, gate=, gate_activation="silu")`` fuses the
-    layer's output path for inference (kla_layer.py:329-338): ``y += lambda_skip * z``
+    layer's output path (kla_layer.py:329-338): ``y += lambda_skip * z``
     (``lambda_skip``: one value or one per channel), then ``y *= g``, ``y_var *= g**2``
-    with ``g = act(gate)``; either half may be left out. Forward only: it raises
-    ``NotImplementedError`` when a gradient would be needed (run it under
-    ``torch.no_grad()``; the training path applies these two steps in torch).
+    with ``g = act(gate)``; either half may be left out. Differentiable with respect
+    to ``z``, ``gate`` and ``lambda_skip`` as well: when a gradient is needed the
+    forward also keeps the scan's own y, y_var, and the backward runs the path's
+    adjoint as one memory-bound kernel before the scan's backward kernel.
 
     ``time_chunks``: the time-parallel form of the scan. The reference's parallel
     path scans trace-normalised Moebius matrices and affine pairs over time
@@ -444,10 +516,6 @@ def kla_scan_b200(
             raise ValueError("log_variance must be (obs_var_min >= 0, obs_var_max or None)")
         log_variance = (float(log_variance[0]), None if log_variance[1] is None else float(log_variance[1]))
     if epilogue:
-        if torch.is_grad_enabled() and any(t is not None and t.requires_grad
-                                           for t in (v, lambda_v, k, q, a, p, lam0, eta0, *epilogue.values())
-                                           if torch.is_tensor(t)):
-            raise _unsupported("fuses the skip/gate epilogue in the forward only; call it under torch.no_grad()")
         epi = dict(epilogue)
         unknown = set(epi) - {"z", "lambda_skip", "gate", "gate_activation"}
         if unknown:
@@ -460,15 +528,18 @@ def kla_scan_b200(
                 if tuple(t.shape) != (B, L, M):
                     raise ValueError(f"epilogue {name} must be [B, L, M]")
                 epi[name] = _rowmajor_last(t if t.dtype == act else t.to(act))
-        if epi.get("lambda_skip") is not None:
-            sk = epi["lambda_skip"].detach().float().reshape(-1).contiguous().to(v.device)
-            if sk.numel() not in (1, M):
+        skip = epi.get("lambda_skip")
+        if skip is not None:
+            if skip.numel() not in (1, M):
                 raise ValueError("lambda_skip must hold one value or one per channel")
-            epi["lambda_skip"] = sk
-        if epi.get("gate_activation", "silu") not in ("silu", "gelu", "relu"):
+            if skip.device != v.device:
+                skip = skip.to(v.device)
+        gate_act = epi.get("gate_activation", "silu")
+        if gate_act not in ("silu", "gelu", "relu"):
             raise ValueError("gate_activation must be 'silu', 'gelu' or 'relu'")
-        y, y_var, lam_fin, eta_fin, _ = _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, bool(decode_from_prior),
-                                                    out_dtype, False, log_variance, epi)
+        y, y_var, lam_fin, eta_fin = _KLAScanEpilogueB200.apply(
+            v, lambda_v, k, q, a, p, lam0, eta0, epi.get("z"), epi.get("gate"), skip, bool(decode_from_prior),
+            out_dtype, log_variance, gate_act)
         return y, y_var, _state_cls()(lam=lam_fin, eta=eta_fin)
     chunks = pick_time_chunks(B, L, M, S, time_chunks) if L > 0 else 1
     y, y_var, lam_fin, eta_fin = _KLAScanB200.apply(

@@ -50,7 +50,7 @@ def oracle_launches(monkeypatch):
             sig = np.minimum(sig, sensors[1])
         return 1.0 / sig, -free / (sig * sig) / (1.0 + np.exp(-x))
 
-    def fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior, out_dtype, need_ckpt, sensors=None, epilogue=None):
+    def fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior, out_dtype, need_ckpt, sensors=None, epilogue=None, raw=None):
         n = lambda t: None if t is None else t.detach().double().numpy()
         lv = n(lambda_v) if sensors is None else precision(n(lambda_v), sensors)[0]
         f = O.scan_fwd(n(v), lv, n(k), n(q), n(a), n(p), n(lam0), n(eta0), prior=prior)

@@ -150,8 +150,11 @@ def test_layer_forward_backward_matches_cpu_torch_backend(kla, checkpoint_ssm):
     y.square().sum().backward()
     torch.cuda.synchronize()
     launches = importlib.import_module("kalman-linear-attention_b200._lib").load().kla_b200_launch_count() - launches0
-    # forward + backward, and the forward once more when the scan is recomputed under checkpointing
-    assert launches == (3 if checkpoint_ssm else 2), launches
+    # forward + backward, and the forward once more when the scan is recomputed under checkpointing; at this shape
+    # (2 x 1024 channels) the scan runs time-parallel: aggregate, fold and scan kernel in each direction
+    ops = importlib.import_module("kalman-linear-attention_b200.ops")
+    per = 3 if ops.pick_time_chunks(2, 1024, 1024, 16) > 1 else 1
+    assert launches == per * (3 if checkpoint_ssm else 2), launches
     rows = [("y", _rel(y.cpu(), y_ref))]
     torch.testing.assert_close(y.cpu(), y_ref, rtol=1e-4, atol=1e-5)
     gp = dict(dut.named_parameters())
@@ -268,3 +271,42 @@ def test_sequence_model_training_step_matches_torch_backend(kla):
             worst = (n, e)
     print(f"\n  SequenceModel step: loss {l_dut.item():.6f} vs {l_ref.item():.6f}; worst gradient {worst[0]} {worst[1]:.2e}")
     assert worst[1] < 2e-3, worst
+
+
+# ------------------------------------------------------------ multi-layer prefill + decode loop
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_model_decoder_generates_what_the_reference_generates(dtype):
+    """``ModelDecoder`` (all layers on the fused decode kernels, the token loop as one CUDA graph) against the
+    reference's own ``SequenceModel.generate`` on its torch backend (sequence_model.py:200-220): the prompt's logits,
+    the per-token logits and, greedily, the generated tokens."""
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    import kla_b200
+    from kla import KLAConfig, ModelConfig, SequenceModel
+
+    torch.manual_seed(0)
+    model = SequenceModel(ModelConfig(vocab_size=512, d_model=128, n_layers=3),
+                          KLAConfig(d_state=16, backend="torch")).cuda().to(dtype).eval()
+    ids = torch.randint(0, 512, (2, 24), generator=torch.Generator().manual_seed(2)).cuda()
+    dec = kla_b200.ModelDecoder.from_model(model)
+    tol = dict(rtol=1e-3, atol=1e-3) if dtype == torch.float32 else dict(rtol=5e-2, atol=1e-1)
+    with torch.no_grad():
+        ref_logits, ref_state = model(ids, state=model.init_state(2))
+        logits, state = dec.prefill(ids)
+        torch.testing.assert_close(logits.float(), ref_logits.float(), **tol)
+        tok = ids[:, -1:]
+        for _ in range(4):  # token-by-token, eagerly
+            ref_l, ref_state = model(tok, state=ref_state)
+            l = dec.step(tok[:, 0], state)
+            torch.testing.assert_close(l.float(), ref_l[:, -1].float(), **tol)
+            tok = ref_l[:, -1].argmax(-1, keepdim=True)
+    if dtype == torch.float32:
+        want = model.generate(ids, 12, temperature=0.0)
+        lib = importlib.import_module("kalman-linear-attention_b200._lib").load()
+        n0 = lib.kla_b200_launch_count()
+        got = dec.generate(ids, 12)
+        assert torch.equal(got, want), (got, want)
+        assert torch.equal(dec.generate(ids, 12, use_graph=False), want)
+        # prefill: conv + scan per layer; then two kernels per layer and token, captured once (+ two warm-up tokens)
+        assert lib.kla_b200_launch_count() - n0 >= 3 * 2

@@ -445,7 +445,7 @@ def test_log_variance_prologue_bf16_keeps_float32_precision_inside(kb):
 @pytest.mark.parametrize("mode", ["both", "skip_vector", "gate_gelu", "bf16"])
 def test_forward_epilogue_matches_torch_ops(kb, mode):
     """epilogue=...: y += lambda_skip * z, then y *= act(gate), y_var *= act(gate)^2 at the store
-    (src/kla/layers/kla_layer.py:329-338), forward only."""
+    (src/kla/layers/kla_layer.py:329-338), in inference."""
     kla_b200 = kb
     dev = torch.device("cuda:0")
     B, L, M, S = 2, 45, 50, 16
@@ -479,8 +479,58 @@ def test_forward_epilogue_matches_torch_ops(kb, mode):
     torch.testing.assert_close(y, ref, rtol=1e-5, atol=1e-5)
     torch.testing.assert_close(y_var, refv, rtol=1e-5, atol=1e-5)
     assert torch.equal(st.lam, st0.lam) and torch.equal(st.eta, st0.eta)
-    with pytest.raises(NotImplementedError, match="no_grad"):
-        kla_b200.kla_scan_b200(v.requires_grad_(True), lv, k, q, a, p, epilogue=epi)
     with pytest.raises(ValueError, match="together"):
         with torch.no_grad():
             kla_b200.kla_scan_b200(v.detach(), lv, k, q, a, p, epilogue=dict(z=z))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["skip_scalar_gate_silu", "skip_vector", "gate_gelu", "gate_relu", "bf16", "log_variance"])
+def test_training_epilogue_matches_torch_autograd(kb, mode):
+    """The fused output path in training: outputs and EVERY gradient (the scan's six inputs, z, gate, lambda_skip)
+    against torch autograd of the same path applied to the plain scan's outputs (kla_layer.py:329-338)."""
+    kla_b200 = kb
+    dev = torch.device("cuda:0")
+    B, L, M, S = 2, 70, 50, 16
+    g = torch.Generator().manual_seed(5)
+    F = torch.nn.functional
+    dt = torch.bfloat16 if mode == "bf16" else torch.float32
+    od = torch.bfloat16 if mode == "bf16" else torch.float32
+    mk = lambda t, d=dt: t.to(dev, d).requires_grad_(True)
+    v = mk(torch.randn(B, L, M, generator=g))
+    lv = mk(torch.randn(B, L, M, generator=g) if mode == "log_variance" else 1.0 / F.softplus(torch.randn(B, L, M, generator=g)))
+    k, q = mk(F.normalize(torch.randn(B, L, S, generator=g), dim=-1)), mk(F.normalize(torch.randn(B, L, S, generator=g), dim=-1))
+    a, p = mk(torch.sigmoid(torch.randn(M, S, generator=g)), torch.float32), mk(F.softplus(torch.randn(M, S, generator=g)), torch.float32)
+    z, gate = mk(torch.randn(B, L, M, generator=g)), mk(torch.randn(B, L, M, generator=g))
+    skip = mk(torch.randn(M, generator=g), torch.float32) if mode == "skip_vector" else mk(torch.tensor(-0.7), torch.float32)
+    act = {"gate_gelu": "gelu", "gate_relu": "relu"}.get(mode, "silu")
+    has_skip, has_gate = mode not in ("gate_gelu", "gate_relu"), mode != "skip_vector"
+    epi = {}
+    if has_skip:
+        epi.update(z=z, lambda_skip=skip)
+    if has_gate:
+        epi.update(gate=gate, gate_activation=act)
+    sensors = (1e-3, 2.0) if mode == "log_variance" else None
+    dout = torch.randn(B, L, M, generator=g).to(dev, od)
+    dvar = torch.randn(B, L, M, generator=g).to(dev, od)
+    leaves = [v, lv, k, q, a, p] + ([z, skip] if has_skip else []) + ([gate] if has_gate else [])
+
+    y, y_var, st = kla_b200.kla_scan_b200(v, lv, k, q, a, p, epilogue=epi, out_dtype=od, log_variance=sensors)
+    got = torch.autograd.grad([y, y_var], leaves, [dout, dvar])
+
+    y0, yv0, _ = kla_b200.kla_scan_b200(v, lv, k, q, a, p, out_dtype=od, log_variance=sensors)
+    ref, refv = y0.float(), yv0.float()
+    if has_skip:
+        ref = ref + skip * z.float()
+    if has_gate:
+        gg = getattr(F, act)(gate.float())
+        ref, refv = ref * gg, refv * gg * gg
+    want = torch.autograd.grad([ref, refv], leaves, [dout.float(), dvar.float()])
+    tol = dict(rtol=2e-2, atol=2e-2) if mode == "bf16" else dict(rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(y.float(), ref.detach().to(od).float(), **tol)
+    torch.testing.assert_close(y_var.float(), refv.detach().to(od).float(), **tol)
+    names = ["v", "lambda_v", "k", "q", "a", "p"] + (["z", "lambda_skip"] if has_skip else []) + (["gate"] if has_gate else [])
+    for n, g_, w_ in zip(names, got, want):
+        assert g_.shape == w_.shape and g_.dtype == w_.dtype, n
+        err = ((g_.float() - w_.float()).abs().max() / (w_.float().abs().max() + 1.0)).item()
+        assert err < (2e-2 if mode == "bf16" else 2e-5), f"d{n}: {err:.2e}"
