@@ -1126,6 +1126,58 @@ def run_epilogue(args):
     }), flush=True)
 
 
+def run_generate(args):
+    """Secondary line: prompt prefill and token-by-token decode of a whole model -- the reference's
+    ``SequenceModel(ModelConfig(vocab 50304, d_model 768, 12 layers), KLAConfig(d_state=16))``, bf16, batch 32, a prompt of
+    512 tokens and 128 generated ones, greedy -- through ``ModelDecoder`` (fused decode kernels per layer, the token loop
+    one CUDA graph) beside the reference's own ``SequenceModel.generate`` on its torch backend."""
+    import torch
+
+    if reference_dir() is None:
+        print(json.dumps({"workload": "generate", "unavailable": "the reference is not installed under baseline/_ref"}))
+        return
+    sys.path.insert(0, reference_dir())
+    import kla_b200
+    from kla import KLAConfig, ModelConfig, SequenceModel
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, LP, NEW, V = (args.batch or 32), 512, 128, 50304
+    torch.manual_seed(0)
+    model = SequenceModel(ModelConfig(vocab_size=V, d_model=768, n_layers=12), KLAConfig(d_state=16, backend="torch"))
+    model = model.to(dev).to(torch.bfloat16).eval()
+    ids = torch.randint(0, V, (B, LP), device=dev, generator=torch.Generator(device=dev).manual_seed(1))
+    dec = kla_b200.ModelDecoder.from_model(model)
+
+    def timed(fn, n):
+        fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            out = fn()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / n, out
+
+    n = max(1, min(args.steps, 3))
+    t_dec, out = timed(lambda: dec.generate(ids, NEW), n)
+    t_pre, _ = timed(lambda: dec.prefill(ids), n)
+    t_ref, ref = timed(lambda: model.generate(ids, NEW, temperature=0.0), 1)
+    same = float((out[:, LP:] == ref[:, LP:]).float().mean())
+    first = float((out[:, LP] == ref[:, LP]).float().mean())
+    per_tok = (t_dec - t_pre) / (NEW - 1)
+    print(json.dumps({
+        "workload": "generate", "metric": "decode tokens/s (whole model)", "value": B / per_tok, "unit": "tokens/s", "n_gpus": 1,
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"SequenceModel(vocab 50304, d_model 768, 12 layers, d_state 16) bf16, batch {B}, prompt {LP}, "
+                               f"{NEW} new tokens, greedy"},
+        "ms_generate": 1e3 * t_dec, "ms_prefill": 1e3 * t_pre, "us_per_token_step": 1e6 * per_tok,
+        "reference_generate_ms": 1e3 * t_ref, "speedup_vs_reference_generate": t_ref / t_dec,
+        "first_generated_token_equal_to_reference": first, "all_generated_tokens_equal_to_reference": same,
+        "note": "a random-weight model's logits are nearly flat, so in bf16 the greedy choice flips where two logits are within "
+                "one rounding step and the sequences part from there; the float32 test demands equal tokens",
+    }), flush=True)
+
+
 def run_inference(args):
     """Secondary line: the inference route of one layer at the decode configuration (batch 32,
     d_model 1024 -> M = 2048, S = 16, bf16): a prompt of 8192 tokens through LayerDecoder.prefill
@@ -1378,7 +1430,7 @@ def main():
                          "(B=4 leaves one CTA per SM, B=16 fills every SM); the headline stays B=8")
     ap.add_argument("--backend", default="", help="reference_gpu child / train_step: the scan backend to run")
     ap.add_argument("--workload", default="raw", choices=["raw", "seqshard", "decode", "rawpair", "decode_layer", "prologue", "epilogue", "inference",
-                                                          "reference_gpu", "_reference_gpu_child", "train_step"],
+                                                          "reference_gpu", "_reference_gpu_child", "train_step", "generate"],
                     help="raw = the headline raw-op workload (default); seqshard = the long-sequence, "
                          "time-sharded workload (secondary line)")
     args = ap.parse_args()
@@ -1388,6 +1440,8 @@ def main():
         return run_reference_gpu_child(args)
     if args.workload == "train_step":
         return run_train_step(args)
+    if args.workload == "generate":
+        return run_generate(args)
     if args.batch > 0:
         WORK["B"] = args.batch
     if args.workload == "seqshard" and args.impl != "reference":

@@ -152,10 +152,10 @@ int prep_fwd(FwdParams &prm, const kla_b200_fwd_args &a, cudaStream_t st) {
 template <typename T, typename TO, int LPC, bool PRIOR>
 int prep_bwd(BwdParams &prm, const kla_b200_bwd_args &a, cudaStream_t st) {
     const int mc = scan_channels_per_cta(LPC);
-    prm.use_tma = !g_no_tma && make_tile_map<T>(&prm.tm_v, a.v, a.B, a.L, a.M, mc, kTT) &&
-                  make_tile_map<T>(&prm.tm_lv, a.lambda_v, a.B, a.L, a.M, mc, kTT) &&
-                  make_tile_map<TO>(&prm.tm_dy, a.dy, a.B, a.L, a.M, mc, kTT) &&
-                  (a.dy_var.ptr == nullptr || make_tile_map<TO>(&prm.tm_dyv, a.dy_var, a.B, a.L, a.M, mc, kTT));
+    prm.use_tma = !g_no_tma && make_tile_map<T>(&prm.tm_v, a.v, a.B, a.L, a.M, mc, kBwdTT) &&
+                  make_tile_map<T>(&prm.tm_lv, a.lambda_v, a.B, a.L, a.M, mc, kBwdTT) &&
+                  make_tile_map<TO>(&prm.tm_dy, a.dy, a.B, a.L, a.M, mc, kBwdTT) &&
+                  (a.dy_var.ptr == nullptr || make_tile_map<TO>(&prm.tm_dyv, a.dy_var, a.B, a.L, a.M, mc, kBwdTT));
     const cudaError_t e = launch_bwd<T, TO, LPC, PRIOR>(prm, st);
     g_launches++;
     return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
@@ -322,6 +322,7 @@ int kla_b200_scan_fwd(const kla_b200_fwd_args *a, void *stream) {
     FwdParams prm{};
     prm.B = (int)a->B; prm.L = (int)a->L; prm.M = (int)a->M; prm.S = (int)a->S;
     prm.NT = (int)((a->L + kTT - 1) / kTT);
+    prm.NC = (int)((a->L + kCkptInterval - 1) / kCkptInterval);
     prm.v = t3(a->v); prm.lv = t3(a->lambda_v); prm.k = t3(a->k); prm.q = t3(a->q);
     prm.y = t3(a->y); prm.yv = t3(a->y_var);
     prm.a = a->a; prm.p = a->p; prm.lam0 = a->lam0; prm.eta0 = a->eta0;
@@ -397,7 +398,7 @@ int kla_b200_scan_bwd(const kla_b200_bwd_args *a, void *stream) {
 
     BwdParams prm{};
     prm.B = (int)a->B; prm.L = (int)a->L; prm.M = (int)a->M; prm.S = (int)a->S;
-    prm.NT = (int)((a->L + kTT - 1) / kTT);
+    prm.NT = (int)((a->L + kBwdTT - 1) / kBwdTT);
     prm.v = t3(a->v); prm.lv = t3(a->lambda_v); prm.k = t3(a->k); prm.q = t3(a->q);
     prm.dy = t3(a->dy); prm.dyv = t3(a->dy_var); prm.dv = t3(a->dv); prm.dlv = t3(a->dlambda_v);
     prm.a = a->a; prm.p = a->p; prm.lam0 = a->lam0; prm.eta0 = a->eta0;

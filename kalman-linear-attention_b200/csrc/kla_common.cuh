@@ -39,7 +39,7 @@ namespace kla {
 constexpr float kEps = 1e-12f;      // EPS,   src/kla/ops/kla_ops.py:43
 constexpr float kPMin = 1e-12f;     // P_MIN, src/kla/ops/kla_ops.py:44
 constexpr float kLamMin = 1e-20f;   // floor on a carried-in precision before 1/lambda
-constexpr int kCkptInterval = 16;   // steps between checkpoints of the filter state
+constexpr int kCkptInterval = 8;    // steps between checkpoints of the filter state (= one tile of the backward)
 
 // Device-side status word: 0 = ok, otherwise the code of the first bounded wait
 // that ran out (kStatusWait | site). Read back by kla_b200_device_status().

@@ -38,12 +38,13 @@ constexpr int kFwdUnroll = KLA_FWD_UNROLL;  // steps unrolled per trip of the ti
 
 struct alignas(64) FwdParams {
     CUtensorMap tm_v, tm_lv;  // rank-3 (M, L, B) maps with box (MC, TT, 1); valid when use_tma
-    int B, L, M, S, NT;
+    int B, L, M, S, NT;  // NT tiles of TT steps
+    int NC;              // checkpoints per sequence: one per kCkptInterval steps
     int use_tma;
     Tensor3 v, lv, k, q, y, yv;
     const float *a, *p, *lam0, *eta0;
     float *lam_fin, *eta_fin;
-    float2 *ckpt;  // [B, NT, M, S] (P, mean) at the start of each tile, or nullptr
+    float2 *ckpt;  // [B, NC, M, S] (P, mean) before every kCkptInterval-th step, or nullptr
     int vec_y, vec_yv;
     // lv holds the sensor projection's raw log-variance output instead of the precision:
     // Lambda_v = 1 / min(softplus(lv) + obs_var_min, obs_var_max) is formed in shared memory by the compute warps,
@@ -93,7 +94,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
     // helper warps split by task: the first NH/2 load and stage inputs, the others sum and store outputs
     constexpr int kProducers = (NH / 2) * 32, kDrainers = Sh::kHelpers - kProducers;
     static_assert(NH >= 2, "one loading and one storing helper warp at least");
-    static_assert(TT == kCkptInterval, "one checkpoint per tile");
+    static_assert(TT % kCkptInterval == 0, "checkpoints fall on fixed steps of a tile");
 
     // Declared with its alignment (no run-time rounding of the pointer) so that
     // the compiler keeps every access below in the shared address space.
@@ -179,8 +180,17 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         }
         // checkpoint pointer of chain (ci = 0, i = 0); advanced by one tile per tile
         float2 *ck = prm.ckpt;
-        if (ck != nullptr) ck += ((long long)b * NT * M + (m_cta + cw)) * S + j;
+        if (ck != nullptr) ck += ((long long)b * prm.NC * M + (m_cta + cw)) * S + j;
         const long long ck_tile = (long long)M * S;
+        auto store_ckpt = [&]() {  // the state before the step about to be taken; advances to the next checkpoint
+#pragma unroll
+            for (int ci = 0; ci < CH; ++ci)
+#pragma unroll
+                for (int i = 0; i < SPT; ++i)
+                    if (m_cta + cw + ci < M && i * LPC + j < S)
+                        ck[ci * S + i * LPC] = make_float2(pair_el(P[ci], i), pair_el(mean[ci], i));
+            ck += ck_tile;
+        };
 
         // The time loop is software-pipelined by hand, because a single warp is
         // bound by the latency of its dependent instructions, not by issue slots:
@@ -292,15 +302,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                 __syncwarp();
             }
             if (tile >= NO && !mbar_wait(prm.wait, &empty_out[o], (tile / NO - 1) & 1, 2)) break;
-            if (ck != nullptr) {
-#pragma unroll
-                for (int ci = 0; ci < CH; ++ci)
-#pragma unroll
-                    for (int i = 0; i < SPT; ++i)
-                        if (m_cta + cw + ci < M && i * LPC + j < S)
-                            ck[ci * S + i * LPC] = make_float2(pair_el(P[ci], i), pair_el(mean[ci], i));
-                ck += ck_tile;
-            }
+            if (ck != nullptr) store_ckpt();
             const T *lrow = lstage(s) + cw;
             const float *lfrow = lfstage(s) + cw;
             const T *vrow = vstage(s) + cw;
@@ -317,6 +319,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
 #pragma unroll
                     for (int u = 0; u < kFwdUnroll; ++u) {
                         const int tt = t4 + u;
+                        if (tt > 0 && tt % kCkptInterval == 0 && ck != nullptr) store_ckpt();
                         fetch(in, lrow, lfrow, vrow, kqrow, (tt + 1) % TT);  // the wrap-around fetch is not used
                         update(pr);
                         readout(pr, yrow, tt);
@@ -326,6 +329,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                 }
             } else {
                 for (int tt = 0; t0 + tt < L; ++tt) {
+                    if (tt > 0 && tt % kCkptInterval == 0 && ck != nullptr) store_ckpt();
                     fetch(in, lrow, lfrow, vrow, kqrow, (tt + 1) % TT);
                     update(pr);
                     readout(pr, yrow, tt);

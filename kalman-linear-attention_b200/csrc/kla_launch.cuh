@@ -18,7 +18,8 @@ constexpr int kNW = KLA_NW;            // compute warps per CTA
 #define KLA_NH 4
 #endif
 constexpr int kNH = KLA_NH;            // helper warps per CTA
-constexpr int kTT = kCkptInterval;     // steps per tile
+constexpr int kTT = 16;                // steps per tile of the forward (two checkpoints)
+constexpr int kBwdTT = kCkptInterval;  // steps per tile of the backward
 #ifndef KLA_SPT
 #define KLA_SPT 4
 #endif

@@ -24,14 +24,26 @@ cudaError_t launch_fwd(const FwdParams &prm, cudaStream_t st) {
 
 template <typename T, typename TO, int LPC, bool PRIOR>
 cudaError_t launch_bwd(const BwdParams &prm, cudaStream_t st) {
-    using Sh = ScanShape<kSPT, LPC, kCH, kNW, kNH, kTT>;
-    using Sm = BwdSmem<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT>;
-    auto kern = prm.lv_log_sigma ? kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, true>
-                                 : kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, false>;
+    using Sh = ScanShape<kSPT, LPC, kCH, kNW, kNH, kBwdTT>;
+    using Sm = BwdSmem<T, TO, kSPT, LPC, kCH, kNW, kNH, kBwdTT>;
+    auto kern = prm.lv_log_sigma ? kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kBwdTT, PRIOR, true>
+                                 : kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kBwdTT, PRIOR, false>;
+    // The kernel's warp groups re-divide the registers the CTA was launched with; if the compiled kernel holds
+    // fewer than the division assumes, the group that grows would wait for registers that never come. Checked
+    // once per instantiation, before anything is launched.
+    static int regs_ok[2] = {-1, -1};
+    int &ok = regs_ok[prm.lv_log_sigma ? 1 : 0];
+    if (ok < 0) {
+        cudaFuncAttributes attr;
+        cudaError_t e = cudaFuncGetAttributes(&attr, kern);
+        if (e != cudaSuccess) return e;
+        ok = attr.numRegs * kBwdThreads >= 128 * (kBwdRegsReverse + kBwdRegsReplay + kBwdRegsHelper) ? 1 : 0;
+    }
+    if (!ok) return cudaErrorLaunchOutOfResources;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sm::kTotal);
     if (e != cudaSuccess) return e;
     dim3 grid((unsigned)((prm.M + Sh::kMC - 1) / Sh::kMC), (unsigned)prm.B);
-    kern<<<grid, Sh::kThreads, Sm::kTotal, st>>>(prm);
+    kern<<<grid, kBwdThreads, Sm::kTotal, st>>>(prm);
     return cudaGetLastError();
 }
 

@@ -39,10 +39,10 @@ def test_version_and_checkpoint_size(L):
     lib = L.load()
     assert lib.kla_b200_version() >= 100
     iv = lib.kla_b200_ckpt_interval()
-    assert iv == 16
+    assert iv == 8
     # one (P, mean) float2 per lane per started interval
     assert lib.kla_b200_ckpt_bytes(8, 4096, 1024, 16) == 8 * (4096 // iv) * 1024 * 16 * 8
-    assert lib.kla_b200_ckpt_bytes(2, 17, 3, 5) == 2 * 2 * 3 * 5 * 8
+    assert lib.kla_b200_ckpt_bytes(2, 17, 3, 5) == 2 * 3 * 3 * 5 * 8
     assert lib.kla_b200_ckpt_bytes(0, 17, 3, 5) == 0
 
 
