@@ -436,3 +436,19 @@ def test_sequence_sharded_scan_under_gloo():
         np.testing.assert_allclose(dp, b.dp, **tol)
         np.testing.assert_allclose(dlam0, b.dlam0, **tol)  # broadcast from the first slab
         np.testing.assert_allclose(deta0, b.deta0, **tol)
+
+
+# ------------------------------------------------------------ time-parallel form: the choice of the chunk count
+
+def test_chunk_count_follows_the_shape():
+    pick = ops.pick_time_chunks
+    assert pick(8, 4096, 1024, 16) == 1          # the grid already fills the GPU
+    assert pick(1, 4096, 1024, 16) == 8          # 32 CTAs: cut the sequence
+    assert pick(1, 4096, 1024, 16, 1) == 1       # switched off
+    assert pick(1, 100, 64, 16, 8) == 1          # chunks keep at least 64 steps
+    assert pick(1, 1100, 64, 16, 8) == 5         # C divides L
+    assert 4096 % pick(2, 4096, 512, 16) == 0
+    v = torch.zeros(2, 8, 4)
+    assert ops._chunkable(v, 2, 8) and not ops._chunkable(torch.zeros(2, 12, 4)[:, :8], 2, 8)
+    c = ops._as_chunks(torch.arange(2 * 8 * 3.0).view(2, 8, 3), 4)
+    assert c.shape == (8, 2, 3) and torch.equal(c[5], torch.arange(2 * 8 * 3.0).view(2, 8, 3)[1, 2:4])

@@ -39,16 +39,6 @@ def kb():
     return kla_b200
 
 
-def test_chunk_count_follows_the_shape():
-    pick = ops.pick_time_chunks
-    assert pick(8, 4096, 1024, 16) == 1          # the grid already fills the GPU
-    assert pick(1, 4096, 1024, 16) == 8          # 32 CTAs: cut the sequence
-    assert pick(1, 4096, 1024, 16, 1) == 1       # switched off
-    assert pick(1, 100, 64, 16, 8) == 1          # chunks keep at least 64 steps
-    assert pick(1, 1100, 64, 16, 8) == 5         # C divides L
-    assert 4096 % pick(2, 4096, 512, 16) == 0
-
-
 @pytest.mark.parametrize("chunks", [2, 4, 8])
 @pytest.mark.parametrize("prior", [False, True])
 def test_time_chunks_match_the_oracle(kb, chunks, prior):
