@@ -92,7 +92,10 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
     constexpr int HP = SPT / 2;  // pairs of states per thread
     static_assert(SPT % 2 == 0, "states are processed in pairs");
     // helper warps split by task: the first NH/2 load and stage inputs, the others sum and store outputs
-    constexpr int kProducers = (NH / 2) * 32, kDrainers = Sh::kHelpers - kProducers;
+    // With the epilogue the drainers carry the heavier load (activation, skip, second store): three drainer warps
+    // and one loader warp there, where that keeps a drainer thread on one channel pair from tile to tile.
+    constexpr bool kWideDrain = EPI && NH == 4 && (3 * 32) % (MC / 2) == 0;
+    constexpr int kProducers = kWideDrain ? 32 : (NH / 2) * 32, kDrainers = Sh::kHelpers - kProducers;
     static_assert(NH >= 2, "one loading and one storing helper warp at least");
     static_assert(TT % kCkptInterval == 0, "checkpoints fall on fixed steps of a tile");
 

@@ -232,8 +232,8 @@ def pick_time_chunks(B: int, L: int, M: int, S: int, requested: Optional[int] = 
     The kernels put one CTA on every 32 / 16 / 8 ... channels (d_state 16 / 32 / 64 ...) of every batch element.
     When that grid leaves most of the GPU empty, the sequence is cut into C chunks that run as B*C batch entries;
     building the chunks' start states costs about 0.7x of a forward + backward pass on top, so chunking is only
-    chosen when the plain grid fills less than a third of the resident CTA slots. C divides L, chunks keep at
-    least 64 steps. ``requested`` (or the environment variable KLA_B200_TIME_CHUNKS) overrides the choice; it is
+    chosen when the plain grid fills less than a third of the resident CTA slots; then up to 16 chunks, enough
+    for about four waves of CTAs. C divides L, chunks keep at least 64 steps. ``requested`` (or the environment variable KLA_B200_TIME_CHUNKS) overrides the choice; it is
     lowered to the nearest usable divisor of L."""
     import os
 
@@ -247,7 +247,8 @@ def pick_time_chunks(B: int, L: int, M: int, S: int, requested: Optional[int] = 
     if requested is None:
         if ctas == 0 or 3 * ctas > _RESIDENT_CTAS:
             return 1
-        want = _RESIDENT_CTAS // ctas
+        # measured on B200 (T=4096, M=1024): several waves of short chunks beat one wave of long ones, up to 16 chunks
+        want = min(16, (4 * _RESIDENT_CTAS) // ctas)
     else:
         want = max(1, int(requested))
     want = min(want, max(1, L // _MIN_CHUNK_STEPS), max(1, 65535 // max(B, 1)))
@@ -289,8 +290,8 @@ class _KLAScanB200(torch.autograd.Function):
             y, y_var, lam_all, eta_all, ckpt = _launch_fwd(
                 vc, lc, kc, qc, a, p, lam_in, eta_in, prior, out_dtype, need_grad)
             S = k.shape[2]
-            lam_fin = lam_all.view(B, C, M, S)[:, C - 1].contiguous()
-            eta_fin = eta_all.view(B, C, M, S)[:, C - 1].contiguous()
+            lam_fin = lam_all.view(B, C, M, S)[:, C - 1]  # views: the last chunk's posterior is the sequence's
+            eta_fin = eta_all.view(B, C, M, S)[:, C - 1]
             ctx.save_for_backward(v, lambda_v, k, q, a, p, lam0, eta0, ckpt, lam_in, eta_in)
             y, y_var = y.view(B, L, M), y_var.view(B, L, M)
         else:

@@ -443,7 +443,7 @@ def test_sequence_sharded_scan_under_gloo():
 def test_chunk_count_follows_the_shape():
     pick = ops.pick_time_chunks
     assert pick(8, 4096, 1024, 16) == 1          # the grid already fills the GPU
-    assert pick(1, 4096, 1024, 16) == 8          # 32 CTAs: cut the sequence
+    assert pick(1, 4096, 1024, 16) == 16         # 32 CTAs: cut the sequence
     assert pick(1, 4096, 1024, 16, 1) == 1       # switched off
     assert pick(1, 100, 64, 16, 8) == 1          # chunks keep at least 64 steps
     assert pick(1, 1100, 64, 16, 8) == 5         # C divides L
