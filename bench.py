@@ -571,15 +571,53 @@ def strong_block(dev, rank, world, steps):
     out = run(mine, groups, dyb, dyvb)
     tn = _event_time(lambda: run(mine, groups, dyb, dyvb), steps, 3, barrier)
 
+    # The same step with the host taken out of the way: at 8 ranks a block's kernels take about half a millisecond,
+    # less than Python needs to issue them. The block's forward + backward (same kernels, same autograd path) are
+    # captured once in a CUDA graph and replayed; the all-reduces are issued after each replay, outside the graph,
+    # as one NCCL call per group (da and dp, and dk and dq, share a buffer).
+    graphed = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                run(mine, None, dyb, dyvb)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            g_out = run(mine, None, dyb, dyvb)
+            ap_buf = torch.stack([g_out[6], g_out[7]])   # da, dp
+            kq_buf = torch.stack([g_out[4], g_out[5]])   # dk, dq
+
+        def replay():
+            graph.replay()
+            if groups.batch_group is not None:
+                dist.all_reduce(ap_buf, group=groups.batch_group)
+            if groups.channel_group is not None:
+                dist.all_reduce(kq_buf, group=groups.channel_group)
+
+        tg = _event_time(replay, steps, 3, barrier)
+        replay()
+        dev_g = max(_dev_rel(ap_buf[0], ref[6][ms]), _dev_rel(ap_buf[1], ref[7][ms]),
+                    _dev_rel(kq_buf[0], ref[4][bs]), _dev_rel(kq_buf[1], ref[5][bs]),
+                    _dev_rel(g_out[0], ref[0][bs, :, ms]), _dev_rel(g_out[2], ref[2][bs, :, ms]))
+        graphed = [tg, dev_g]
+    except Exception as exc:  # noqa: BLE001
+        if world > 1:
+            raise
+        graphed = f"{type(exc).__name__}: {exc}"[:200]
+
     y, yv, dv, dlv, dk, dq, da, dp = out
     ry, ryv, rdv, rdlv, rdk, rdq, rda, rdp = ref
     elem = max(_dev_ratio(y, ry[bs, :, ms]), _dev_ratio(yv, ryv[bs, :, ms]), _dev_ratio(dv, rdv[bs, :, ms]),
                _dev_ratio(dlv, rdlv[bs, :, ms]))
     red = max(_dev_rel(dk, rdk[bs]), _dev_rel(dq, rdq[bs]), _dev_rel(da, rda[ms]), _dev_rel(dp, rdp[ms]))
-    tm = torch.tensor([tn, t1, elem, red], device=dev, dtype=torch.float64)
+    tm = torch.tensor([tn, t1, elem, red] + (graphed if isinstance(graphed, list) else [0.0, 0.0]), device=dev,
+                      dtype=torch.float64)
     if world > 1:
         dist.all_reduce(tm, op=dist.ReduceOp.MAX)
-    tn, t1, elem, red = tm.tolist()
+    tn, t1, elem, red, tg, dev_g = tm.tolist()
     Bb, Mb = blk.b1 - blk.b0, blk.m1 - blk.m0
     return {
         "workload": f"ONE problem B={B} T={T} M={M} S={S} fp32 split over {world} rank(s): {blk.batch_parts} batch x "
@@ -590,6 +628,11 @@ def strong_block(dev, rank, world, steps):
         "time_chunks_per_rank": ops.pick_time_chunks(Bb, T, Mb, S),
         "parity": {"elementwise_max_ratio_of_rtol1e-5_atol1e-6": elem, "reduced_gradients_max_rel_err": red,
                    "against": "the same problem scanned whole on one GPU by the lane-serial kernels"},
+        "graphed": ({"ms_per_step": tg, "tokens_per_s": B * T / (tg * 1e-3), "efficiency": t1 / (world * tg),
+                     "max_rel_err": dev_g,
+                     "what": "the block's forward + backward replayed from a CUDA graph, the all-reduces issued after each "
+                             "replay (one NCCL call per group): the same kernels without the host's launch cost"}
+                    if isinstance(graphed, list) else {"error": graphed}),
         "steps": steps,
     }
 
