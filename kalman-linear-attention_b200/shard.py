@@ -110,6 +110,31 @@ def sum_grad_over(x: torch.Tensor, group) -> torch.Tensor:
     return x if group is None else _SumGradOver.apply(x, group)
 
 
+class _SumGradsOver(torch.autograd.Function):
+    """Identity on several tensors in the forward; ONE all-reduce (sum) of all their gradients in the backward:
+    the gradients are small here, so a step pays per collective call, not per byte."""
+
+    @staticmethod
+    def forward(ctx, group, *xs):
+        ctx.group = group
+        return tuple(x.view_as(x) for x in xs)
+
+    @staticmethod
+    def backward(ctx, *gs):
+        live = [g for g in gs if g is not None]
+        if not live:
+            return (None, *gs)
+        flat = torch.cat([g.reshape(-1).to(live[0].dtype) for g in live])
+        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=ctx.group)
+        parts = iter(flat.split([g.numel() for g in live]))
+        return (None, *[None if g is None else next(parts).view_as(g).to(g.dtype) for g in gs])
+
+
+def sum_grads_over(xs, group):
+    """``sum_grad_over`` for several tensors at once, with a single collective."""
+    return tuple(xs) if group is None else _SumGradsOver.apply(group, *xs)
+
+
 def take_block(blk: Block, v, lambda_v, k, q, a, p, initial_state=None):
     """Slice full tensors down to one rank's block (views, no copies)."""
     bs, ms = slice(blk.b0, blk.b1), slice(blk.m0, blk.m1)
@@ -124,10 +149,8 @@ def scan_block(scan_fn: Callable, groups: Groups, v, lambda_v, k, q, a, p,
     """Scan this rank's block with ``scan_fn`` (e.g. ``kla_scan_b200``). The
     forward communicates nothing; in the backward the gradients of a, p are
     summed over the batch group and those of k, q over the channel group, so
-    every rank ends with the gradients of the full problem for its slices."""
-    a = sum_grad_over(a, groups.batch_group)
-    p = sum_grad_over(p, groups.batch_group)
-    k = sum_grad_over(k, groups.channel_group)
-    q = sum_grad_over(q, groups.channel_group)
+    every rank ends with the gradients of the full problem for its slices (one collective per group)."""
+    a, p = sum_grads_over((a, p), groups.batch_group)
+    k, q = sum_grads_over((k, q), groups.channel_group)
     return scan_fn(v, lambda_v, k, q, a, p, initial_state=initial_state,
                    decode_from_prior=decode_from_prior)
