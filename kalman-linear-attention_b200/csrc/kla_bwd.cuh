@@ -40,7 +40,8 @@
 // 0.53 ms, the sums 0.12 ms; side by side they overlap only in part. Variants that were measured and are not kept:
 // the trajectory through tensor memory (tcgen05.st / tcgen05.ld, a third less shared-memory traffic: 1.56 ms),
 // the reverse walk on paired fp32 instructions (a third fewer instructions: 1.68 ms), other register splits between
-// the groups and deeper unrolling (1.54-1.79 ms). No single resource is the limit: issue slots, the FP32 pipe and
+// the groups and deeper unrolling (1.54-1.79 ms), the reverse walk's shared-memory reads fetched one step ahead by hand
+// (1.62 ms). No single resource is the limit: issue slots, the FP32 pipe and
 // the shared-memory pipe are each a half to three quarters busy on the SMs that hold two CTAs.
 #pragma once
 
