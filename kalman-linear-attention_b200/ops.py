@@ -16,6 +16,7 @@ can; nothing falls back silently, and there is no CPU or Triton path.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import sys
 from typing import NamedTuple, Optional
@@ -93,6 +94,17 @@ def _rowmajor_last(t: torch.Tensor) -> torch.Tensor:
     return t.contiguous()
 
 
+_NULL_CTX = contextlib.nullcontext()
+
+
+def _on(device: torch.device):
+    """Context that makes ``device`` current for a launch; free when it already is (the usual case)."""
+    idx = device.index
+    if idx is None or idx == torch.cuda.current_device():
+        return _NULL_CTX
+    return torch.cuda.device(device)
+
+
 def _stream(device: torch.device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
@@ -146,7 +158,7 @@ def _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype, nee
         ckpt=_ptr(ckpt), **_sensor_fields(sensors), **_epilogue_fields(epilogue),
         **({} if raw is None else dict(y_raw=_t3(raw[0]), y_var_raw=_t3(raw[1]))),
     )
-    with torch.cuda.device(dev):
+    with _on(dev):
         _lib.check(lib.kla_b200_scan_fwd(ctypes.byref(args), _stream(dev)))
     return y, y_var, lam_fin, eta_fin, ckpt
 
@@ -175,7 +187,7 @@ def _launch_bwd(v, lambda_v, k, q, a, p, lam0, eta0, ckpt, dy, dy_var, dlam_fin,
         dv=_t3(dv), dlambda_v=_t3(dlv), dk=_ptr(dk), dq=_ptr(dq), da=_ptr(da), dp=_ptr(dp),
         dlam0=_ptr(dlam0), deta0=_ptr(deta0), **_sensor_fields(sensors),
     )
-    with torch.cuda.device(dev):
+    with _on(dev):
         _lib.check(lib.kla_b200_scan_bwd(ctypes.byref(args), _stream(dev)))
     return dv, dlv, dk, dq, da, dp, dlam0, deta0
 
@@ -197,7 +209,7 @@ def slab_aggregate(v, lambda_v, k, a, p, *, q=None, dy=None, dy_var=None, lam0=N
         a=_ptr(a), p=_ptr(p), lam0=_ptr(lam0), eta0=_ptr(eta0),
         dy=_t3(dy), dy_var=_t3(dy_var), out=_ptr(out),
     )
-    with torch.cuda.device(v.device):
+    with _on(v.device):
         _lib.check(lib.kla_b200_slab_aggregate(ctypes.byref(args), _stream(v.device)))
     return out
 
@@ -211,7 +223,7 @@ def chunk_fold(agg: torch.Tensor, C: int, in_a, in_b, adjoint: bool):
     out_b = torch.empty((BC, M, S), device=agg.device, dtype=torch.float32)
     args = ChunkFoldArgs(B=BC // C, C=C, M=M, S=S, adjoint=int(adjoint), agg=_ptr(agg),
                          in_a=_ptr(in_a), in_b=_ptr(in_b), out_a=_ptr(out_a), out_b=_ptr(out_b))
-    with torch.cuda.device(agg.device):
+    with _on(agg.device):
         _lib.check(lib.kla_b200_chunk_fold(ctypes.byref(args), _stream(agg.device)))
     return out_a, out_b
 
@@ -408,7 +420,7 @@ class _KLAScanEpilogueB200(torch.autograd.Function):
             dout=_t3(dout), dout_var=_t3(dout_var), y_raw=_t3(raw[0] if raw else None), y_var_raw=_t3(raw[1] if raw else None),
             z=_t3(z), gate=_t3(gate), lambda_skip=_ptr(skip_flat),
             dy=_t3(dy), dy_var=_t3(dy_var), dz=_t3(dz), dgate=_t3(dgate), dlambda_skip=_ptr(dskip))
-        with torch.cuda.device(dev):
+        with _on(dev):
             _lib.check(lib.kla_b200_epilogue_bwd(ctypes.byref(args), _stream(dev)))
         if (dlam_fin is None) != (deta_fin is None):
             zero = torch.zeros((B, M, S), device=dev, dtype=torch.float32)
@@ -618,6 +630,6 @@ def kla_step_b200(
         a=_ptr(a), p=_ptr(p), lam=_ptr(lam), eta=_ptr(eta),
         y=_ptr(y), y_var=_ptr(y_var), lam_out=_ptr(lam_out), eta_out=_ptr(eta_out),
     )
-    with torch.cuda.device(dev):
+    with _on(dev):
         _lib.check(lib.kla_b200_step(ctypes.byref(args), _stream(dev)))
     return y, y_var, _state_cls()(lam=lam_out, eta=eta_out)
