@@ -356,9 +356,16 @@ def run_b200(args):
         torch.cuda.synchronize()
 
     if args.profile_batch:
-        step()
+        if args.profile_chunks > 1:
+            # the time-parallel path through the public API: aggregate, fold, forward; aggregate, fold, backward
+            req = {n: d[n].clone().requires_grad_(True) for n in ("v", "lambda_v", "k", "q", "a", "p")}
+            yy, yyv, _ = kla_b200.kla_scan_b200(*(req[n] for n in ("v", "lambda_v", "k", "q", "a", "p")),
+                                                time_chunks=args.profile_chunks)
+            torch.autograd.backward((yy, yyv), (d["dy"], d["dyvar"]))
+        else:
+            step()
         barrier()
-        print(json.dumps({"profile_only": True, "B": B, "L": T, "M": M, "S": S}))
+        print(json.dumps({"profile_only": True, "B": B, "L": T, "M": M, "S": S, "time_chunks": max(args.profile_chunks, 1)}))
         return
     sampler = ClockSampler(local)
     if rank == 0:
@@ -1468,6 +1475,9 @@ def main():
     ap.add_argument("--profile-batch", type=int, default=0,
                     help="profiling aid: run exactly one forward and one backward launch at this batch size "
                          "(same T, M, S) and exit without timing; for captures under ncu")
+    ap.add_argument("--profile-chunks", type=int, default=0,
+                    help="with --profile-batch: run that one forward + backward through the time-parallel path "
+                         "with this many time chunks (aggregate and fold kernels included)")
     ap.add_argument("--batch", type=int, default=0,
                     help="raw workload only: batch size per GPU instead of 8, for the occupancy sweep "
                          "(B=4 leaves one CTA per SM, B=16 fills every SM); the headline stays B=8")
