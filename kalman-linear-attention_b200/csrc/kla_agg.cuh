@@ -154,10 +154,10 @@ __global__ void __launch_bounds__((NW + 1) * 32) kla_agg_kernel(const __grid_con
                 for (int h = 0; h < HP; ++h) {
                     float2 phi, r;
                     chain_inputs2(lv, vv, kk[h], phi, r);
-                    const float2 c0 = fma2(cp[h], phi, dup2(1.0f)), c1 = mul2(ca2[h], phi);
-                    const float2 n00 = fma2(c1, A[2][h], mul2(c0, A[0][h])), n01 = fma2(c1, A[3][h], mul2(c0, A[1][h]));
+                    // the step as two shears: w' = p x + a2 w, then x' = x + phi w' (= (1 + p phi) x + a2 phi w)
                     const float2 n10 = fma2(ca2[h], A[2][h], mul2(cp[h], A[0][h]));
                     const float2 n11 = fma2(ca2[h], A[3][h], mul2(cp[h], A[1][h]));
+                    const float2 n00 = fma2(phi, n10, A[0][h]), n01 = fma2(phi, n11, A[1][h]);
                     A[4][h] = fma2(r, n10, mul2(ca[h], A[4][h]));
                     A[5][h] = fma2(r, n11, mul2(ca[h], A[5][h]));
                     A[6][h] = mul2(ca[h], A[6][h]);
