@@ -32,7 +32,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-from . import _lib, ops
+from . import ops
 
 
 # ------------------------------------------------------------------ kernels

@@ -9,7 +9,6 @@ all the same; no kernel faults, traps or waits without a bound.
 
 import importlib
 
-import numpy as np
 import pytest
 import torch
 
