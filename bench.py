@@ -1417,7 +1417,7 @@ def run_train_step(args):
         dist.init_process_group("nccl", device_id=dev)
     backend = args.backend or "b200"
     if backend == "b200":
-        kla_b200.register()
+        kla_b200.register(fuse_layer=args.fused_layer)
     GB, T, V = 16, 2048, 50304
     Bl = max(1, GB // world)
     if args.batch:
@@ -1455,7 +1455,9 @@ def run_train_step(args):
             "unit": UNIT, "n_gpus": world, "steps": args.steps, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong" if not args.batch else "weak", "dtype": "bf16 autocast, float32 scan", "data": "synthetic",
             "config": {"workload": f"SequenceModel(vocab 50304, d_model 768, 12 layers, d_state 16) fwd+bwd, batch {Bl} per GPU x "
-                                   f"T={T}, scan backend '{backend}', DDP over {world} rank(s)",
+                                   f"T={T}, scan backend '{backend}'" + (", KLALayer.forward through the fused route "
+                                   "(sensor prologue and skip/gate epilogue inside the scan kernels)" if args.fused_layer else "")
+                                   + f", DDP over {world} rank(s)",
                        "global_batch": Bl * world, "seq_len": T, "parallelism": f"dp{world}"},
             "loss": float(loss), "scan_kernel_launches_per_step": launches,
             "peak_memory_gb": torch.cuda.max_memory_allocated() / 1e9,
@@ -1480,6 +1482,8 @@ def main():
     ap.add_argument("--batch", type=int, default=0,
                     help="raw workload only: batch size per GPU instead of 8, for the occupancy sweep "
                          "(B=4 leaves one CTA per SM, B=16 fills every SM); the headline stays B=8")
+    ap.add_argument("--fused-layer", action="store_true",
+                    help="train_step: route KLALayer.forward through the package's fused layer forward")
     ap.add_argument("--backend", default="", help="reference_gpu child / train_step: the scan backend to run")
     ap.add_argument("--workload", default="raw", choices=["raw", "seqshard", "decode", "rawpair", "decode_layer", "prologue", "epilogue", "inference",
                                                           "reference_gpu", "_reference_gpu_child", "train_step", "generate"],

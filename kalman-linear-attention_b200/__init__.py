@@ -16,6 +16,8 @@ from . import seqshard  # noqa: F401
 from .seqshard import kla_scan_seq_sharded  # noqa: F401
 from .rawscan import affine_scan_b200, mobius_scan_b200  # noqa: F401
 from .decode import LayerDecoder, ModelDecoder  # noqa: F401
+from . import layer  # noqa: F401
+from .layer import fused_forward  # noqa: F401
 from .hostpipe import scan_fwd_bwd_host  # noqa: F401
 from ._lib import LIB_PATH, LibraryMissing, SYMBOLS  # noqa: F401
 from .build import build  # noqa: F401

@@ -19,18 +19,23 @@ from __future__ import annotations
 
 import torch
 
+from . import layer as fused_layer
 from . import ops
 
 _ORIG_STEP = None
 
 
-def register(name: str = "b200", decode_hook: bool = True) -> None:
+def register(name: str = "b200", decode_hook: bool = True, fuse_layer: bool = False) -> None:
+    """``fuse_layer=True`` also routes ``KLALayer.forward`` through ``layer.fused_forward`` for layers whose
+    config says ``backend="b200"`` (sensor prologue and skip/gate epilogue inside the scan kernels)."""
     import kla  # the reference package; ImportError if it is not installed
     import kla.layers.kla_layer as kla_layer
     import kla.ops as kla_ops_pkg
     import kla.ops.kla_ops as kla_ops
 
     kla_ops._BACKENDS[name] = ops.kla_scan_b200
+    if fuse_layer:
+        fused_layer.enable()
 
     global _ORIG_STEP
     if decode_hook and _ORIG_STEP is None:
@@ -59,6 +64,7 @@ def unregister(name: str = "b200") -> None:
     import kla.ops.kla_ops as kla_ops
 
     kla_ops._BACKENDS.pop(name, None)
+    fused_layer.disable()
     global _ORIG_STEP
     if _ORIG_STEP is not None:
         for mod in (kla_layer, kla_ops_pkg, kla):

@@ -168,6 +168,123 @@ def test_layer_forward_backward_matches_cpu_torch_backend(kla, checkpoint_ssm):
     assert not bad, bad
 
 
+@pytest.fixture()
+def fused_layers(kla):
+    """KLALayer.forward routed through the fused path for the duration of a test."""
+    layer = importlib.import_module("kalman-linear-attention_b200.layer")
+    layer.enable()
+    yield layer
+    layer.disable()
+
+
+_FUSED_CONFIGS = {
+    "default": {},
+    "checkpointed": dict(checkpoint_ssm=True),
+    "value_from_conv": dict(value_rank="conv"),
+    "low_rank_sensors": dict(value_rank=24, var_rank="dt"),
+    "vector_skip_gelu_gate": dict(lambda_skip_mode="vector", gating_activation="gelu"),
+    "bare": dict(use_gating=False, use_lambda_skip=False, use_conv=False, qk_norm=False),
+    "variance_out_prior_readout": dict(return_variance=True, decode_from_prior=True),
+}
+
+
+@pytest.mark.parametrize("name", list(_FUSED_CONFIGS))
+def test_fused_layer_forward_backward_matches_cpu_torch_backend(kla, fused_layers, name):
+    """layer.fused_forward (sensor prologue and skip/gate epilogue inside the scan kernels) against the reference
+    layer on its torch backend on the CPU: output(s) and every parameter gradient, float32."""
+    cfg = _FUSED_CONFIGS[name]
+    ref, dut = _layer_pair(kla, 256, **cfg)
+    torch.manual_seed(0)
+    x = torch.randn(2, 200, 256)
+    ref.train(); dut.train()
+
+    def loss(out):
+        return sum(o.square().sum() for o in out) if isinstance(out, tuple) else out.square().sum()
+
+    out_ref = ref(x)
+    loss(out_ref).backward()
+    lib = importlib.import_module("kalman-linear-attention_b200._lib").load()
+    n0 = lib.kla_b200_launch_count()
+    xg = x.cuda().requires_grad_(True)
+    out = dut(xg)
+    loss(out).backward()
+    torch.cuda.synchronize()
+    assert lib.kla_b200_launch_count() > n0
+    pairs = list(zip(out, out_ref)) if isinstance(out, tuple) else [(out, out_ref)]
+    for got, want in pairs:
+        torch.testing.assert_close(got.detach().cpu(), want.detach(), rtol=1e-4, atol=1e-5)
+    gp = dict(dut.named_parameters())
+    bad = []
+    for n, p in ref.named_parameters():
+        if p.grad is None:
+            assert gp[n].grad is None, n
+            continue
+        assert gp[n].grad is not None, n
+        e = _rel(gp[n].grad.cpu(), p.grad)
+        if not e < 2e-3:
+            bad.append((n, e))
+    assert not bad, bad
+
+
+def test_fused_layer_is_the_route_taken_and_saves_elementwise_kernels(kla, fused_layers):
+    """With the route enabled a b200 layer launches fewer kernels than the same layer on the reference's forward,
+    returns the same state, and leaves layers of other backends and the single-token route alone."""
+    from torch.profiler import ProfilerActivity, profile
+
+    ref, dut = _layer_pair(kla, 128)
+    dut.eval()
+    x = torch.randn(2, 64, 128).cuda()
+
+    def kernels(fn):
+        fn(); torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            fn(); torch.cuda.synchronize()
+        return sum(e.count for e in prof.key_averages() if e.device_time_total > 0)
+
+    with torch.no_grad():
+        n_fused = kernels(lambda: dut(x))
+        (out, st) = dut(x, return_state=True)
+        fused_layers.disable()
+        n_plain = kernels(lambda: dut(x))
+        (out0, st0) = dut(x, return_state=True)
+        fused_layers.enable()
+        o1, st1 = dut(x[:, :1], state=st)          # decode by one token: the reference method with the step kernel
+        fused_layers.disable()
+        o2, st2 = dut(x[:, :1], state=st0)
+        fused_layers.enable()
+    assert n_fused < n_plain, (n_fused, n_plain)
+    torch.testing.assert_close(out, out0, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(st.ssm.lam, st0.ssm.lam, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(st.ssm.eta, st0.ssm.eta, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(st.conv, st0.conv)
+    torch.testing.assert_close(o1, o2, rtol=1e-5, atol=1e-6)
+
+
+def test_fused_layer_under_bf16_autocast_tracks_the_unfused_route(kla, fused_layers):
+    """Under bf16 autocast the fused route reads the projections' bf16 slices directly and writes bf16; against the
+    reference forward with the same backend (which widens to float32 around the scan) outputs and gradients agree
+    to bf16 rounding."""
+    ref, dut = _layer_pair(kla, 256)
+    dut.train()
+    torch.manual_seed(1)
+    x = torch.randn(2, 256, 256).cuda()
+
+    def run():
+        dut.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = dut(x)
+        y.float().square().sum().backward()
+        return y.detach().float(), {n: p.grad.detach().float().clone() for n, p in dut.named_parameters()}
+
+    y_f, g_f = run()
+    fused_layers.disable()
+    y_u, g_u = run()
+    fused_layers.enable()
+    assert _rel(y_f, y_u) < 2e-2, _rel(y_f, y_u)
+    bad = [(n, _rel(g_f[n], g_u[n])) for n in g_u if not _rel(g_f[n], g_u[n]) < 5e-2]
+    assert not bad, bad
+
+
 def test_layer_runs_under_autocast_and_no_grad(kla):
     """The layer switches autocast off around the scan (kla_layer.py:261) and hands it float32; bf16 autocast
     outside must therefore change nothing for the backend, and no_grad must not ask for checkpoints."""
