@@ -337,6 +337,29 @@ typedef struct kla_b200_conv_seq_args {
 int kla_b200_conv_seq(const kla_b200_conv_seq_args *args, void *stream);
 
 /*
+ * Backward of kla_b200_conv_seq, i.e. what torch autograd computes for
+ * CausalConv1d.forward (src/kla/layers/common.py:87-96: cat, conv1d, activation,
+ * transposes): given x and the gradient dz of the activated output, dx and the
+ * sums dweight, dbias. The pre-activation is recomputed from x; nothing else of
+ * the forward is kept. dweight and dbias are ADDED to (zero them, or pass an
+ * accumulator); no gradient is formed for the carried window.
+ */
+typedef struct kla_b200_conv_seq_bwd_args {
+    int64_t B, L, D, K;
+    int32_t dtype, activation;
+    kla_b200_tensor3 x;   /* in  [B, L, D] */
+    kla_b200_tensor3 dz;  /* in  [B, L, D] */
+    const float *weight;  /* in  [D, K] */
+    const float *bias;    /* in  [D] or NULL */
+    const void *state;    /* in  [B, D, K-1] contiguous: the window before the sequence; NULL = zeros */
+    kla_b200_tensor3 dx;  /* out [B, L, D] */
+    float *dweight;       /* in/out [D, K] float32 */
+    float *dbias;         /* in/out [D] float32 or NULL */
+} kla_b200_conv_seq_bwd_args;
+
+int kla_b200_conv_seq_bwd(const kla_b200_conv_seq_bwd_args *args, void *stream);
+
+/*
  * kla_b200_step_layer is kla_b200_step with the layer's prologue and epilogue
  * folded in (src/kla/layers/kla_layer.py:199-231, 277-293, 329-338): it takes
  * the sensor projection's raw outputs and produces the input of out_proj.

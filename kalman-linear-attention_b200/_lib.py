@@ -27,6 +27,7 @@ SYMBOLS = (
     "kla_b200_epilogue_bwd",
     "kla_b200_conv_step",
     "kla_b200_conv_seq",
+    "kla_b200_conv_seq_bwd",
     "kla_b200_step_layer",
     "kla_b200_mobius_scan_fwd",
     "kla_b200_mobius_scan_bwd",
@@ -63,6 +64,15 @@ class ConvSeqArgs(Structure):
         ("dtype", c_int32), ("activation", c_int32),
         ("x", Tensor3), ("weight", c_void_p), ("bias", c_void_p), ("state", c_void_p), ("state_out", c_void_p),
         ("z", Tensor3),
+    ]
+
+
+class ConvSeqBwdArgs(Structure):
+    _fields_ = [
+        ("B", c_int64), ("L", c_int64), ("D", c_int64), ("K", c_int64),
+        ("dtype", c_int32), ("activation", c_int32),
+        ("x", Tensor3), ("dz", Tensor3), ("weight", c_void_p), ("bias", c_void_p), ("state", c_void_p),
+        ("dx", Tensor3), ("dweight", c_void_p), ("dbias", c_void_p),
     ]
 
 
@@ -201,6 +211,8 @@ def load() -> ctypes.CDLL:
     lib.kla_b200_conv_step.argtypes = [POINTER(ConvStepArgs), c_void_p]
     lib.kla_b200_conv_seq.restype = c_int
     lib.kla_b200_conv_seq.argtypes = [POINTER(ConvSeqArgs), c_void_p]
+    lib.kla_b200_conv_seq_bwd.restype = c_int
+    lib.kla_b200_conv_seq_bwd.argtypes = [POINTER(ConvSeqBwdArgs), c_void_p]
     lib.kla_b200_step_layer.restype = c_int
     lib.kla_b200_step_layer.argtypes = [POINTER(StepLayerArgs), c_void_p]
     lib.kla_b200_step.restype = c_int

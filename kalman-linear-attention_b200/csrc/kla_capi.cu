@@ -7,6 +7,7 @@
 #include <mutex>
 
 #include "../../include/kla_b200.h"
+#include "kla_conv_bwd.cuh"
 #include "kla_decode.cuh"
 #include "kla_epilogue.cuh"
 #include "kla_launch.cuh"
@@ -592,6 +593,33 @@ int kla_b200_conv_seq(const kla_b200_conv_seq_args *a, void *stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (a->dtype == KLA_B200_F32) kla_conv_seq_kernel<float><<<grid, 128, 0, st>>>(prm);
     else kla_conv_seq_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(prm);
+    g_launches++;
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
+}
+
+int kla_b200_conv_seq_bwd(const kla_b200_conv_seq_bwd_args *a, void *stream) {
+    if (a == nullptr || a->B < 0 || a->L < 0 || a->D < 0) return KLA_B200_EINVAL;
+    if (a->K < 1 || a->K > KLA_B200_MAX_CONV_TAPS) return KLA_B200_EUNSUPPORTED;
+    if (a->dtype != KLA_B200_F32 && a->dtype != KLA_B200_BF16) return KLA_B200_EUNSUPPORTED;
+    if (a->activation < KLA_B200_ACT_SILU || a->activation > KLA_B200_ACT_NONE) return KLA_B200_EINVAL;
+    if (a->B > 65535 || a->L > (1 << 30) || a->D > (1 << 30)) return KLA_B200_EUNSUPPORTED;
+    if (a->B == 0 || a->D == 0 || a->L == 0) return KLA_B200_OK;
+    if (!a->weight || !a->dweight) return KLA_B200_EINVAL;
+    const size_t esz = a->dtype == KLA_B200_F32 ? 4 : 2;
+    int rc;
+    if ((rc = check_t3(a->x, esz, true)) || (rc = check_t3(a->dz, esz, true)) || (rc = check_t3(a->dx, esz, true))) return rc;
+    if (a->state && !aligned(a->state, esz)) return KLA_B200_EALIGN;
+    const int64_t chunks = (a->L + kConvBwdChunk - 1) / kConvBwdChunk;
+    if (chunks > 65535) return KLA_B200_EUNSUPPORTED;
+    ConvSeqBwdParams prm{};
+    prm.B = (int)a->B; prm.L = (int)a->L; prm.D = (int)a->D; prm.K = (int)a->K;
+    prm.x = t3(a->x); prm.dz = t3(a->dz); prm.dx = t3(a->dx); prm.w = a->weight; prm.bias = a->bias;
+    prm.state = a->state; prm.dw = a->dweight; prm.dbias = a->dbias; prm.act = a->activation;
+    dim3 grid((unsigned)((a->D + 127) / 128), (unsigned)chunks, (unsigned)a->B);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (a->dtype == KLA_B200_F32) kla_conv_seq_bwd_kernel<float><<<grid, 128, 0, st>>>(prm);
+    else kla_conv_seq_bwd_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(prm);
     g_launches++;
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);

@@ -9,8 +9,11 @@ the gate (kla_layer.py:329-338) -- and autograd's backward of each of them.
 folded into ``kla_scan_b200``: the kernels read the sensor projection's slices in
 the activation dtype, form the precision in registers, and apply skip and gate
 where they store ``y``; the backward is the epilogue's adjoint kernel followed by
-the scan's backward kernel. The projections and the causal convolution stay the
-layer's own modules.
+the scan's backward kernel. The causal convolution in front of the sensor
+projection (``CausalConv1d``, src/kla/layers/common.py:57-96: transpose, cat,
+``conv1d``, activation, transpose back, and autograd's backward of each) runs as one
+kernel per direction in the layer's own ``[B, L, D]`` layout (``causal_conv_b200``).
+The projections stay the layer's own modules.
 
 ``enable()`` rebinds ``KLALayer.forward`` so that layers configured with
 ``backend="b200"`` take this route for sequences on an sm_100 GPU; every other
@@ -20,14 +23,83 @@ to the original method. ``disable()`` restores it.
 
 from __future__ import annotations
 
+import ctypes
 import sys
 
 import torch
 import torch.nn.functional as F
 
-from .ops import kla_scan_b200
+from . import _lib
+from .ops import _on, _rowmajor_last, _stream, _t3, kla_scan_b200
 
 _ORIG_FORWARD = None
+
+
+class _CausalConvB200(torch.autograd.Function):
+    """``CausalConv1d.forward`` (common.py:87-96) on ``[B, L, D]`` tensors: ``kla_b200_conv_seq`` forward,
+    ``kla_b200_conv_seq_bwd`` backward (the pre-activation is recomputed from ``x``)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, state, activation):
+        B, L, D = x.shape
+        K = weight.shape[-1]
+        lib = _lib.load()
+        w = weight.detach().float().reshape(D, K).contiguous()
+        b = None if bias is None else bias.detach().float().contiguous()
+        x = _rowmajor_last(x)
+        if state is None:
+            state = torch.zeros((B, D, K - 1), device=x.device, dtype=x.dtype)
+        else:
+            state = state.detach().to(x.dtype).contiguous()
+        z = torch.empty((B, L, D), device=x.device, dtype=x.dtype)
+        new_state = torch.empty_like(state)
+        args = _lib.ConvSeqArgs(B=B, L=L, D=D, K=K, dtype=_lib.F32 if x.dtype == torch.float32 else _lib.BF16,
+                                activation=_lib.ACT[activation], x=_t3(x), weight=w.data_ptr(),
+                                bias=None if b is None else b.data_ptr(), state=state.data_ptr(),
+                                state_out=new_state.data_ptr(), z=_t3(z))
+        with _on(x.device):
+            _lib.check(lib.kla_b200_conv_seq(ctypes.byref(args), _stream(x.device)))
+        ctx.save_for_backward(x, w, b, state)
+        ctx.activation, ctx.wshape = activation, weight.shape
+        ctx.wdtype, ctx.bdtype = weight.dtype, None if bias is None else bias.dtype
+        ctx.mark_non_differentiable(new_state)
+        return z, new_state
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, dz, _dstate):
+        x, w, b, state = ctx.saved_tensors
+        B, L, D = x.shape
+        K = w.shape[1]
+        dz = _rowmajor_last(dz if dz.dtype == x.dtype else dz.to(x.dtype))
+        dx = torch.empty((B, L, D), device=x.device, dtype=x.dtype)
+        dw = torch.zeros((D, K), device=x.device, dtype=torch.float32)
+        db = None if b is None else torch.zeros((D,), device=x.device, dtype=torch.float32)
+        args = _lib.ConvSeqBwdArgs(B=B, L=L, D=D, K=K, dtype=_lib.F32 if x.dtype == torch.float32 else _lib.BF16,
+                                   activation=_lib.ACT[ctx.activation], x=_t3(x), dz=_t3(dz), weight=w.data_ptr(),
+                                   bias=None if b is None else b.data_ptr(), state=state.data_ptr(), dx=_t3(dx),
+                                   dweight=dw.data_ptr(), dbias=None if db is None else db.data_ptr())
+        with _on(x.device):
+            _lib.check(_lib.load().kla_b200_conv_seq_bwd(ctypes.byref(args), _stream(x.device)))
+        return dx, dw.reshape(ctx.wshape).to(ctx.wdtype), None if db is None else db.to(ctx.bdtype), None, None
+
+
+def causal_conv_b200(x: torch.Tensor, weight: torch.Tensor, bias, state=None, activation: str = "silu"):
+    """Depthwise causal convolution over time with its activation, ``x`` ``[B, L, D]`` float32 or bfloat16,
+    ``weight`` ``[D, 1, K]`` (``K <= 8``), ``state`` the ``K-1`` inputs before the sequence (``[B, D, K-1]``, zeros
+    when None). Returns ``(z [B, L, D], new_state)`` like the reference module; differentiable with respect to
+    ``x``, ``weight`` and ``bias`` (the carried window is treated as a constant)."""
+    return _CausalConvB200.apply(x, weight, bias, state, activation)
+
+
+def _conv(layer, z, conv_state):
+    """The layer's convolution: the B200 kernels where they apply, the layer's own module otherwise."""
+    conv, cfg = layer.conv, layer.config
+    if (z.dtype in (torch.float32, torch.bfloat16) and conv.kernel_size <= _lib.MAX_CONV_TAPS
+            and cfg.conv_activation in ("silu", "gelu", "relu")
+            and not (conv_state is not None and conv_state.requires_grad and torch.is_grad_enabled())):
+        return causal_conv_b200(z, conv.weight, conv.bias, conv_state, cfg.conv_activation)
+    return conv(z, conv_state)
 
 
 def _fusable(layer, x: torch.Tensor, state) -> bool:
@@ -57,7 +129,7 @@ def fused_forward(layer, x: torch.Tensor, state=None, return_state: bool = False
         z, gate = projected, None
     conv_state = state.conv if state is not None else None
     if layer.conv is not None:
-        z, conv_state = layer.conv(z, conv_state)
+        z, conv_state = _conv(layer, z, conv_state)
 
     # the four sensor signals, left in the dtype and memory the projection wrote them in (kla_layer.py:199-222)
     v, log_sigma_v, k, q = torch.split(layer.sensor_proj(z), [layer._w_value, layer._w_var, S, S], dim=-1)

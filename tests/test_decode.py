@@ -167,3 +167,69 @@ def test_prefill_then_decode_matches_reference_layer(name):
         out = res[0] if isinstance(res, tuple) else res
         torch.testing.assert_close(out.cpu(), torch.from_numpy(z[f"out{t}"]), rtol=2e-4, atol=3e-5)
     torch.testing.assert_close(state[1].cpu(), torch.from_numpy(z["lam3"]), rtol=1e-4, atol=1e-5)
+
+
+# ------------------------------------------------------------ causal convolution over a sequence, forward + backward
+
+def _conv_module_math(x, weight, bias, state, act):
+    """CausalConv1d.forward (src/kla/layers/common.py:87-96) as plain torch operations."""
+    B, L, D = x.shape
+    K = weight.shape[-1]
+    x_t = x.transpose(1, 2)
+    if state is None:
+        state = torch.zeros(B, D, K - 1, device=x.device, dtype=x.dtype)
+    x_pad = torch.cat((state.to(x_t.dtype), x_t), dim=-1)
+    y = torch.nn.functional.conv1d(x_pad, weight, bias, groups=D)
+    return getattr(torch.nn.functional, act)(y).transpose(1, 2), x_pad[..., x_pad.shape[-1] - (K - 1):]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,L,D,K,act,with_state,with_bias", [
+    (2, 200, 96, 4, "silu", False, True),     # the layer's defaults; L not a multiple of the kernels' chunks
+    (1, 64, 130, 4, "gelu", True, True),      # carried window, channels not a multiple of the block
+    (3, 129, 32, 8, "relu", True, False),     # most taps, no bias
+    (2, 2, 16, 4, "silu", True, True),        # sequence shorter than the window
+    (2, 33, 20, 1, "silu", False, True),      # one tap: no window at all
+    (2, 70, 64, 2, "gelu", False, False),
+])
+def test_causal_conv_forward_backward(B, L, D, K, act, with_state, with_bias):
+    layer = import_module("kalman-linear-attention_b200.layer")
+    g = torch.Generator().manual_seed(B * 1000 + L + K)
+    # x as the layer hands it over: one half of a wider projection, i.e. a view with a row stride of 2 D
+    wide = torch.randn(B, L, 2 * D, generator=g).cuda()
+    weight = (torch.randn(D, 1, K, generator=g) * 0.5).cuda().requires_grad_(True)
+    bias = torch.randn(D, generator=g).cuda().requires_grad_(True) if with_bias else None
+    state = torch.randn(B, D, K - 1, generator=g).cuda() if with_state else None
+    dz = torch.randn(B, L, D, generator=g).cuda()
+
+    def run(fn):
+        w2 = wide.clone().requires_grad_(True)
+        z, st = fn(w2[..., :D], weight, bias, state, act)
+        grads = torch.autograd.grad(z, [w2, weight] + ([bias] if with_bias else []), dz)
+        return [z.detach(), st.detach()] + [t.detach() for t in grads]
+
+    got = run(layer.causal_conv_b200)
+    want = run(_conv_module_math)
+    names = ["z", "new_state", "dx", "dweight", "dbias"]
+    for n, a_, b_ in zip(names, got, want):
+        assert a_.shape == b_.shape, n
+        torch.testing.assert_close(a_, b_, rtol=2e-5, atol=2e-5, msg=lambda m, n=n: f"{n}: {m}")
+
+
+@pytest.mark.gpu
+def test_causal_conv_bf16_tracks_float32():
+    layer = import_module("kalman-linear-attention_b200.layer")
+    g = torch.Generator().manual_seed(5)
+    B, L, D, K = 2, 300, 256, 4
+    x32 = torch.randn(B, L, D, generator=g).cuda()
+    weight = (torch.randn(D, 1, K, generator=g) * 0.5).cuda().requires_grad_(True)
+    bias = torch.randn(D, generator=g).cuda().requires_grad_(True)
+    dz = torch.randn(B, L, D, generator=g).cuda()
+    outs = {}
+    for dt in (torch.float32, torch.bfloat16):
+        x = x32.to(dt).requires_grad_(True)
+        z, _ = layer.causal_conv_b200(x, weight, bias, None, "silu")
+        assert z.dtype == dt
+        outs[dt] = [z.float().detach()] + [t.float() for t in torch.autograd.grad(z, [x, weight, bias], dz.to(dt))]
+    for a_, b_ in zip(outs[torch.bfloat16], outs[torch.float32]):
+        assert ((a_ - b_).abs().max() / (b_.abs().max() + 1e-6)).item() < 2e-2
