@@ -100,6 +100,11 @@ int check_common(int64_t B, int64_t L, int64_t M, int64_t S, int32_t in_dtype, i
     return KLA_B200_OK;
 }
 
+// rows of t can be read and written two elements at a time
+bool pair_ok(const kla_b200_tensor3 &t, size_t esz) {
+    return (reinterpret_cast<uintptr_t>(t.ptr) % (2 * esz)) == 0 && t.stride_b % 2 == 0 && t.stride_t % 2 == 0;
+}
+
 int check_t3(const kla_b200_tensor3 &t, size_t esz, bool required) {
     if (t.ptr == nullptr) return required ? KLA_B200_EINVAL : KLA_B200_OK;
     if (!aligned(t.ptr, esz)) return KLA_B200_EALIGN;
@@ -589,10 +594,23 @@ int kla_b200_conv_seq(const kla_b200_conv_seq_args *a, void *stream) {
     prm.B = (int)a->B; prm.L = (int)a->L; prm.D = (int)a->D; prm.K = (int)a->K;
     prm.x = t3(a->x); prm.z = t3(a->z); prm.w = a->weight; prm.bias = a->bias; prm.state = a->state;
     prm.state_out = a->state_out; prm.act = a->activation;
-    dim3 grid((unsigned)((a->D + 127) / 128), (unsigned)chunks, (unsigned)a->B);
+    // two channels per thread when every row starts on a 2-element boundary
+    const bool pair = a->D % 2 == 0 && pair_ok(a->x, esz) && pair_ok(a->z, esz);
+    const int64_t lanes = pair ? a->D / 2 : a->D;
+    dim3 grid((unsigned)((lanes + 127) / 128), (unsigned)chunks, (unsigned)a->B);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (a->dtype == KLA_B200_F32) kla_conv_seq_kernel<float><<<grid, 128, 0, st>>>(prm);
-    else kla_conv_seq_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(prm);
+#define KLA_CONV_LAUNCH(KERNEL, T)                                                    \
+    do {                                                                              \
+        if (a->K <= 4) {                                                              \
+            if (pair) KERNEL<T, 2, 4><<<grid, 128, 0, st>>>(prm);                     \
+            else KERNEL<T, 1, 4><<<grid, 128, 0, st>>>(prm);                          \
+        } else {                                                                      \
+            if (pair) KERNEL<T, 2, kConvMaxTaps><<<grid, 128, 0, st>>>(prm);          \
+            else KERNEL<T, 1, kConvMaxTaps><<<grid, 128, 0, st>>>(prm);               \
+        }                                                                             \
+    } while (0)
+    if (a->dtype == KLA_B200_F32) KLA_CONV_LAUNCH(kla_conv_seq_kernel, float);
+    else KLA_CONV_LAUNCH(kla_conv_seq_kernel, __nv_bfloat16);
     g_launches++;
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
@@ -616,10 +634,17 @@ int kla_b200_conv_seq_bwd(const kla_b200_conv_seq_bwd_args *a, void *stream) {
     prm.B = (int)a->B; prm.L = (int)a->L; prm.D = (int)a->D; prm.K = (int)a->K;
     prm.x = t3(a->x); prm.dz = t3(a->dz); prm.dx = t3(a->dx); prm.w = a->weight; prm.bias = a->bias;
     prm.state = a->state; prm.dw = a->dweight; prm.dbias = a->dbias; prm.act = a->activation;
+    // one channel per thread: with two, the backward's five register windows cost more in occupancy than the wider
+    // accesses give back (0.35 against 0.22 ms at B=16, L=2048, D=1536, bfloat16)
     dim3 grid((unsigned)((a->D + 127) / 128), (unsigned)chunks, (unsigned)a->B);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (a->dtype == KLA_B200_F32) kla_conv_seq_bwd_kernel<float><<<grid, 128, 0, st>>>(prm);
-    else kla_conv_seq_bwd_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(prm);
+#define KLA_CONV_BWD_LAUNCH(T)                                                                  \
+    do {                                                                                        \
+        if (a->K <= 4) kla_conv_seq_bwd_kernel<T, 1, 4><<<grid, 128, 0, st>>>(prm);             \
+        else kla_conv_seq_bwd_kernel<T, 1, kConvMaxTaps><<<grid, 128, 0, st>>>(prm);            \
+    } while (0)
+    if (a->dtype == KLA_B200_F32) KLA_CONV_BWD_LAUNCH(float);
+    else KLA_CONV_BWD_LAUNCH(__nv_bfloat16);
     g_launches++;
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);

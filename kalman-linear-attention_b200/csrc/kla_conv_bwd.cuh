@@ -32,9 +32,19 @@ struct ConvSeqBwdParams {
     int act;
 };
 
-template <typename T>
+// derivative of the activation with the hardware's exp2 and reciprocal approximations for the sigmoid of silu
+// (relative error ~1e-6), as activate_fast
+__device__ __forceinline__ float activate_slope_fast(float x, int act) {
+    if (act == kActSilu) {
+        const float s = rcp_approx(1.0f + __expf(-x));
+        return s * fmaf(x, 1.0f - s, 1.0f);
+    }
+    return activate_slope(x, act);
+}
+
+template <typename T, int VEC, int KT>
 __global__ void __launch_bounds__(128) kla_conv_seq_bwd_kernel(const ConvSeqBwdParams prm) {
-    const int d = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.z;
+    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * VEC, b = blockIdx.z;
     const int t0 = blockIdx.y * kConvBwdChunk;
     if (d >= prm.D) return;
     const int K = prm.K, L = prm.L;
@@ -45,59 +55,78 @@ __global__ void __launch_bounds__(128) kla_conv_seq_bwd_kernel(const ConvSeqBwdP
     // Windows and taps sit right-aligned in arrays of kConvMaxTaps entries, so that every index below is a
     // compile-time constant (the arrays stay in registers for any K): xw[i] is x at time t - (MAXT-1) + i with the
     // newest input last, wr the taps aligned the same way (zeros in front), dwin the last MAXT values of dpre,
-    // wl the taps from the front (zeros behind).
-    constexpr int MAXT = kConvMaxTaps;
+    // wl the taps from the front (zeros behind). A thread owns VEC adjacent channels (see kla_conv_seq_kernel).
+    constexpr int MAXT = KT;  // 4 for up to four taps, else kConvMaxTaps
     const int lead = MAXT - K;  // entries in front of the K live ones
-    float wl[MAXT], wr[MAXT], xw[MAXT], dwin[MAXT], accw[MAXT];
+    float wl[MAXT][VEC], wr[MAXT][VEC], xw[MAXT][VEC], dwin[MAXT][VEC], accw[MAXT][VEC], bias[VEC], accb[VEC];
 #pragma unroll
-    for (int i = 0; i < MAXT; ++i) {
-        wl[i] = i < K ? prm.w[(long long)d * K + i] : 0.0f;
-        wr[i] = i >= lead ? prm.w[(long long)d * K + (i - lead)] : 0.0f;
-        dwin[i] = accw[i] = 0.0f;
-        xw[i] = 0.0f;
-        if (i > lead) {  // the K-1 inputs before t0, one place further back than in the loop, which shifts first
-            const int t = t0 - MAXT + i;
-            xw[i] = t >= 0 ? to_f32<T>(xb[(long long)t * prm.x.st]) : (st != nullptr ? to_f32<T>(st[t + (K - 1)]) : 0.0f);
-        }
-    }
-    const float bias = prm.bias != nullptr ? prm.bias[d] : 0.0f;
-    float accb = 0.0f;
-    const int t1 = min(L, t0 + kConvBwdChunk);
-    const int tend = t1 + K - 1;  // dx[t1 - 1] needs dpre up to t1 + K - 2
-#pragma unroll 2
-    for (int t = t0; t < tend; ++t) {
-        float dpre = 0.0f;
-        if (t < L) {
-            const float xin = to_f32<T>(xb[(long long)t * prm.x.st]);
-            const float g = to_f32<T>(gb[(long long)t * prm.dz.st]);
+    for (int e = 0; e < VEC; ++e) {
+        bias[e] = prm.bias != nullptr ? prm.bias[d + e] : 0.0f;
+        accb[e] = 0.0f;
 #pragma unroll
-            for (int i = 0; i < MAXT - 1; ++i) xw[i] = i >= lead ? xw[i + 1] : 0.0f;
-            xw[MAXT - 1] = xin;
-            float pre = bias;
-#pragma unroll
-            for (int i = 0; i < MAXT; ++i) pre = fmaf(wr[i], xw[i], pre);
-            dpre = g * activate_slope(pre, prm.act);
-            if (t < t1) {  // the sums over t belong to the chunk that owns t
-                accb += dpre;
-#pragma unroll
-                for (int i = 0; i < MAXT; ++i) accw[i] = fmaf(dpre, xw[i], accw[i]);
+        for (int i = 0; i < MAXT; ++i) {
+            wl[i][e] = i < K ? prm.w[(long long)(d + e) * K + i] : 0.0f;
+            wr[i][e] = i >= lead ? prm.w[(long long)(d + e) * K + (i - lead)] : 0.0f;
+            dwin[i][e] = accw[i][e] = 0.0f;
+            xw[i][e] = 0.0f;
+            if (i > lead) {  // the K-1 inputs before t0, one place further back than in the loop, which shifts first
+                const int t = t0 - MAXT + i;
+                xw[i][e] = t >= 0 ? to_f32<T>(xb[(long long)t * prm.x.st + e])
+                                  : (st != nullptr ? to_f32<T>(st[(long long)e * (K - 1) + t + (K - 1)]) : 0.0f);
             }
         }
+    }
+    const int t1 = min(L, t0 + kConvBwdChunk);
+    const int tend = t1 + K - 1;  // dx[t1 - 1] needs dpre up to t1 + K - 2
+    for (int tb = t0; tb < tend; tb += kConvBlock) {
+        float xin[kConvBlock][VEC], gin[kConvBlock][VEC];
 #pragma unroll
-        for (int i = 0; i < MAXT - 1; ++i) dwin[i] = dwin[i + 1];
-        dwin[MAXT - 1] = dpre;
-        const int u = t - (K - 1);
-        if (u >= t0) {  // dx[u] = sum_j w[j] dpre[t - j]
-            float acc = 0.0f;
+        for (int u = 0; u < kConvBlock; ++u)
+            if (tb + u < tend && tb + u < L) {
+                conv_load<T, VEC>(xb + (long long)(tb + u) * prm.x.st, xin[u]);
+                conv_load<T, VEC>(gb + (long long)(tb + u) * prm.dz.st, gin[u]);
+            }
 #pragma unroll
-            for (int jj = 0; jj < MAXT; ++jj) acc = fmaf(wl[jj], dwin[MAXT - 1 - jj], acc);
-            ob[(long long)u * prm.dx.st] = from_f32<T>(acc);
+        for (int u = 0; u < kConvBlock; ++u) {
+            const int t = tb + u;
+            if (t < tend) {
+                float out[VEC];
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    float dpre = 0.0f;
+                    if (t < L) {
+#pragma unroll
+                        for (int i = 0; i < MAXT - 1; ++i) xw[i][e] = i >= lead ? xw[i + 1][e] : 0.0f;
+                        xw[MAXT - 1][e] = xin[u][e];
+                        float pre = bias[e];
+#pragma unroll
+                        for (int i = 0; i < MAXT; ++i) pre = fmaf(wr[i][e], xw[i][e], pre);
+                        dpre = gin[u][e] * activate_slope_fast(pre, prm.act);
+                        if (t < t1) {  // the sums over t belong to the chunk that owns t
+                            accb[e] += dpre;
+#pragma unroll
+                            for (int i = 0; i < MAXT; ++i) accw[i][e] = fmaf(dpre, xw[i][e], accw[i][e]);
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < MAXT - 1; ++i) dwin[i][e] = dwin[i + 1][e];
+                    dwin[MAXT - 1][e] = dpre;
+                    float acc = 0.0f;  // dx[u] = sum_j w[j] dpre[t - j], u = t - (K-1)
+#pragma unroll
+                    for (int jj = 0; jj < MAXT; ++jj) acc = fmaf(wl[jj][e], dwin[MAXT - 1 - jj][e], acc);
+                    out[e] = acc;
+                }
+                if (t - (K - 1) >= t0) conv_store<T, VEC>(ob + (long long)(t - (K - 1)) * prm.dx.st, out);
+            }
         }
     }
 #pragma unroll
-    for (int i = 0; i < MAXT; ++i)
-        if (i >= lead) atomicAdd(prm.dw + (long long)d * K + (i - lead), accw[i]);
-    if (prm.dbias != nullptr) atomicAdd(prm.dbias + d, accb);
+    for (int e = 0; e < VEC; ++e) {
+#pragma unroll
+        for (int i = 0; i < MAXT; ++i)
+            if (i >= lead) atomicAdd(prm.dw + (long long)(d + e) * K + (i - lead), accw[i][e]);
+        if (prm.dbias != nullptr) atomicAdd(prm.dbias + d + e, accb[e]);
+    }
 }
 
 }  // namespace kla

@@ -71,58 +71,100 @@ struct ConvSeqParams {
 };
 
 constexpr int kConvChunk = 32;
+constexpr int kConvBlock = 8;  // steps whose inputs are fetched before any of them is used
 
-template <typename T>
+// VEC consecutive channels of one row, widened to float32 (VEC = 2: one 4- or 8-byte access)
+template <typename T, int VEC>
+__device__ __forceinline__ void conv_load(const T *p, float (&x)[VEC]) {
+    if constexpr (VEC == 1) {
+        x[0] = to_f32<T>(*p);
+    } else if constexpr (sizeof(T) == 2) {
+        const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162 *>(p);
+        x[0] = __low2float(v);
+        x[1] = __high2float(v);
+    } else {
+        const float2 v = *reinterpret_cast<const float2 *>(p);
+        x[0] = v.x;
+        x[1] = v.y;
+    }
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void conv_store(T *p, const float (&x)[VEC]) {
+    if constexpr (VEC == 1) {
+        *p = from_f32<T>(x[0]);
+    } else if constexpr (sizeof(T) == 2) {
+        *reinterpret_cast<__nv_bfloat162 *>(p) = __floats2bfloat162_rn(x[0], x[1]);
+    } else {
+        *reinterpret_cast<float2 *>(p) = make_float2(x[0], x[1]);
+    }
+}
+
+// A thread owns VEC adjacent channels (2 when the rows allow 4-/8-byte accesses) and fetches the inputs of
+// kConvBlock steps before it uses any of them, so that a warp keeps kilobytes, not one 64-byte row, in flight.
+// Window and taps sit right-aligned in arrays of kConvMaxTaps entries (zeros in front of the K live ones), which
+// keeps every register index a compile-time constant for any K.
+// KT: the length of those arrays, 4 for up to four taps (the layer's default), else kConvMaxTaps.
+template <typename T, int VEC, int KT>
 __global__ void __launch_bounds__(128) kla_conv_seq_kernel(const ConvSeqParams prm) {
-    const int d = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.z;
+    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * VEC, b = blockIdx.z;
     const int t0 = blockIdx.y * kConvChunk;
     if (d >= prm.D) return;
-    const int K = prm.K, L = prm.L;
+    constexpr int MAXT = KT;
+    const int K = prm.K, L = prm.L, lead = MAXT - K;
     const T *xb = static_cast<const T *>(prm.x.ptr) + (long long)b * prm.x.sb + d;
     T *zb = static_cast<T *>(prm.z.ptr) + (long long)b * prm.z.sb + d;
     const T *st = static_cast<const T *>(prm.state) + ((long long)b * prm.D + d) * (K - 1);
     T *sto = static_cast<T *>(prm.state_out) + ((long long)b * prm.D + d) * (K - 1);
-    float w[kConvMaxTaps], win[kConvMaxTaps];  // win[jj]: input at time t - (K-1) + jj, jj < K-1
+    // xw[i]: input at time t - (MAXT-1) + i once step t has shifted its input in; before the first step the window
+    // sits one place further back
+    float wr[MAXT][VEC], xw[MAXT][VEC], bias[VEC];
 #pragma unroll
-    for (int jj = 0; jj < kConvMaxTaps; ++jj) {
-        w[jj] = jj < K ? prm.w[(long long)d * K + jj] : 0.0f;
-        win[jj] = 0.0f;
-        if (jj < K - 1) {
-            const int t = t0 - (K - 1) + jj;  // before the prompt: the carried window
-            win[jj] = t >= 0 ? to_f32<T>(xb[(long long)t * prm.x.st]) : to_f32<T>(st[t + (K - 1)]);
+    for (int e = 0; e < VEC; ++e) {
+        bias[e] = prm.bias != nullptr ? prm.bias[d + e] : 0.0f;
+#pragma unroll
+        for (int i = 0; i < MAXT; ++i) {
+            wr[i][e] = i >= lead ? prm.w[(long long)(d + e) * K + (i - lead)] : 0.0f;
+            xw[i][e] = 0.0f;
+            if (i > lead) {
+                const int t = t0 - MAXT + i;  // before the prompt: the carried window
+                xw[i][e] = t >= 0 ? to_f32<T>(xb[(long long)t * prm.x.st + e]) : to_f32<T>(st[(long long)e * (K - 1) + t + (K - 1)]);
+            }
         }
     }
-    const float bias = prm.bias != nullptr ? prm.bias[d] : 0.0f;
     const int t1 = min(L, t0 + kConvChunk);
-    const bool last = t1 == L;
-    // the window after the prompt is made of the last K-1 inputs; those older than the prompt come from the
-    // carried window
-    float keep[kConvMaxTaps];
-    if (last) {
+    for (int tb = t0; tb < t1; tb += kConvBlock) {
+        float xin[kConvBlock][VEC];
 #pragma unroll
-        for (int jj = 0; jj < kConvMaxTaps; ++jj)
-            if (jj < K - 1) {
-                const int t = L - (K - 1) + jj;
-                keep[jj] = t >= 0 ? to_f32<T>(xb[(long long)t * prm.x.st]) : to_f32<T>(st[t + (K - 1)]);
+        for (int u = 0; u < kConvBlock; ++u)
+            if (tb + u < t1) conv_load<T, VEC>(xb + (long long)(tb + u) * prm.x.st, xin[u]);
+#pragma unroll
+        for (int u = 0; u < kConvBlock; ++u) {
+            if (tb + u < t1) {
+                float out[VEC];
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+#pragma unroll
+                    for (int i = 0; i < MAXT - 1; ++i) xw[i][e] = i >= lead ? xw[i + 1][e] : 0.0f;
+                    xw[MAXT - 1][e] = xin[u][e];
+                    float acc = bias[e];
+#pragma unroll
+                    for (int i = 0; i < MAXT; ++i) acc = fmaf(wr[i][e], xw[i][e], acc);
+                    out[e] = activate_fast(acc, prm.act);
+                }
+                conv_store<T, VEC>(zb + (long long)(tb + u) * prm.z.st, out);
             }
+        }
     }
-    for (int t = t0; t < t1; ++t) {
-        const float xin = to_f32<T>(xb[(long long)t * prm.x.st]);
-        float acc = bias;
+    if (t1 == L) {
+        // the window after the prompt is made of the last K-1 inputs; those older than the prompt come from the
+        // carried window
 #pragma unroll
-        for (int jj = 0; jj < kConvMaxTaps; ++jj)
-            if (jj < K - 1) acc = fmaf(w[jj], win[jj], acc);
-        acc = fmaf(w[K - 1], xin, acc);
-#pragma unroll
-        for (int jj = 0; jj < kConvMaxTaps - 1; ++jj)
-            if (jj + 1 < K - 1) win[jj] = win[jj + 1];
-        if (K > 1) win[K - 2] = xin;
-        zb[(long long)t * prm.z.st] = from_f32<T>(activate(acc, prm.act));
-    }
-    if (last) {
-#pragma unroll
-        for (int jj = 0; jj < kConvMaxTaps; ++jj)
-            if (jj < K - 1) sto[jj] = from_f32<T>(keep[jj]);
+        for (int e = 0; e < VEC; ++e)
+            for (int jj = 0; jj < K - 1; ++jj) {
+                const int t = L - (K - 1) + jj;
+                sto[(long long)e * (K - 1) + jj] =
+                    t >= 0 ? xb[(long long)t * prm.x.st + e] : st[(long long)e * (K - 1) + t + (K - 1)];
+            }
     }
 }
 

@@ -99,6 +99,13 @@ def test_new_entry_points_reject_bad_arguments_without_cuda(L):
                          state_out=ctypes.addressof(buf))
     assert lib.kla_b200_conv_seq(ctypes.byref(same), None) == 1                                # state_out aliases state
     assert lib.kla_b200_conv_seq(ctypes.byref(L.ConvSeqArgs(B=1, L=0, D=4, K=4)), None) == 0
+    assert lib.kla_b200_conv_seq_bwd(None, None) == 1
+    assert lib.kla_b200_conv_seq_bwd(ctypes.byref(L.ConvSeqBwdArgs(B=1, L=8, D=4, K=9)), None) == 2
+    assert lib.kla_b200_conv_seq_bwd(ctypes.byref(L.ConvSeqBwdArgs(B=1, L=8, D=4, K=4, activation=9)), None) == 1
+    assert lib.kla_b200_conv_seq_bwd(ctypes.byref(L.ConvSeqBwdArgs(B=1, L=8, D=4, K=4)), None) == 1   # NULL tensors
+    assert lib.kla_b200_conv_seq_bwd(ctypes.byref(L.ConvSeqBwdArgs(B=1, L=8, D=4, K=4, weight=ctypes.addressof(buf))),
+                                     None) == 1                                                        # no dweight
+    assert lib.kla_b200_conv_seq_bwd(ctypes.byref(L.ConvSeqBwdArgs(B=1, L=0, D=4, K=4)), None) == 0
     assert lib.kla_b200_step_layer(None, None) == 1
     assert lib.kla_b200_step_layer(ctypes.byref(L.StepLayerArgs(B=1, M=4, S=200)), None) == 2
     assert lib.kla_b200_step_layer(ctypes.byref(L.StepLayerArgs(B=1, M=4, S=4, gate_activation=7)), None) == 1
