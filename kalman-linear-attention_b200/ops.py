@@ -390,7 +390,7 @@ class _KLAScanEpilogueB200(torch.autograd.Function):
                                                        sensors, epi, raw)
         ctx.save_for_backward(v, lambda_v, k, q, a, p, lam0, eta0, ckpt, z, gate, skip_flat, *(raw or ()))
         ctx.prior, ctx.sensors, ctx.out_dtype, ctx.gate_act = prior, sensors, out_dtype, gate_act
-        ctx.skip_shape = None if skip is None else skip.shape
+        ctx.skip_shape, ctx.skip_dtype = (None, None) if skip is None else (skip.shape, skip.dtype)
         return y, y_var, lam_fin, eta_fin
 
     @staticmethod
@@ -434,7 +434,7 @@ class _KLAScanEpilogueB200(torch.autograd.Function):
             dk, dq = dk.to(k.dtype), dq.to(k.dtype)
         has_state = lam0 is not None
         return (dv, dlv, dk, dq, da, dp, dlam0 if has_state else None, deta0 if has_state else None,
-                dz, dgate, None if dskip is None else dskip.reshape(ctx.skip_shape), None, None, None, None)
+                dz, dgate, None if dskip is None else dskip.reshape(ctx.skip_shape).to(ctx.skip_dtype), None, None, None, None)
 
 
 def kla_scan_b200(

@@ -285,6 +285,31 @@ def test_fused_layer_under_bf16_autocast_tracks_the_unfused_route(kla, fused_lay
     assert not bad, bad
 
 
+def test_fused_layer_in_a_bfloat16_model(kla, fused_layers):
+    """Every parameter in bfloat16 (no autocast): gradients come back in the parameters' dtype and track the
+    unfused route to bf16 rounding."""
+    ref, dut = _layer_pair(kla, 256, lambda_skip_mode="vector")
+    dut = dut.to(torch.bfloat16).train()
+    torch.manual_seed(2)
+    x = torch.randn(2, 128, 256, device="cuda", dtype=torch.bfloat16)
+
+    def run():
+        dut.zero_grad(set_to_none=True)
+        y = dut(x)
+        y.float().square().sum().backward()
+        for n, p in dut.named_parameters():
+            assert p.grad is not None and p.grad.dtype == p.dtype, n
+        return y.detach().float(), {n: p.grad.detach().float().clone() for n, p in dut.named_parameters()}
+
+    y_f, g_f = run()
+    fused_layers.disable()
+    y_u, g_u = run()
+    fused_layers.enable()
+    assert y_f.dtype == y_u.dtype and _rel(y_f, y_u) < 3e-2, _rel(y_f, y_u)
+    bad = [(n, _rel(g_f[n], g_u[n])) for n in g_u if not _rel(g_f[n], g_u[n]) < 8e-2]
+    assert not bad, bad
+
+
 def test_layer_runs_under_autocast_and_no_grad(kla):
     """The layer switches autocast off around the scan (kla_layer.py:261) and hands it float32; bf16 autocast
     outside must therefore change nothing for the backend, and no_grad must not ask for checkpoints."""
