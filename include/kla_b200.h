@@ -105,9 +105,14 @@ typedef struct kla_b200_fwd_args {
     kla_b200_tensor3 y_raw, y_var_raw; /* out, or ptr NULL */
 } kla_b200_fwd_args;
 
-/* Bytes of the checkpoint scratch the forward writes for the backward:
- * the filter state of every lane once per kla_b200_ckpt_interval() steps. */
+/* Bytes of the scratch the forward writes for the backward: the filter state
+ * of every lane once per kla_b200_ckpt_interval() steps (rounded up to 256
+ * bytes), followed by kla_b200_segment_scratch_bytes(B, M, S) of working memory
+ * that both kernels use when they cut the sequences into segments to even out
+ * the load of the SMs (tickets, completion counts and the state handed from a
+ * segment to the next: 28 bytes per (b, m, s) plus 8 per (b, m)). */
 size_t kla_b200_ckpt_bytes(int64_t B, int64_t L, int64_t M, int64_t S);
+size_t kla_b200_segment_scratch_bytes(int64_t B, int64_t M, int64_t S);
 int64_t kla_b200_ckpt_interval(void);
 
 int kla_b200_scan_fwd(const kla_b200_fwd_args *args, void *stream);
@@ -159,7 +164,7 @@ typedef struct kla_b200_bwd_args {
     kla_b200_tensor3 v, lambda_v, k, q; /* in, as in the forward */
     const float *a, *p;
     const float *lam0, *eta0;           /* or both NULL */
-    const void *ckpt;                   /* in: what the forward wrote */
+    const void *ckpt;                   /* in: what the forward wrote (the working memory behind the checkpoints is written) */
     kla_b200_tensor3 dy;                /* in  [B, L, M] */
     kla_b200_tensor3 dy_var;            /* in  [B, L, M], ptr may be NULL = zero */
     const float *dlam_fin, *deta_fin;   /* in  [B, M, S] contiguous, or both NULL = zero */

@@ -17,6 +17,7 @@ STATIC_CKPT_BYTES = 32 << 20
 
 SYMBOLS = (
     "kla_b200_ckpt_bytes",
+    "kla_b200_segment_scratch_bytes",
     "kla_b200_ckpt_interval",
     "kla_b200_scan_fwd",
     "kla_b200_scan_fwd_static",
@@ -190,6 +191,8 @@ def load() -> ctypes.CDLL:
     lib = ctypes.CDLL(LIB_PATH)
     lib.kla_b200_ckpt_bytes.restype = c_size_t
     lib.kla_b200_ckpt_bytes.argtypes = [c_int64] * 4
+    lib.kla_b200_segment_scratch_bytes.restype = c_size_t
+    lib.kla_b200_segment_scratch_bytes.argtypes = [c_int64] * 3
     lib.kla_b200_ckpt_interval.restype = c_int64
     lib.kla_b200_scan_fwd.restype = c_int
     lib.kla_b200_scan_fwd.argtypes = [POINTER(FwdArgs), c_void_p]

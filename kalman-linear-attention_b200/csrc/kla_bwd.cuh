@@ -100,6 +100,7 @@ struct alignas(64) BwdParams {
     int lv_log_sigma;
     float obs_var_min, obs_var_max;
     WaitCtl wait;
+    SegCtl seg;  // hand: five planes [B, M, S]: the two carries and the running sums for da, da2, dp
 };
 
 template <typename T, typename TO, int SPT, int LPC, int CH, int NW, int NH, int TT>
@@ -161,9 +162,16 @@ __global__ void __launch_bounds__(kBwdThreads, 2) kla_bwd_kernel(const __grid_co
     constexpr bool pro = LOGV;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int b = blockIdx.y;
-    const int m_cta = blockIdx.x * MC;
-    const int L = prm.L, M = prm.M, S = prm.S, NT = prm.NT;
+    // This CTA's sequence and, when sequences are cut into segments, its stretch of it: t_off steps in, L steps long
+    // (tiles and steps below count from the start of the stretch; segments are processed last-first).
+    const SegUnit unit = seg_assign(prm.seg, true);
+    const int b = unit.b;
+    const int m_cta = unit.bx * MC;
+    const int M = prm.M, S = prm.S;
+    const int t_off = unit.seg * prm.seg.seg_len, tile_off = t_off / TT;
+    const int L = prm.seg.nseg > 1 ? min(prm.seg.seg_len, prm.L - t_off) : prm.L;
+    const int NT = (L + TT - 1) / TT;
+    const bool first_seg = unit.seg == 0, last_seg = unit.seg == prm.seg.nseg - 1;
     const bool has_dyv = prm.dyv.ptr != nullptr;
 
     if (tid == 0) {
@@ -216,7 +224,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) kla_bwd_kernel(const __grid_co
             // checkpoint of the tile about to be replayed, fetched one tile ahead
             float2 ck[CH][SPT];
             auto load_ck = [&](int tile) {
-                const float2 *src = prm.ckpt + (((long long)b * NT + tile) * M + (m_cta + cw)) * S + j;
+                const float2 *src = prm.ckpt + (((long long)b * prm.NT + tile_off + tile) * M + (m_cta + cw)) * S + j;
 #pragma unroll
                 for (int ci = 0; ci < CH; ++ci)
 #pragma unroll
@@ -346,8 +354,13 @@ __global__ void __launch_bounds__(kBwdThreads, 2) kla_bwd_kernel(const __grid_co
                 float2 *dpart = dpartbuf(bf);
 
                 if (ti == 0) {
-                    // The walk starts from the state after the last step; the carries are seeded from the gradient
-                    // of the returned state: lam_fin = 1/P, eta_fin = mean/P.
+                    // The walk starts from the state after the stretch's last step; at the end of the sequence the
+                    // carries are seeded from the gradient of the returned state: lam_fin = 1/P, eta_fin = mean/P,
+                    // at the end of an inner segment they and the running sums come from the segment after it.
+                    bool carried = true;
+                    if (!last_seg) carried = seg_wait(prm.wait, prm.seg.done + unit.seq, prm.seg.nseg - 1 - unit.seg, 19);
+                    if (!carried) break;
+                    const long long plane = (long long)prm.B * M * S;
 #pragma unroll
                     for (int ci = 0; ci < CH; ++ci) {
                         const int m = m_cta + cw + ci;
@@ -357,7 +370,16 @@ __global__ void __launch_bounds__(kBwdThreads, 2) kla_bwd_kernel(const __grid_co
                             const float2 fin = post[(ci * SPT + i) * ROW + ctid];
                             Pn[ci][i] = fin.x;
                             mn[ci][i] = fin.y;
-                            if (prm.dlam_fin != nullptr && m < M && st < S) {
+                            if (!last_seg) {
+                                if (m < M && st < S) {
+                                    const float *h = prm.seg.hand + ((long long)b * M + m) * S + st;
+                                    cP[ci][i] = __ldcg(h);
+                                    cm[ci][i] = __ldcg(h + plane);
+                                    accA[ci][i] = __ldcg(h + 2 * plane);
+                                    accA2[ci][i] = __ldcg(h + 3 * plane);
+                                    accP[ci][i] = __ldcg(h + 4 * plane);
+                                }
+                            } else if (prm.dlam_fin != nullptr && m < M && st < S) {
                                 const float Lb = prm.dlam_fin[((long long)b * M + m) * S + st];
                                 const float Eb = prm.deta_fin[((long long)b * M + m) * S + st];
                                 const float lam = 1.0f / fin.x;
@@ -470,14 +492,37 @@ __global__ void __launch_bounds__(kBwdThreads, 2) kla_bwd_kernel(const __grid_co
                 }
             }
 
-            // ---- end of sequence: gradients of a, p and of the carried-in state
+            if (!first_seg) {
+                // ---- start of an inner segment: hand the carries and the running sums to the segment before it
+                const long long plane = (long long)prm.B * M * S;
+#pragma unroll
+                for (int ci = 0; ci < CH; ++ci) {
+                    const int m = m_cta + cw + ci;
+#pragma unroll
+                    for (int i = 0; i < SPT; ++i) {
+                        const int st = i * LPC + j;
+                        if (m < M && st < S) {
+                            float *h = prm.seg.hand + ((long long)b * M + m) * S + st;
+                            __stcg(h, cP[ci][i]);
+                            __stcg(h + plane, cm[ci][i]);
+                            __stcg(h + 2 * plane, accA[ci][i]);
+                            __stcg(h + 3 * plane, accA2[ci][i]);
+                            __stcg(h + 4 * plane, accP[ci][i]);
+                        }
+                    }
+                }
+                __threadfence();
+                group_barrier_128();
+                if (tid == 0) st_release_gpu(prm.seg.done + unit.seq, prm.seg.nseg - unit.seg);
+            }
+            // ---- start of the sequence: gradients of a, p and of the carried-in state
 #pragma unroll
             for (int ci = 0; ci < CH; ++ci) {
                 const int m = m_cta + cw + ci;
 #pragma unroll
                 for (int i = 0; i < SPT; ++i) {
                     const int st = i * LPC + j;
-                    if (m < M && st < S) {
+                    if (first_seg && m < M && st < S) {
                         const long long ms = (long long)m * S + st, bms = ((long long)b * M + m) * S + st;
                         const float a = ca[ci][i];
                         const float da2_da = (a * a >= kEps) ? 2.0f * a : 0.0f;  // clamp_min subgradient
@@ -507,12 +552,12 @@ __global__ void __launch_bounds__(kBwdThreads, 2) kla_bwd_kernel(const __grid_co
 
         if (htid < kProducers) {
             // ---- loader: TMA tiles of v, lambda_v, dy, dy_var and (k, q), NS tiles ahead
-            const T *vb = static_cast<const T *>(prm.v.ptr) + (long long)b * prm.v.sb;
-            const T *lb = static_cast<const T *>(prm.lv.ptr) + (long long)b * prm.lv.sb;
-            const T *kb = static_cast<const T *>(prm.k.ptr) + (long long)b * prm.k.sb;
-            const T *qb = static_cast<const T *>(prm.q.ptr) + (long long)b * prm.q.sb;
-            const TO *dyb = static_cast<const TO *>(prm.dy.ptr) + (long long)b * prm.dy.sb;
-            const TO *dyvb = has_dyv ? static_cast<const TO *>(prm.dyv.ptr) + (long long)b * prm.dyv.sb : nullptr;
+            const T *vb = static_cast<const T *>(prm.v.ptr) + (long long)b * prm.v.sb + (long long)t_off * prm.v.st;
+            const T *lb = static_cast<const T *>(prm.lv.ptr) + (long long)b * prm.lv.sb + (long long)t_off * prm.lv.st;
+            const T *kb = static_cast<const T *>(prm.k.ptr) + (long long)b * prm.k.sb + (long long)t_off * prm.k.st;
+            const T *qb = static_cast<const T *>(prm.q.ptr) + (long long)b * prm.q.sb + (long long)t_off * prm.q.st;
+            const TO *dyb = static_cast<const TO *>(prm.dy.ptr) + (long long)b * prm.dy.sb + (long long)t_off * prm.dy.st;
+            const TO *dyvb = has_dyv ? static_cast<const TO *>(prm.dyv.ptr) + (long long)b * prm.dyv.sb + (long long)t_off * prm.dyv.st : nullptr;
             if (!has_dyv) {  // dyvar absent: its stage buffers stay zero for the whole kernel
                 for (int s = 0; s < NS; ++s)
                     for (int idx = htid; idx < TT * MC; idx += kProducers) dyvstage(s)[idx] = from_f32<TO>(0.0f);
@@ -538,10 +583,10 @@ __global__ void __launch_bounds__(kBwdThreads, 2) kla_bwd_kernel(const __grid_co
                 if (prm.use_tma) {
                     if (htid == 0) {
                         mbar_arrive_expect_tx(&full_in[s], 2 * kBytesI + (has_dyv ? 2 : 1) * kBytesO);
-                        tma_load_3d(vstage(s), &prm.tm_v, m_cta, t0, b, &full_in[s]);
-                        tma_load_3d(lstage(s), &prm.tm_lv, m_cta, t0, b, &full_in[s]);
-                        tma_load_3d(dystage(s), &prm.tm_dy, m_cta, t0, b, &full_in[s]);
-                        if (has_dyv) tma_load_3d(dyvstage(s), &prm.tm_dyv, m_cta, t0, b, &full_in[s]);
+                        tma_load_3d(vstage(s), &prm.tm_v, m_cta, t_off + t0, b, &full_in[s]);
+                        tma_load_3d(lstage(s), &prm.tm_lv, m_cta, t_off + t0, b, &full_in[s]);
+                        tma_load_3d(dystage(s), &prm.tm_dy, m_cta, t_off + t0, b, &full_in[s]);
+                        if (has_dyv) tma_load_3d(dyvstage(s), &prm.tm_dyv, m_cta, t_off + t0, b, &full_in[s]);
                     }
                 } else {
                     stage_tile_plain<T, TT, MC, kProducers>(vstage(s), vb, prm.v.st, t0, L, m_cta, M, htid);
@@ -564,8 +609,8 @@ __global__ void __launch_bounds__(kBwdThreads, 2) kla_bwd_kernel(const __grid_co
         } else {
             // ---- summing helpers: finish the sums of each processed tile
             const int ctid = htid - kProducers;
-            T *dvb = static_cast<T *>(prm.dv.ptr) + (long long)b * prm.dv.sb;
-            T *dlvb = static_cast<T *>(prm.dlv.ptr) + (long long)b * prm.dlv.sb;
+            T *dvb = static_cast<T *>(prm.dv.ptr) + (long long)b * prm.dv.sb + (long long)t_off * prm.dv.st;
+            T *dlvb = static_cast<T *>(prm.dlv.ptr) + (long long)b * prm.dlv.sb + (long long)t_off * prm.dlv.st;
             for (int jt = 0; jt < NT; ++jt) {
                 const int tile = NT - 1 - jt, s = jt % NS, t0 = tile * TT, bf = jt & 1;
                 const int n = min(TT, L - t0);
@@ -589,8 +634,8 @@ __global__ void __launch_bounds__(kBwdThreads, 2) kla_bwd_kernel(const __grid_co
                         sk1 += x1.x; sq1 += x1.y;
                     }
                     if (st < S && u < n) {
-                        atomicAdd(prm.dk + ((long long)b * L + t0 + u) * S + st, sk0 + sk1);
-                        atomicAdd(prm.dq + ((long long)b * L + t0 + u) * S + st, sq0 + sq1);
+                        atomicAdd(prm.dk + ((long long)b * prm.L + t_off + t0 + u) * S + st, sk0 + sk1);
+                        atomicAdd(prm.dq + ((long long)b * prm.L + t_off + t0 + u) * S + st, sq0 + sq1);
                     }
                 }
                 // dv, dlambda_v: add the lane groups. v enters only through v*lambda_v (kla_ops.py:177): with

@@ -141,10 +141,104 @@ int wait_ctl(WaitCtl *w) {
     return KLA_B200_OK;
 }
 
+// ---- sequences cut into segments (SegCtl, kla_common.cuh): the scratch behind the checkpoints and the plan
+//   [forward: ticket (256 B) | done, one int per (b, m)] [backward: the same] [forward hand-over: float2 per lane]
+//   [backward hand-over: 5 floats per lane]
+constexpr size_t kSegAlign = 256;
+size_t seg_round(size_t n) { return (n + kSegAlign - 1) / kSegAlign * kSegAlign; }
+struct SegScratch {
+    size_t flags;   // bytes of one direction's ticket + done block
+    size_t hand_f;  // offset of the forward's hand-over records
+    size_t hand_b;  // offset of the backward's
+    size_t total;
+};
+// false when the sizes do not fit size_t
+bool seg_scratch(int64_t B, int64_t M, int64_t S, SegScratch *out) {
+    if (B <= 0 || M <= 0 || S <= 0) { *out = SegScratch{0, 0, 0, 0}; return true; }
+    const size_t bm = (size_t)B * (size_t)M;  // B <= 65535 and M <= 2^30 (check_common)
+    if (bm > SIZE_MAX / ((size_t)S * 64)) return false;
+    const size_t lanes = bm * (size_t)S;
+    out->flags = kSegAlign + seg_round(bm * sizeof(int));
+    out->hand_f = 2 * out->flags;
+    out->hand_b = out->hand_f + seg_round(lanes * sizeof(float2));
+    out->total = out->hand_b + seg_round(lanes * 5 * sizeof(float));
+    return true;
+}
+size_t ckpt_part_bytes(int64_t B, int64_t L, int64_t M, int64_t S) {
+    const int64_t nt = (L + kCkptInterval - 1) / kCkptInterval;
+    // saturating product: a size that does not fit size_t reads as SIZE_MAX, never as a small number
+    size_t n = sizeof(float2);
+    for (const int64_t f : {B, nt, M, S}) {
+        if (n > SIZE_MAX / (size_t)f) return SIZE_MAX;
+        n *= (size_t)f;
+    }
+    return n > SIZE_MAX - kSegAlign ? SIZE_MAX : seg_round(n);
+}
+
+// How many segments for `ctas` sequences of L steps (and their length). Segments pay when the sequences do not
+// fill the SMs' CTA slots evenly. Measured on B200 at T=4096, M=1024, S=16 (ms without -> with): backward, two
+// CTAs per SM: B=8 1.50 -> 1.42, B=10 2.35 -> 1.68, B=12 2.35 -> 1.96, B=14 2.97 -> 2.32, B=16 2.96 -> 2.60;
+// forward, four per SM: B=10 0.62 -> 0.59, B=14 0.81 -> 0.65, B=16 0.81 -> 0.71, but B=8 0.44 -> 0.55: with
+// fewer sequences than half its slots the waiting CTAs spread the running ones unevenly over the SMs. So: the
+// backward whenever there are more sequences than SMs (16 segments up to two per SM, else 8), the forward from
+// two sequences per SM on. KLA_B200_SEGMENTS=0 switches segments off, =N asks for N in both kernels.
+int plan_segments(int64_t ctas, int64_t L, bool backward, int *seg_len) {
+    const char *env = getenv("KLA_B200_SEGMENTS");  // read per launch: the tests switch it within one process
+    const int forced = env != nullptr ? atoi(env) : -1;
+    *seg_len = (int)L;
+    if (forced == 0 || forced == 1) return 1;
+    int want = 8;
+    int64_t min_len = 128;
+    if (forced > 1) {
+        want = forced;
+        min_len = kTT;
+    } else {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            return 1;
+        if (ctas <= (backward ? sms : 2 * sms)) return 1;
+        if (backward && ctas <= 2 * sms) want = 16;
+    }
+    int64_t len = (L + want - 1) / want;
+    len = (len + kTT - 1) / kTT * kTT;  // whole tiles of both kernels (and whole checkpoint intervals)
+    if (len < min_len) len = min_len;
+    const int64_t n = (L + len - 1) / len;
+    if (n < 2 || n > 65535) return 1;
+    *seg_len = (int)len;
+    return (int)n;
+}
+
+// Fill prm.seg for one direction and clear its ticket and done words. scratch: the bytes behind the checkpoints.
+template <typename Params>
+int seg_setup(Params &prm, void *ckpt, int64_t B, int64_t L, int64_t M, int64_t S, int lpc, bool backward, cudaStream_t st) {
+    prm.seg = SegCtl{1, (int)L, nullptr, nullptr, nullptr};
+    if (ckpt == nullptr || L <= 0) return KLA_B200_OK;
+    const int mc = scan_channels_per_cta(lpc);
+    const int64_t ctas = ((M + mc - 1) / mc) * B;
+    int seg_len = (int)L;
+    const int nseg = plan_segments(ctas, L, backward, &seg_len);
+    if (nseg <= 1) return KLA_B200_OK;
+    SegScratch sc;
+    if (!seg_scratch(B, M, S, &sc)) return KLA_B200_OK;
+    const size_t base = ckpt_part_bytes(B, L, M, S);
+    if (base == SIZE_MAX) return KLA_B200_OK;
+    unsigned char *p = static_cast<unsigned char *>(ckpt) + base;
+    unsigned char *flags = p + (backward ? sc.flags : 0);
+    const cudaError_t e = cudaMemsetAsync(flags, 0, sc.flags, st);
+    if (e != cudaSuccess) return cuda_fail(e);
+    prm.seg.nseg = nseg;
+    prm.seg.seg_len = seg_len;
+    prm.seg.ticket = reinterpret_cast<int *>(flags);
+    prm.seg.done = reinterpret_cast<int *>(flags + kSegAlign);
+    prm.seg.hand = reinterpret_cast<float *>(p + (backward ? sc.hand_b : sc.hand_f));
+    return KLA_B200_OK;
+}
+
 // Tensor maps of the forward's tiles (box: the CTA's channels x one tile of steps), then the launch.
 template <typename T, typename TO, int LPC, bool PRIOR>
 int prep_fwd(FwdParams &prm, const kla_b200_fwd_args &a, cudaStream_t st) {
     const int mc = scan_channels_per_cta(LPC);
+    if (int rc = seg_setup(prm, a.ckpt, a.B, a.L, a.M, a.S, LPC, false, st)) return rc;
     prm.use_tma = !g_no_tma && make_tile_map<T>(&prm.tm_v, a.v, a.B, a.L, a.M, mc, kTT) &&
                   make_tile_map<T>(&prm.tm_lv, a.lambda_v, a.B, a.L, a.M, mc, kTT);
     if (prm.epilogue)  // z and gate tiles travel like v and lambda_v when they meet the tensor-map rules
@@ -158,6 +252,7 @@ int prep_fwd(FwdParams &prm, const kla_b200_fwd_args &a, cudaStream_t st) {
 template <typename T, typename TO, int LPC, bool PRIOR>
 int prep_bwd(BwdParams &prm, const kla_b200_bwd_args &a, cudaStream_t st) {
     const int mc = scan_channels_per_cta(LPC);
+    if (int rc = seg_setup(prm, const_cast<void *>(a.ckpt), a.B, a.L, a.M, a.S, LPC, true, st)) return rc;
     prm.use_tma = !g_no_tma && make_tile_map<T>(&prm.tm_v, a.v, a.B, a.L, a.M, mc, kBwdTT) &&
                   make_tile_map<T>(&prm.tm_lv, a.lambda_v, a.B, a.L, a.M, mc, kBwdTT) &&
                   make_tile_map<TO>(&prm.tm_dy, a.dy, a.B, a.L, a.M, mc, kBwdTT) &&
@@ -298,14 +393,17 @@ int64_t kla_b200_ckpt_interval(void) { return kCkptInterval; }
 
 size_t kla_b200_ckpt_bytes(int64_t B, int64_t L, int64_t M, int64_t S) {
     if (B <= 0 || L <= 0 || M <= 0 || S <= 0) return 0;
-    const int64_t nt = (L + kCkptInterval - 1) / kCkptInterval;
-    // saturating product: a size that does not fit size_t reads as SIZE_MAX, never as a small number
-    size_t n = sizeof(float2);
-    for (const int64_t f : {B, nt, M, S}) {
-        if (n > SIZE_MAX / (size_t)f) return SIZE_MAX;
-        n *= (size_t)f;
-    }
-    return n;
+    if (B > 65535 || M > (1 << 30)) return SIZE_MAX;
+    const size_t ck = ckpt_part_bytes(B, L, M, S);
+    SegScratch sc;
+    if (ck == SIZE_MAX || !seg_scratch(B, M, S, &sc) || ck > SIZE_MAX - sc.total) return SIZE_MAX;
+    return ck + sc.total;
+}
+
+size_t kla_b200_segment_scratch_bytes(int64_t B, int64_t M, int64_t S) {
+    SegScratch sc;
+    if (B > 65535 || M > (1 << 30) || !seg_scratch(B, M, S, &sc)) return SIZE_MAX;
+    return sc.total;
 }
 
 int kla_b200_scan_fwd(const kla_b200_fwd_args *a, void *stream) {

@@ -53,6 +53,71 @@ struct WaitCtl {
                         // for it runs out; -1 in normal operation
 };
 
+// Sequences cut into segments. A CTA of the scan kernels owns one (batch element, channel block) sequence
+// for its whole length, and a grid rarely divides evenly over the SMs' CTA slots: at 256 sequences 40 of
+// the 148 SMs hold one CTA instead of two and finish early; at 768 the last of three rounds is half empty. With
+// nseg > 1 the grid has nseg CTAs per sequence. A CTA draws a ticket when it starts; tickets map to
+// (segment, sequence) with the segment that must run first in the slowest position, so the CTA that owns the
+// preceding segment of the same sequence always drew its ticket earlier, i.e. is running or done. The CTA
+// brings its inputs in, waits (bounded) until `done[sequence]` says the preceding segment is finished, takes
+// the carried state from `hand`, and leaves its own there. SMs that finish their CTAs early simply draw more
+// tickets, which evens the load out. The arithmetic and its order are those of the unsegmented kernel.
+struct SegCtl {
+    int nseg;     // segments per sequence; 1 = off (nothing below is touched)
+    int seg_len;  // steps per segment, a multiple of the kernels' tile lengths
+    int *ticket;  // one counter, zero before the launch
+    int *done;    // [sequences] segments finished so far, zero before the launch
+    float *hand;  // carried state between segments, planes of [B, M, S] floats
+};
+
+// What a CTA works on: its channel block, batch element and segment.
+struct SegUnit {
+    int bx, b, seg, seq;
+};
+
+// Called by every thread of the CTA (contains a CTA-wide barrier). reverse: segments run last-first.
+__device__ __forceinline__ SegUnit seg_assign(const SegCtl &sc, bool reverse) {
+    SegUnit u{(int)blockIdx.x, (int)blockIdx.y, 0, (int)(blockIdx.y * gridDim.x + blockIdx.x)};
+    if (sc.nseg > 1) {
+        __shared__ int ticket;
+        if (threadIdx.x == 0) ticket = atomicAdd(sc.ticket, 1);
+        __syncthreads();
+        const int nseq = gridDim.x * gridDim.y;
+        const int order = ticket / nseq;
+        u.seq = ticket % nseq;
+        u.bx = u.seq % gridDim.x;
+        u.b = u.seq / gridDim.x;
+        u.seg = reverse ? sc.nseg - 1 - order : order;
+    }
+    return u;
+}
+
+__device__ __forceinline__ int ld_acquire_gpu(const int *p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(int *p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Wait until `need` segments of the sequence are finished; every calling thread polls (and thereby acquires what
+// the finishing CTA released). Gives up like mbar_wait: status word, false.
+__device__ __forceinline__ bool seg_wait(const WaitCtl &w, const int *done, int need, int site) {
+    const unsigned limit = w.limit_ns / 256u + 1u;
+    for (unsigned it = 0;; ++it) {
+        if (ld_acquire_gpu(done) >= need) return true;
+        if (it >= limit) {
+            atomicCAS(w.status, 0, kStatusWait | site);
+            return false;
+        }
+        __nanosleep(200);
+    }
+}
+
+// The 128 threads of a compute group meet here (hardware barrier 1; barrier 0 is __syncthreads).
+__device__ __forceinline__ void group_barrier_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 struct Tensor3 {
     void *ptr;
     long long sb, st;  // batch and time strides, in elements

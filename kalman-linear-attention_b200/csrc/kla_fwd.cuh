@@ -61,6 +61,7 @@ struct alignas(64) FwdParams {
     Tensor3 y_raw, yv_raw;
     int skip_len, gate_act, epilogue, epi_tma;
     WaitCtl wait;
+    SegCtl seg;  // hand: one plane pair (P, mean) as float2 [B, M, S]
     alignas(64) CUtensorMap tm_z, tm_gate;  // maps of the epilogue operands, like tm_v; valid when epi_tma
 };
 
@@ -126,9 +127,16 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
     auto ystage = [&](int o) { return reinterpret_cast<float2 *>(out_base + o * Sm::kOut); };
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int b = blockIdx.y;
-    const int m_cta = blockIdx.x * MC;
-    const int L = prm.L, M = prm.M, S = prm.S, NT = prm.NT;
+    // This CTA's sequence and, when sequences are cut into segments, its stretch of it: t_off steps in, L steps long
+    // (everything below counts tiles and steps from the start of the stretch).
+    const SegUnit unit = seg_assign(prm.seg, false);
+    const int b = unit.b;
+    const int m_cta = unit.bx * MC;
+    const int M = prm.M, S = prm.S;
+    const int t_off = unit.seg * prm.seg.seg_len;
+    const int L = prm.seg.nseg > 1 ? min(prm.seg.seg_len, prm.L - t_off) : prm.L;
+    const int NT = (L + TT - 1) / TT;
+    const bool first_seg = unit.seg == 0, last_seg = unit.seg == prm.seg.nseg - 1;
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
@@ -181,9 +189,28 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                 pair_el(mean[ci], i) = eta * P0;
             }
         }
+        bool carried = true;
+        if (!first_seg) {
+            // the state the preceding segment ended in, as it left that CTA's registers
+            carried = seg_wait(prm.wait, prm.seg.done + unit.seq, unit.seg, 9);
+            const float2 *hand = reinterpret_cast<const float2 *>(prm.seg.hand);
+#pragma unroll
+            for (int ci = 0; ci < CH; ++ci) {
+                const int m = m_cta + cw + ci;
+#pragma unroll
+                for (int i = 0; i < SPT; ++i) {
+                    const int s = i * LPC + j;
+                    if (carried && m < M && s < S) {
+                        const float2 h = __ldcg(hand + ((long long)b * M + m) * S + s);
+                        pair_el(P[ci], i) = h.x;
+                        pair_el(mean[ci], i) = h.y;
+                    }
+                }
+            }
+        }
         // checkpoint pointer of chain (ci = 0, i = 0); advanced by one tile per tile
         float2 *ck = prm.ckpt;
-        if (ck != nullptr) ck += ((long long)b * prm.NC * M + (m_cta + cw)) * S + j;
+        if (ck != nullptr) ck += (((long long)b * prm.NC + t_off / kCkptInterval) * M + (m_cta + cw)) * S + j;
         const long long ck_tile = (long long)M * S;
         auto store_ckpt = [&]() {  // the state before the step about to be taken; advances to the next checkpoint
 #pragma unroll
@@ -290,7 +317,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             }
         };
 
-        for (int tile = 0; tile < NT; ++tile) {
+        for (int tile = 0; tile < (carried ? NT : 0); ++tile) {
             const int s = tile % NS, o = tile % NO;
             const int t0 = tile * TT;
             if (!mbar_wait(prm.wait, &full_in[s], (tile / NS) & 1, 1)) break;
@@ -347,7 +374,9 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             }
         }
 
-        // final state back in information form: lambda = 1/P, eta = mean * lambda
+        // final state back in information form: lambda = 1/P, eta = mean * lambda; between segments the state is
+        // handed on as it is
+        float2 *hand = reinterpret_cast<float2 *>(prm.seg.hand);
 #pragma unroll
         for (int ci = 0; ci < CH; ++ci) {
             const int m = m_cta + cw + ci;
@@ -355,11 +384,20 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
             for (int i = 0; i < SPT; ++i) {
                 const int s = i * LPC + j;
                 if (m < M && s < S) {
-                    const float lam = 1.0f / pair_el(P[ci], i);
-                    prm.lam_fin[((long long)b * M + m) * S + s] = lam;
-                    prm.eta_fin[((long long)b * M + m) * S + s] = pair_el(mean[ci], i) * lam;
+                    if (last_seg) {
+                        const float lam = 1.0f / pair_el(P[ci], i);
+                        prm.lam_fin[((long long)b * M + m) * S + s] = lam;
+                        prm.eta_fin[((long long)b * M + m) * S + s] = pair_el(mean[ci], i) * lam;
+                    } else {
+                        __stcg(hand + ((long long)b * M + m) * S + s, make_float2(pair_el(P[ci], i), pair_el(mean[ci], i)));
+                    }
                 }
             }
+        }
+        if (!last_seg) {
+            __threadfence();
+            group_barrier_128();
+            if (tid == 0) st_release_gpu(prm.seg.done + unit.seq, unit.seg + 1);
         }
     } else {
         // ================================================================ helpers
@@ -370,10 +408,10 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         bool ok = true;
         if (htid < kProducers) {
             // ---- loaders: TMA tiles of v, lambda_v and the (k, q) pairs, NS tiles ahead
-            const T *vb = static_cast<const T *>(prm.v.ptr) + (long long)b * prm.v.sb;
-            const T *lb = static_cast<const T *>(prm.lv.ptr) + (long long)b * prm.lv.sb;
-            const T *kb = static_cast<const T *>(prm.k.ptr) + (long long)b * prm.k.sb;
-            const T *qb = static_cast<const T *>(prm.q.ptr) + (long long)b * prm.q.sb;
+            const T *vb = static_cast<const T *>(prm.v.ptr) + (long long)b * prm.v.sb + (long long)t_off * prm.v.st;
+            const T *lb = static_cast<const T *>(prm.lv.ptr) + (long long)b * prm.lv.sb + (long long)t_off * prm.lv.st;
+            const T *kb = static_cast<const T *>(prm.k.ptr) + (long long)b * prm.k.sb + (long long)t_off * prm.k.st;
+            const T *qb = static_cast<const T *>(prm.q.ptr) + (long long)b * prm.q.sb + (long long)t_off * prm.q.st;
             // (k, q) of the next tile are fetched into registers while the current one
             // is handed over, so the loader never sits on a global-memory latency
             constexpr int KQP = (TT * SPAD + kProducers - 1) / kProducers;
@@ -394,8 +432,8 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                 if (prm.use_tma) {
                     if (htid == 0) {
                         mbar_arrive_expect_tx(&full_in[s], 2 * kTileBytes);
-                        tma_load_3d(vstage(s), &prm.tm_v, m_cta, t0, b, &full_in[s]);
-                        tma_load_3d(lstage(s), &prm.tm_lv, m_cta, t0, b, &full_in[s]);
+                        tma_load_3d(vstage(s), &prm.tm_v, m_cta, t_off + t0, b, &full_in[s]);
+                        tma_load_3d(lstage(s), &prm.tm_lv, m_cta, t_off + t0, b, &full_in[s]);
                     }
                 } else {
                     stage_tile_plain<T, TT, MC, kProducers>(vstage(s), vb, prm.v.st, t0, L, m_cta, M, htid);
@@ -422,16 +460,16 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                     if (prm.epi_tma) {
                         if (htid == 0) {
                             mbar_arrive_expect_tx(&epi_full[e], ((has_z ? 1 : 0) + (has_g ? 1 : 0)) * kTileBytes);
-                            if (has_z) tma_load_3d(zstage(e), &prm.tm_z, m_cta, t0, b, &epi_full[e]);
-                            if (has_g) tma_load_3d(gstage(e), &prm.tm_gate, m_cta, t0, b, &epi_full[e]);
+                            if (has_z) tma_load_3d(zstage(e), &prm.tm_z, m_cta, t_off + t0, b, &epi_full[e]);
+                            if (has_g) tma_load_3d(gstage(e), &prm.tm_gate, m_cta, t_off + t0, b, &epi_full[e]);
                         }
                     } else {
                         if (has_z)
                             stage_tile_plain<T, TT, MC, kProducers>(
-                                zstage(e), static_cast<const T *>(prm.z.ptr) + (long long)b * prm.z.sb, prm.z.st, t0, L, m_cta, M, htid);
+                                zstage(e), static_cast<const T *>(prm.z.ptr) + (long long)b * prm.z.sb + (long long)t_off * prm.z.st, prm.z.st, t0, L, m_cta, M, htid);
                         if (has_g)
                             stage_tile_plain<T, TT, MC, kProducers>(
-                                gstage(e), static_cast<const T *>(prm.gate.ptr) + (long long)b * prm.gate.sb, prm.gate.st, t0, L, m_cta, M, htid);
+                                gstage(e), static_cast<const T *>(prm.gate.ptr) + (long long)b * prm.gate.sb + (long long)t_off * prm.gate.st, prm.gate.st, t0, L, m_cta, M, htid);
                     }
                     if (!(prm.epi_tma && htid == 0)) mbar_arrive(&epi_full[e]);
                     epi_issued = it + 1;
@@ -440,8 +478,8 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
         } else {
             // ---- drainers: per finished tile, sum the LPC partial read-outs and store y, y_var
             const int dtid = htid - kProducers;
-            TO *yb = static_cast<TO *>(prm.y.ptr) + (long long)b * prm.y.sb;
-            TO *yvb = static_cast<TO *>(prm.yv.ptr) + (long long)b * prm.yv.sb;
+            TO *yb = static_cast<TO *>(prm.y.ptr) + (long long)b * prm.y.sb + (long long)t_off * prm.y.st;
+            TO *yvb = static_cast<TO *>(prm.yv.ptr) + (long long)b * prm.yv.sb + (long long)t_off * prm.yv.st;
             float skip0 = 0.0f, skip1 = 0.0f;
             if constexpr (EPI) {
                 static_assert(kDrainers % (MC / 2) == 0, "a drainer thread keeps its channel pair from tile to tile");
@@ -458,8 +496,8 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
                     const int e = jt % NE;
                     if (!mbar_wait(prm.wait, &epi_full[e], (jt / NE) & 1, 7, 100)) { ok = false; break; }
                     const T *zs = prm.z.ptr ? zstage(e) : nullptr, *gs = prm.gate.ptr ? gstage(e) : nullptr;
-                    TO *yr = prm.y_raw.ptr ? static_cast<TO *>(prm.y_raw.ptr) + (long long)b * prm.y_raw.sb + (long long)t0 * prm.y_raw.st : nullptr;
-                    TO *yvr = prm.y_raw.ptr ? static_cast<TO *>(prm.yv_raw.ptr) + (long long)b * prm.yv_raw.sb + (long long)t0 * prm.yv_raw.st : nullptr;
+                    TO *yr = prm.y_raw.ptr ? static_cast<TO *>(prm.y_raw.ptr) + (long long)b * prm.y_raw.sb + (long long)(t_off + t0) * prm.y_raw.st : nullptr;
+                    TO *yvr = prm.y_raw.ptr ? static_cast<TO *>(prm.yv_raw.ptr) + (long long)b * prm.yv_raw.sb + (long long)(t_off + t0) * prm.yv_raw.st : nullptr;
                     output_pass<TO, LPC, MC, MCP, TT, kDrainers>(
                         ystage(o), yb + (long long)t0 * prm.y.st, prm.y.st, prm.vec_y,
                         yvb + (long long)t0 * prm.yv.st, prm.yv.st, prm.vec_yv, min(TT, L - t0), m_cta, M, dtid,

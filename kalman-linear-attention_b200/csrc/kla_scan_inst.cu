@@ -17,7 +17,7 @@ cudaError_t launch_fwd(const FwdParams &prm, cudaStream_t st) {
     const size_t smem = prm.epilogue ? Sm::kTotal : Sm::kPlain;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sm::kTotal);
     if (e != cudaSuccess) return e;
-    dim3 grid((unsigned)((prm.M + Sh::kMC - 1) / Sh::kMC), (unsigned)prm.B);
+    dim3 grid((unsigned)((prm.M + Sh::kMC - 1) / Sh::kMC), (unsigned)prm.B, (unsigned)prm.seg.nseg);
     kern<<<grid, Sh::kThreads, smem, st>>>(prm);
     return cudaGetLastError();
 }
@@ -42,7 +42,7 @@ cudaError_t launch_bwd(const BwdParams &prm, cudaStream_t st) {
     if (!ok) return cudaErrorLaunchOutOfResources;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sm::kTotal);
     if (e != cudaSuccess) return e;
-    dim3 grid((unsigned)((prm.M + Sh::kMC - 1) / Sh::kMC), (unsigned)prm.B);
+    dim3 grid((unsigned)((prm.M + Sh::kMC - 1) / Sh::kMC), (unsigned)prm.B, (unsigned)prm.seg.nseg);
     kern<<<grid, kBwdThreads, Sm::kTotal, st>>>(prm);
     return cudaGetLastError();
 }

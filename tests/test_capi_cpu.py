@@ -41,8 +41,11 @@ def test_version_and_checkpoint_size(L):
     iv = lib.kla_b200_ckpt_interval()
     assert iv == 8
     # one (P, mean) float2 per lane per started interval
-    assert lib.kla_b200_ckpt_bytes(8, 4096, 1024, 16) == 8 * (4096 // iv) * 1024 * 16 * 8
-    assert lib.kla_b200_ckpt_bytes(2, 17, 3, 5) == 2 * 3 * 3 * 5 * 8
+    up = lambda n: (n + 255) // 256 * 256
+    seg = lambda B, M, S: 2 * (256 + up(4 * B * M)) + up(8 * B * M * S) + up(20 * B * M * S)
+    assert lib.kla_b200_segment_scratch_bytes(8, 1024, 16) == seg(8, 1024, 16)
+    assert lib.kla_b200_ckpt_bytes(8, 4096, 1024, 16) == up(8 * (4096 // iv) * 1024 * 16 * 8) + seg(8, 1024, 16)
+    assert lib.kla_b200_ckpt_bytes(2, 17, 3, 5) == up(2 * 3 * 3 * 5 * 8) + seg(2, 3, 5)
     assert lib.kla_b200_ckpt_bytes(0, 17, 3, 5) == 0
 
 

@@ -534,3 +534,51 @@ def test_training_epilogue_matches_torch_autograd(kb, mode):
         assert g_.shape == w_.shape and g_.dtype == w_.dtype, n
         err = ((g_.float() - w_.float()).abs().max() / (w_.float().abs().max() + 1.0)).item()
         assert err < (2e-2 if mode == "bf16" else 2e-5), f"d{n}: {err:.2e}"
+
+
+# ------------------------------------------------------------ sequences cut into segments
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,L,M,S,segs,prior,state,dtype", [
+    (2, 100, 40, 16, 4, False, False, torch.float32),    # ragged last segment, channels not a multiple of the CTA's
+    (1, 257, 33, 5, 3, True, True, torch.float32),       # prior read-out, carried state and its gradients
+    (3, 64, 64, 16, 4, False, True, torch.float32),      # segments of one forward tile
+    (2, 130, 64, 16, 5, False, False, torch.bfloat16),
+    (10, 1024, 1024, 16, None, False, False, torch.float32),  # what the library picks by itself: 320 sequences
+])
+def test_segmented_kernels_equal_the_unsegmented_ones(kb, monkeypatch, B, L, M, S, segs, prior, state, dtype):
+    """With KLA_B200_SEGMENTS=N every sequence is processed as N segments by different CTAs that hand the filter
+    state (forward) or the carries and running sums (backward) to one another. The arithmetic and its order are
+    unchanged: everything that does not go through atomics must be bit-identical to the unsegmented kernels."""
+    F = torch.nn.functional
+    g = torch.Generator().manual_seed(L + M)
+    v = torch.randn(B, L, M, generator=g).cuda().to(dtype)
+    lv = (1 / F.softplus(torch.randn(B, L, M, generator=g))).cuda().to(dtype)
+    k = F.normalize(torch.randn(B, L, S, generator=g), dim=-1).cuda().to(dtype)
+    q = F.normalize(torch.randn(B, L, S, generator=g), dim=-1).cuda().to(dtype)
+    a, p = torch.sigmoid(torch.randn(M, S, generator=g)).cuda(), F.softplus(torch.randn(M, S, generator=g)).cuda()
+    dy, dyv = torch.randn(B, L, M, generator=g).cuda(), torch.randn(B, L, M, generator=g).cuda()
+    gl, ge = torch.randn(B, M, S, generator=g).cuda(), torch.randn(B, M, S, generator=g).cuda()
+    st = (torch.rand(B, M, S, generator=g).cuda() + 0.5, torch.randn(B, M, S, generator=g).cuda()) if state else None
+
+    def run(setting):
+        if setting is None:
+            monkeypatch.delenv("KLA_B200_SEGMENTS", raising=False)
+        else:
+            monkeypatch.setenv("KLA_B200_SEGMENTS", str(setting))
+        ins = [t.clone().requires_grad_(True) for t in (v, lv, k, q, a, p)]
+        sti = None if st is None else tuple(t.clone().requires_grad_(True) for t in st)
+        y, yv, fin = kb.kla_scan_b200(*ins, initial_state=sti, decode_from_prior=prior, time_chunks=1)
+        grads = torch.autograd.grad([y, yv, fin.lam, fin.eta], ins + (list(sti) if sti else []),
+                                    [dy.to(y.dtype), dyv.to(y.dtype), gl, ge])
+        torch.cuda.synchronize()
+        return [t.detach() for t in (y, yv, fin.lam, fin.eta, *grads)]
+
+    plain, cut = run(0), run(segs)
+    __import__("importlib").import_module("kalman-linear-attention_b200._lib").check_status()
+    names = ["y", "y_var", "lam", "eta", "dv", "dlambda_v", "dk", "dq", "da", "dp", "dlam0", "deta0"]
+    for n, x, r in zip(names, cut, plain):
+        if n in ("dk", "dq", "da", "dp"):  # sums by atomics: the order of the additions is not fixed in either form
+            assert ((x.float() - r.float()).abs().max() / (r.float().abs().max() + 1e-30)).item() < 1e-5, n
+        else:
+            assert torch.equal(x, r), n
