@@ -165,6 +165,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) kla_bwd_kernel(const __grid_co
     // This CTA's sequence and, when sequences are cut into segments, its stretch of it: t_off steps in, L steps long
     // (tiles and steps below count from the start of the stretch; segments are processed last-first).
     const SegUnit unit = seg_assign(prm.seg, true);
+    if (unit.seg < 0) return;
     const int b = unit.b;
     const int m_cta = unit.bx * MC;
     const int M = prm.M, S = prm.S;

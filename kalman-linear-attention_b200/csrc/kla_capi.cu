@@ -188,7 +188,7 @@ int plan_segments(int64_t ctas, int64_t L, bool backward, int *seg_len) {
     *seg_len = (int)L;
     if (forced == 0 || forced == 1) return 1;
     int want = 8;
-    int64_t min_len = 128;
+    int64_t min_len = 256;  // shorter segments cost more in hand-overs than they even out (chunks of 256 steps: no gain)
     if (forced > 1) {
         want = forced;
         min_len = kTT;

@@ -84,6 +84,10 @@ __device__ __forceinline__ SegUnit seg_assign(const SegCtl &sc, bool reverse) {
         __syncthreads();
         const int nseq = gridDim.x * gridDim.y;
         const int order = ticket / nseq;
+        if (ticket < 0 || order >= sc.nseg) {  // a counter that was not zero before the launch: touch nothing
+            u.seg = -1;
+            return u;
+        }
         u.seq = ticket % nseq;
         u.bx = u.seq % gridDim.x;
         u.b = u.seq / gridDim.x;

@@ -130,6 +130,7 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
     // This CTA's sequence and, when sequences are cut into segments, its stretch of it: t_off steps in, L steps long
     // (everything below counts tiles and steps from the start of the stretch).
     const SegUnit unit = seg_assign(prm.seg, false);
+    if (unit.seg < 0) return;
     const int b = unit.b;
     const int m_cta = unit.bx * MC;
     const int M = prm.M, S = prm.S;
