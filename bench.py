@@ -458,8 +458,8 @@ def run_b200(args):
                          "peak_source": peak_src, "algorithmic_bytes": bwd_bytes, "ms": bwd_ms,
                          "nominal_peak_gbs": 8000.0, "frac_of_nominal": ach_bwd / 8000.0,
                          "note": "not HBM-bound at d_state=16: 66 warp-instructions per 32 lane-steps against 24.8 KB per "
-                                 "token; ncu shows issue slots 73 % busy on average over all SMs (about 80 % on the 108 SMs "
-                                 "that hold two of the 256 CTAs), the FP32 pipe 51 %, the shared-memory pipe 56 %"},
+                                 "token; ncu shows issue slots 71 % busy on average over all SMs (75 % on the busiest scheduler; the "
+                                 "256 sequences run as 16 segments each, handed from CTA to CTA), the FP32 pipe 49 %"},
             "roofline_fwd": {"bound": "hbm", "kernel": "kla_fwd_kernel", "achieved": ach_fwd, "peak": peak,
                              "unit": "GB/s", "frac": ach_fwd / peak, "traffic": NCU_TRAFFIC["kla_fwd_kernel"] * B / 8 if "kla_fwd_kernel" in NCU_TRAFFIC else None,
                              "algorithmic_bytes": fwd_bytes, "ms": fwd_ms},
