@@ -124,7 +124,9 @@ constexpr int kBwdThreads = 384;  // reverse, replay and helper groups of four w
 
 // LOGV: lambda_v arrives as a log-variance (BwdParams::lv_log_sigma). A separate instantiation, so that the plain
 // kernel does not carry that code.
-template <typename T, typename TO, int SPT, int LPC, int CH, int NW, int NH, int TT, bool PRIOR, bool LOGV>
+// SEG: sequences cut into segments (BwdParams::seg, SegCtl), also a separate instantiation: with that code in it the
+// unsegmented kernel ran 8 % slower at one CTA per SM.
+template <typename T, typename TO, int SPT, int LPC, int CH, int NW, int NH, int TT, bool PRIOR, bool LOGV, bool SEG>
 __global__ void __launch_bounds__(kBwdThreads, 2) kla_bwd_kernel(const __grid_constant__ BwdParams prm) {
     using Sh = ScanShape<SPT, LPC, CH, NW, NH, TT>;
     using Sm = BwdSmem<T, TO, SPT, LPC, CH, NW, NH, TT>;
@@ -164,15 +166,18 @@ __global__ void __launch_bounds__(kBwdThreads, 2) kla_bwd_kernel(const __grid_co
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // This CTA's sequence and, when sequences are cut into segments, its stretch of it: t_off steps in, L steps long
     // (tiles and steps below count from the start of the stretch; segments are processed last-first).
-    const SegUnit unit = seg_assign(prm.seg, true);
-    if (unit.seg < 0) return;
+    SegUnit unit{(int)blockIdx.x, (int)blockIdx.y, 0, 0};
+    if constexpr (SEG) {
+        unit = seg_assign(prm.seg, true);
+        if (unit.seg < 0) return;
+    }
     const int b = unit.b;
     const int m_cta = unit.bx * MC;
     const int M = prm.M, S = prm.S;
-    const int t_off = unit.seg * prm.seg.seg_len, tile_off = t_off / TT;
-    const int L = prm.seg.nseg > 1 ? min(prm.seg.seg_len, prm.L - t_off) : prm.L;
-    const int NT = (L + TT - 1) / TT;
-    const bool first_seg = unit.seg == 0, last_seg = unit.seg == prm.seg.nseg - 1;
+    const int t_off = SEG ? unit.seg * prm.seg.seg_len : 0, tile_off = t_off / TT;
+    const int L = SEG ? min(prm.seg.seg_len, prm.L - t_off) : prm.L;
+    const int NT = SEG ? (L + TT - 1) / TT : prm.NT;
+    const bool first_seg = !SEG || unit.seg == 0, last_seg = !SEG || unit.seg == prm.seg.nseg - 1;
     const bool has_dyv = prm.dyv.ptr != nullptr;
 
     if (tid == 0) {

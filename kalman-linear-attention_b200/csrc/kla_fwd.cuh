@@ -84,7 +84,9 @@ struct FwdSmem {
 
 // EPI: the forward-only layer epilogue (FwdParams::epilogue). A separate instantiation, so that the plain
 // kernel does not carry that code: even untaken it costs the plain path a few per cent.
-template <typename T, typename TO, int SPT, int LPC, int CH, int NW, int NH, int TT, bool PRIOR, bool EPI>
+// SEG: sequences cut into segments (FwdParams::seg, SegCtl). Again a separate instantiation: the unsegmented kernel
+// then carries none of that code (with it, one CTA per SM ran 3 % slower).
+template <typename T, typename TO, int SPT, int LPC, int CH, int NW, int NH, int TT, bool PRIOR, bool EPI, bool SEG>
 __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_constant__ FwdParams prm) {
     using Sh = ScanShape<SPT, LPC, CH, NW, NH, TT>;
     using Sm = FwdSmem<T, SPT, LPC, CH, NW, NH, TT>;
@@ -129,15 +131,18 @@ __global__ void __launch_bounds__((NW + NH) * 32) kla_fwd_kernel(const __grid_co
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // This CTA's sequence and, when sequences are cut into segments, its stretch of it: t_off steps in, L steps long
     // (everything below counts tiles and steps from the start of the stretch).
-    const SegUnit unit = seg_assign(prm.seg, false);
-    if (unit.seg < 0) return;
+    SegUnit unit{(int)blockIdx.x, (int)blockIdx.y, 0, 0};
+    if constexpr (SEG) {
+        unit = seg_assign(prm.seg, false);
+        if (unit.seg < 0) return;
+    }
     const int b = unit.b;
     const int m_cta = unit.bx * MC;
     const int M = prm.M, S = prm.S;
-    const int t_off = unit.seg * prm.seg.seg_len;
-    const int L = prm.seg.nseg > 1 ? min(prm.seg.seg_len, prm.L - t_off) : prm.L;
-    const int NT = (L + TT - 1) / TT;
-    const bool first_seg = unit.seg == 0, last_seg = unit.seg == prm.seg.nseg - 1;
+    const int t_off = SEG ? unit.seg * prm.seg.seg_len : 0;
+    const int L = SEG ? min(prm.seg.seg_len, prm.L - t_off) : prm.L;
+    const int NT = SEG ? (L + TT - 1) / TT : prm.NT;
+    const bool first_seg = !SEG || unit.seg == 0, last_seg = !SEG || unit.seg == prm.seg.nseg - 1;
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {

@@ -12,8 +12,11 @@ template <typename T, typename TO, int LPC, bool PRIOR>
 cudaError_t launch_fwd(const FwdParams &prm, cudaStream_t st) {
     using Sh = ScanShape<kSPT, LPC, kCH, kNW, kNH, kTT>;
     using Sm = FwdSmem<T, kSPT, LPC, kCH, kNW, kNH, kTT>;
-    auto kern = prm.epilogue ? kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, true>
-                             : kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, false>;
+    const bool seg = prm.seg.nseg > 1;
+    auto kern = prm.epilogue ? (seg ? kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, true, true>
+                                    : kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, true, false>)
+                             : (seg ? kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, false, true>
+                                    : kla_fwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kTT, PRIOR, false, false>);
     const size_t smem = prm.epilogue ? Sm::kTotal : Sm::kPlain;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sm::kTotal);
     if (e != cudaSuccess) return e;
@@ -26,13 +29,16 @@ template <typename T, typename TO, int LPC, bool PRIOR>
 cudaError_t launch_bwd(const BwdParams &prm, cudaStream_t st) {
     using Sh = ScanShape<kSPT, LPC, kCH, kNW, kNH, kBwdTT>;
     using Sm = BwdSmem<T, TO, kSPT, LPC, kCH, kNW, kNH, kBwdTT>;
-    auto kern = prm.lv_log_sigma ? kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kBwdTT, PRIOR, true>
-                                 : kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kBwdTT, PRIOR, false>;
+    const bool seg = prm.seg.nseg > 1;
+    auto kern = prm.lv_log_sigma ? (seg ? kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kBwdTT, PRIOR, true, true>
+                                        : kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kBwdTT, PRIOR, true, false>)
+                                 : (seg ? kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kBwdTT, PRIOR, false, true>
+                                        : kla_bwd_kernel<T, TO, kSPT, LPC, kCH, kNW, kNH, kBwdTT, PRIOR, false, false>);
     // The kernel's warp groups re-divide the registers the CTA was launched with; if the compiled kernel holds
     // fewer than the division assumes, the group that grows would wait for registers that never come. Checked
     // once per instantiation, before anything is launched.
-    static int regs_ok[2] = {-1, -1};
-    int &ok = regs_ok[prm.lv_log_sigma ? 1 : 0];
+    static int regs_ok[4] = {-1, -1, -1, -1};
+    int &ok = regs_ok[(prm.lv_log_sigma ? 1 : 0) + (seg ? 2 : 0)];
     if (ok < 0) {
         cudaFuncAttributes attr;
         cudaError_t e = cudaFuncGetAttributes(&attr, kern);
