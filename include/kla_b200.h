@@ -113,6 +113,10 @@ typedef struct kla_b200_fwd_args {
  * segment to the next: 28 bytes per (b, m, s) plus 8 per (b, m)). */
 size_t kla_b200_ckpt_bytes(int64_t B, int64_t L, int64_t M, int64_t S);
 size_t kla_b200_segment_scratch_bytes(int64_t B, int64_t M, int64_t S);
+/* The segment plan the scan kernels use for `sequences` = B * ceil(M / channels per CTA) sequences of L steps on a
+ * device with `sms` SMs: returns the segments per sequence (1 = unsegmented) and their length in *seg_len.
+ * forced: -1 = the library's policy, 0 = off, N > 1 = N segments (what KLA_B200_SEGMENTS sets). No device call. */
+int kla_b200_plan_segments(int64_t sequences, int64_t L, int backward, int sms, int forced, int *seg_len);
 int64_t kla_b200_ckpt_interval(void);
 
 int kla_b200_scan_fwd(const kla_b200_fwd_args *args, void *stream);

@@ -18,6 +18,7 @@ STATIC_CKPT_BYTES = 32 << 20
 SYMBOLS = (
     "kla_b200_ckpt_bytes",
     "kla_b200_segment_scratch_bytes",
+    "kla_b200_plan_segments",
     "kla_b200_ckpt_interval",
     "kla_b200_scan_fwd",
     "kla_b200_scan_fwd_static",
@@ -193,6 +194,8 @@ def load() -> ctypes.CDLL:
     lib.kla_b200_ckpt_bytes.argtypes = [c_int64] * 4
     lib.kla_b200_segment_scratch_bytes.restype = c_size_t
     lib.kla_b200_segment_scratch_bytes.argtypes = [c_int64] * 3
+    lib.kla_b200_plan_segments.restype = c_int
+    lib.kla_b200_plan_segments.argtypes = [c_int64, c_int64, c_int, c_int, c_int, POINTER(c_int)]
     lib.kla_b200_ckpt_interval.restype = c_int64
     lib.kla_b200_scan_fwd.restype = c_int
     lib.kla_b200_scan_fwd.argtypes = [POINTER(FwdArgs), c_void_p]

@@ -182,21 +182,17 @@ size_t ckpt_part_bytes(int64_t B, int64_t L, int64_t M, int64_t S) {
 // fewer sequences than half its slots the waiting CTAs spread the running ones unevenly over the SMs. So: the
 // backward whenever there are more sequences than SMs (16 segments up to two per SM, else 8), the forward from
 // two sequences per SM on. KLA_B200_SEGMENTS=0 switches segments off, =N asks for N in both kernels.
-int plan_segments(int64_t ctas, int64_t L, bool backward, int *seg_len) {
-    const char *env = getenv("KLA_B200_SEGMENTS");  // read per launch: the tests switch it within one process
-    const int forced = env != nullptr ? atoi(env) : -1;
+// forced: -1 = the policy above, 0 / 1 = off, N = N segments. sms: SMs of the device.
+int plan_segments_for(int64_t ctas, int64_t L, bool backward, int sms, int forced, int *seg_len) {
     *seg_len = (int)L;
-    if (forced == 0 || forced == 1) return 1;
+    if (forced == 0 || forced == 1 || L <= 0) return 1;
     int want = 8;
     int64_t min_len = 256;  // shorter segments cost more in hand-overs than they even out (chunks of 256 steps: no gain)
     if (forced > 1) {
         want = forced;
         min_len = kTT;
     } else {
-        int dev = 0, sms = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-            return 1;
-        if (ctas <= (backward ? sms : 2 * sms)) return 1;
+        if (sms <= 0 || ctas <= (backward ? sms : 2 * sms)) return 1;
         if (backward && ctas <= 2 * sms) want = 16;
     }
     int64_t len = (L + want - 1) / want;
@@ -206,6 +202,16 @@ int plan_segments(int64_t ctas, int64_t L, bool backward, int *seg_len) {
     if (n < 2 || n > 65535) return 1;
     *seg_len = (int)len;
     return (int)n;
+}
+
+int plan_segments(int64_t ctas, int64_t L, bool backward, int *seg_len) {
+    const char *env = getenv("KLA_B200_SEGMENTS");  // read per launch: the tests switch it within one process
+    const int forced = env != nullptr ? atoi(env) : -1;
+    int dev = 0, sms = 0;
+    if (forced < 0 && (cudaGetDevice(&dev) != cudaSuccess ||
+                       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess))
+        sms = 0;
+    return plan_segments_for(ctas, L, backward, sms, forced, seg_len);
 }
 
 // Fill prm.seg for one direction and clear its ticket and done words. scratch: the bytes behind the checkpoints.
@@ -398,6 +404,13 @@ size_t kla_b200_ckpt_bytes(int64_t B, int64_t L, int64_t M, int64_t S) {
     SegScratch sc;
     if (ck == SIZE_MAX || !seg_scratch(B, M, S, &sc) || ck > SIZE_MAX - sc.total) return SIZE_MAX;
     return ck + sc.total;
+}
+
+int kla_b200_plan_segments(int64_t sequences, int64_t L, int backward, int sms, int forced, int *seg_len) {
+    int len = 0;
+    const int n = plan_segments_for(sequences, L, backward != 0, sms, forced, &len);
+    if (seg_len != nullptr) *seg_len = len;
+    return n;
 }
 
 size_t kla_b200_segment_scratch_bytes(int64_t B, int64_t M, int64_t S) {

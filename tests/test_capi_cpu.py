@@ -159,3 +159,25 @@ def test_missing_library_fails_loudly(L, monkeypatch):
     monkeypatch.setattr(L, "LIB_PATH", "/nonexistent/libkla_b200.so")
     with pytest.raises(L.LibraryMissing, match="no CPU or Triton fallback"):
         L.load()
+
+
+def test_segment_plan(L):
+    """Host logic of the segmented kernels: when sequences are cut, into how many segments of what length."""
+    lib = L.load()
+
+    def plan(seqs, steps, backward, sms=148, forced=-1):
+        n = ctypes.c_int(0)
+        return lib.kla_b200_plan_segments(seqs, steps, int(backward), sms, forced, ctypes.byref(n)), n.value
+
+    assert plan(128, 4096, True) == (1, 4096)            # no more sequences than SMs: every CTA has an SM to itself
+    assert plan(256, 4096, True) == (16, 256)            # up to two per SM: the backward in 16 segments
+    assert plan(256, 4096, False) == (1, 4096)           # the forward only from two sequences per SM on
+    assert plan(320, 4096, True) == (8, 512) and plan(320, 4096, False) == (8, 512)
+    assert plan(768, 2048, True) == (8, 256)
+    assert plan(512, 256, True) == (1, 256)              # too short to cut (segments of at least 256 steps)
+    assert plan(512, 600, True) == (3, 256)              # ragged last segment: 256 + 256 + 88
+    assert plan(320, 4096, True, forced=0) == (1, 4096)
+    assert plan(4, 100, True, forced=4) == (4, 32)       # forced: whole tiles of 16 steps
+    assert plan(4, 16, True, forced=4) == (1, 16)
+    n, length = plan(320, 1 << 20, True)
+    assert n == 8 and length % 16 == 0 and n * length >= 1 << 20
