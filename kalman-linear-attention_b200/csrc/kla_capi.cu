@@ -722,6 +722,7 @@ int kla_b200_conv_seq(const kla_b200_conv_seq_args *a, void *stream) {
     } while (0)
     if (a->dtype == KLA_B200_F32) KLA_CONV_LAUNCH(kla_conv_seq_kernel, float);
     else KLA_CONV_LAUNCH(kla_conv_seq_kernel, __nv_bfloat16);
+#undef KLA_CONV_LAUNCH
     g_launches++;
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
@@ -756,6 +757,7 @@ int kla_b200_conv_seq_bwd(const kla_b200_conv_seq_bwd_args *a, void *stream) {
     } while (0)
     if (a->dtype == KLA_B200_F32) KLA_CONV_BWD_LAUNCH(float);
     else KLA_CONV_BWD_LAUNCH(__nv_bfloat16);
+#undef KLA_CONV_BWD_LAUNCH
     g_launches++;
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? KLA_B200_OK : cuda_fail(e);
