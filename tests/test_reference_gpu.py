@@ -385,11 +385,23 @@ def test_prefill_then_decode_bf16_equals_one_shot_scan(kla):
 
 # ------------------------------------------------------------ SequenceModel training step
 
-def test_sequence_model_training_step_matches_torch_backend(kla):
+@pytest.mark.parametrize("fused", [False, True])
+def test_sequence_model_training_step_matches_torch_backend(kla, fused):
     """SequenceModel(ModelConfig(vocab 50304, d_model 768, 12 layers), KLAConfig(d_state=16)) on a short batch:
-    loss and every parameter gradient with backend='b200' against backend='torch' (both on the GPU, float32)."""
+    loss and every parameter gradient with backend='b200' against backend='torch' (both on the GPU, float32);
+    once with the reference's own layer forward, once with the layers routed through layer.fused_forward."""
     from kla import KLAConfig, ModelConfig, SequenceModel
 
+    layer = importlib.import_module("kalman-linear-attention_b200.layer")
+    if fused:
+        layer.enable()
+    try:
+        _model_step_parity(KLAConfig, ModelConfig, SequenceModel)
+    finally:
+        layer.disable()
+
+
+def _model_step_parity(KLAConfig, ModelConfig, SequenceModel):
     torch.manual_seed(0)
     mc = ModelConfig(vocab_size=50304, d_model=768, n_layers=12)
     ref = SequenceModel(mc, KLAConfig(d_state=16, backend="torch")).cuda()
