@@ -1175,6 +1175,51 @@ def run_epilogue(args):
     }), flush=True)
 
 
+def run_conv(args):
+    """Secondary line: the layer's causal depthwise convolution with its activation, forward + backward, at the
+    training step's shape (B=16, L=2048, D=1536, 4 taps, silu, bfloat16) through ``causal_conv_b200`` beside the same
+    operation as the reference module issues it (transpose, cat with the carried window, conv1d, activation, transpose
+    back; src/kla/layers/common.py:87-96) with torch autograd's backward."""
+    import torch
+    import torch.nn.functional as F
+    import kla_b200
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, L, D, K = (args.batch or 16), 2048, 1536, 4
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(B, L, D, generator=g).to(dev, torch.bfloat16)
+    w = (0.5 * torch.randn(D, 1, K, generator=g)).to(dev)
+    bias = torch.randn(D, generator=g).to(dev)
+    dz = torch.randn(B, L, D, generator=g).to(dev, torch.bfloat16)
+
+    def ours():
+        ins = [t.detach().requires_grad_(True) for t in (x, w, bias)]
+        z, _ = kla_b200.layer.causal_conv_b200(*ins, None, "silu")
+        return torch.autograd.grad(z, ins, dz)
+
+    def module_math():
+        ins = [t.detach().requires_grad_(True) for t in (x, w, bias)]
+        x_t = ins[0].transpose(1, 2)
+        x_pad = torch.cat((torch.zeros(B, D, K - 1, device=dev, dtype=x_t.dtype), x_t), dim=-1)
+        z = F.silu(F.conv1d(x_pad, ins[1].to(x_t.dtype), ins[2].to(x_t.dtype), groups=D)).transpose(1, 2)
+        return torch.autograd.grad(z, ins, dz)
+
+    go, gm = ours(), module_math()
+    diff = max(float((a_.float() - b_.float()).abs().max() / (b_.float().abs().max() + 1e-12)) for a_, b_ in zip(go, gm))
+    sync = torch.cuda.synchronize
+    ms_o = _event_time(ours, args.steps, max(args.warmup, 3), sync)
+    ms_m = _event_time(module_math, args.steps, max(args.warmup, 3), sync)
+    print(json.dumps({
+        "metric": "causal depthwise conv + activation fwd+bwd, tokens/s", "value": B * L / (ms_o * 1e-3), "unit": UNIT,
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_o, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"CausalConv1d forward + backward, B={B} L={L} D={D} K={K}, silu, [B, L, D] layout",
+                   "ms_b200": ms_o, "ms_torch_module_math": ms_m, "speedup": ms_m / ms_o,
+                   "max_rel_diff_of_gradients_bf16": diff},
+    }), flush=True)
+
+
 def run_generate(args):
     """Secondary line: prompt prefill and token-by-token decode of a whole model -- the reference's
     ``SequenceModel(ModelConfig(vocab 50304, d_model 768, 12 layers), KLAConfig(d_state=16))``, bf16, batch 32, a prompt of
@@ -1485,7 +1530,7 @@ def main():
     ap.add_argument("--fused-layer", action="store_true",
                     help="train_step: route KLALayer.forward through the package's fused layer forward")
     ap.add_argument("--backend", default="", help="reference_gpu child / train_step: the scan backend to run")
-    ap.add_argument("--workload", default="raw", choices=["raw", "seqshard", "decode", "rawpair", "decode_layer", "prologue", "epilogue", "inference",
+    ap.add_argument("--workload", default="raw", choices=["raw", "seqshard", "decode", "rawpair", "decode_layer", "prologue", "epilogue", "inference", "conv",
                                                           "reference_gpu", "_reference_gpu_child", "train_step", "generate"],
                     help="raw = the headline raw-op workload (default); seqshard = the long-sequence, "
                          "time-sharded workload (secondary line)")
@@ -1514,6 +1559,8 @@ def main():
         return run_epilogue(args)
     if args.workload == "inference" and args.impl != "reference":
         return run_inference(args)
+    if args.workload == "conv" and args.impl != "reference":
+        return run_conv(args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -16,6 +16,8 @@
 // the carried window (`state`, or zeros).
 #pragma once
 
+#include <type_traits>
+
 #include "kla_decode.cuh"
 #include "kla_epilogue.cuh"
 
@@ -78,23 +80,26 @@ __global__ void __launch_bounds__(128) kla_conv_seq_bwd_kernel(const ConvSeqBwdP
     }
     const int t1 = min(L, t0 + kConvBwdChunk);
     const int tend = t1 + K - 1;  // dx[t1 - 1] needs dpre up to t1 + K - 2
-    for (int tb = t0; tb < tend; tb += kConvBlock) {
+    // One block of kConvBlock steps. FULL: every step lies inside the chunk and, from the second block on, every
+    // dx it completes too, so none of the range checks is needed (all blocks but the first and the last ones).
+    auto block = [&](int tb, auto full) {
+        constexpr bool FULL = decltype(full)::value;
         float xin[kConvBlock][VEC], gin[kConvBlock][VEC];
 #pragma unroll
         for (int u = 0; u < kConvBlock; ++u)
-            if (tb + u < tend && tb + u < L) {
+            if (FULL || (tb + u < tend && tb + u < L)) {
                 conv_load<T, VEC>(xb + (long long)(tb + u) * prm.x.st, xin[u]);
                 conv_load<T, VEC>(gb + (long long)(tb + u) * prm.dz.st, gin[u]);
             }
 #pragma unroll
         for (int u = 0; u < kConvBlock; ++u) {
             const int t = tb + u;
-            if (t < tend) {
+            if (FULL || t < tend) {
                 float out[VEC];
 #pragma unroll
                 for (int e = 0; e < VEC; ++e) {
                     float dpre = 0.0f;
-                    if (t < L) {
+                    if (FULL || t < L) {
 #pragma unroll
                         for (int i = 0; i < MAXT - 1; ++i) xw[i][e] = i >= lead ? xw[i + 1][e] : 0.0f;
                         xw[MAXT - 1][e] = xin[u][e];
@@ -102,7 +107,7 @@ __global__ void __launch_bounds__(128) kla_conv_seq_bwd_kernel(const ConvSeqBwdP
 #pragma unroll
                         for (int i = 0; i < MAXT; ++i) pre = fmaf(wr[i][e], xw[i][e], pre);
                         dpre = gin[u][e] * activate_slope_fast(pre, prm.act);
-                        if (t < t1) {  // the sums over t belong to the chunk that owns t
+                        if (FULL || t < t1) {  // the sums over t belong to the chunk that owns t
                             accb[e] += dpre;
 #pragma unroll
                             for (int i = 0; i < MAXT; ++i) accw[i][e] = fmaf(dpre, xw[i][e], accw[i][e]);
@@ -116,9 +121,13 @@ __global__ void __launch_bounds__(128) kla_conv_seq_bwd_kernel(const ConvSeqBwdP
                     for (int jj = 0; jj < MAXT; ++jj) acc = fmaf(wl[jj][e], dwin[MAXT - 1 - jj][e], acc);
                     out[e] = acc;
                 }
-                if (t - (K - 1) >= t0) conv_store<T, VEC>(ob + (long long)(t - (K - 1)) * prm.dx.st, out);
+                if (FULL || t - (K - 1) >= t0) conv_store<T, VEC>(ob + (long long)(t - (K - 1)) * prm.dx.st, out);
             }
         }
+    };
+    for (int tb = t0; tb < tend; tb += kConvBlock) {
+        if (tb >= t0 + kConvMaxTaps && tb + kConvBlock <= t1) block(tb, std::true_type{});
+        else block(tb, std::false_type{});
     }
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
