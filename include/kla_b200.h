@@ -103,6 +103,10 @@ typedef struct kla_b200_fwd_args {
     int32_t lambda_skip_len;
     int32_t gate_activation;
     kla_b200_tensor3 y_raw, y_var_raw; /* out, or ptr NULL */
+    /* Optional, for a forward without checkpoints (ckpt == NULL): kla_b200_segment_scratch_bytes(B, M, S) bytes of
+     * working memory, with which this forward too can hand its sequences from CTA to CTA in segments; NULL: it runs
+     * unsegmented. Ignored when ckpt is given (the working memory then sits behind the checkpoints). */
+    void *work;
 } kla_b200_fwd_args;
 
 /* Bytes of the scratch the forward writes for the backward: the filter state

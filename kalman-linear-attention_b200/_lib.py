@@ -111,7 +111,7 @@ class FwdArgs(Structure):
         ("lambda_v_is_log_variance", c_int32), ("obs_var_min", c_float), ("obs_var_max", c_float),
         ("z", Tensor3), ("gate", Tensor3), ("lambda_skip", c_void_p),
         ("lambda_skip_len", c_int32), ("gate_activation", c_int32),
-        ("y_raw", Tensor3), ("y_var_raw", Tensor3),
+        ("y_raw", Tensor3), ("y_var_raw", Tensor3), ("work", c_void_p),
     ]
 
 

@@ -214,11 +214,13 @@ int plan_segments(int64_t ctas, int64_t L, bool backward, int *seg_len) {
     return plan_segments_for(ctas, L, backward, sms, forced, seg_len);
 }
 
-// Fill prm.seg for one direction and clear its ticket and done words. scratch: the bytes behind the checkpoints.
+// Fill prm.seg for one direction and clear its ticket and done words. The working memory is the bytes behind the
+// checkpoints, or, for a forward without checkpoints, the caller's `work` buffer of the same layout.
 template <typename Params>
-int seg_setup(Params &prm, void *ckpt, int64_t B, int64_t L, int64_t M, int64_t S, int lpc, bool backward, cudaStream_t st) {
+int seg_setup(Params &prm, void *ckpt, void *work, int64_t B, int64_t L, int64_t M, int64_t S, int lpc, bool backward,
+              cudaStream_t st) {
     prm.seg = SegCtl{1, (int)L, nullptr, nullptr, nullptr};
-    if (ckpt == nullptr || L <= 0) return KLA_B200_OK;
+    if ((ckpt == nullptr && work == nullptr) || L <= 0) return KLA_B200_OK;
     const int mc = scan_channels_per_cta(lpc);
     const int64_t ctas = ((M + mc - 1) / mc) * B;
     int seg_len = (int)L;
@@ -226,9 +228,9 @@ int seg_setup(Params &prm, void *ckpt, int64_t B, int64_t L, int64_t M, int64_t 
     if (nseg <= 1) return KLA_B200_OK;
     SegScratch sc;
     if (!seg_scratch(B, M, S, &sc)) return KLA_B200_OK;
-    const size_t base = ckpt_part_bytes(B, L, M, S);
+    const size_t base = ckpt != nullptr ? ckpt_part_bytes(B, L, M, S) : 0;
     if (base == SIZE_MAX) return KLA_B200_OK;
-    unsigned char *p = static_cast<unsigned char *>(ckpt) + base;
+    unsigned char *p = static_cast<unsigned char *>(ckpt != nullptr ? ckpt : work) + base;
     unsigned char *flags = p + (backward ? sc.flags : 0);
     const cudaError_t e = cudaMemsetAsync(flags, 0, sc.flags, st);
     if (e != cudaSuccess) return cuda_fail(e);
@@ -244,7 +246,7 @@ int seg_setup(Params &prm, void *ckpt, int64_t B, int64_t L, int64_t M, int64_t 
 template <typename T, typename TO, int LPC, bool PRIOR>
 int prep_fwd(FwdParams &prm, const kla_b200_fwd_args &a, cudaStream_t st) {
     const int mc = scan_channels_per_cta(LPC);
-    if (int rc = seg_setup(prm, a.ckpt, a.B, a.L, a.M, a.S, LPC, false, st)) return rc;
+    if (int rc = seg_setup(prm, a.ckpt, a.work, a.B, a.L, a.M, a.S, LPC, false, st)) return rc;
     prm.use_tma = !g_no_tma && make_tile_map<T>(&prm.tm_v, a.v, a.B, a.L, a.M, mc, kTT) &&
                   make_tile_map<T>(&prm.tm_lv, a.lambda_v, a.B, a.L, a.M, mc, kTT);
     if (prm.epilogue)  // z and gate tiles travel like v and lambda_v when they meet the tensor-map rules
@@ -258,7 +260,7 @@ int prep_fwd(FwdParams &prm, const kla_b200_fwd_args &a, cudaStream_t st) {
 template <typename T, typename TO, int LPC, bool PRIOR>
 int prep_bwd(BwdParams &prm, const kla_b200_bwd_args &a, cudaStream_t st) {
     const int mc = scan_channels_per_cta(LPC);
-    if (int rc = seg_setup(prm, const_cast<void *>(a.ckpt), a.B, a.L, a.M, a.S, LPC, true, st)) return rc;
+    if (int rc = seg_setup(prm, const_cast<void *>(a.ckpt), nullptr, a.B, a.L, a.M, a.S, LPC, true, st)) return rc;
     prm.use_tma = !g_no_tma && make_tile_map<T>(&prm.tm_v, a.v, a.B, a.L, a.M, mc, kBwdTT) &&
                   make_tile_map<T>(&prm.tm_lv, a.lambda_v, a.B, a.L, a.M, mc, kBwdTT) &&
                   make_tile_map<TO>(&prm.tm_dy, a.dy, a.B, a.L, a.M, mc, kBwdTT) &&

@@ -134,6 +134,21 @@ def _epilogue_fields(epilogue):
     return out
 
 
+_SM_COUNT: dict = {}
+
+
+def _forward_segments(lib, dev: torch.device, B: int, L: int, M: int, S: int) -> bool:
+    """Whether the forward kernel would cut a problem of this shape into segments (``kla_b200_plan_segments``)."""
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    lpc = 1
+    while 4 * lpc < S:
+        lpc *= 2
+    per_cta = 128 // lpc  # channels per CTA of the scan kernels
+    return lib.kla_b200_plan_segments(B * ((M + per_cta - 1) // per_cta), L, 0, _SM_COUNT[idx], -1, None) > 1
+
+
 def _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype, need_ckpt: bool, sensors=None,
                 epilogue=None, raw=None):
     """Allocate outputs (and the checkpoint scratch when a backward will follow)
@@ -146,16 +161,20 @@ def _launch_fwd(v, lambda_v, k, q, a, p, lam0, eta0, prior: bool, out_dtype, nee
     y_var = torch.empty((B, L, M), device=dev, dtype=out_dtype)
     lam_fin = torch.empty((B, M, S), device=dev, dtype=torch.float32)
     eta_fin = torch.empty((B, M, S), device=dev, dtype=torch.float32)
-    ckpt = None
+    ckpt = work = None
     if need_ckpt and L > 0:
         ckpt = torch.empty(lib.kla_b200_ckpt_bytes(B, L, M, S), device=dev, dtype=torch.uint8)
+    elif _forward_segments(lib, dev, B, L, M, S):
+        # no backward will follow, but the sequences are many enough for the kernel to hand them from CTA to CTA in
+        # segments: that needs a little working memory
+        work = torch.empty(lib.kla_b200_segment_scratch_bytes(B, M, S), device=dev, dtype=torch.uint8)
     args = FwdArgs(
         B=B, L=L, M=M, S=S, in_dtype=_dt(v.dtype), out_dtype=_dt(out_dtype),
         decode_from_prior=int(prior),
         v=_t3(v), lambda_v=_t3(lambda_v), k=_t3(k), q=_t3(q),
         a=_ptr(a), p=_ptr(p), lam0=_ptr(lam0), eta0=_ptr(eta0),
         y=_t3(y), y_var=_t3(y_var), lam_fin=_ptr(lam_fin), eta_fin=_ptr(eta_fin),
-        ckpt=_ptr(ckpt), **_sensor_fields(sensors), **_epilogue_fields(epilogue),
+        ckpt=_ptr(ckpt), work=_ptr(work), **_sensor_fields(sensors), **_epilogue_fields(epilogue),
         **({} if raw is None else dict(y_raw=_t3(raw[0]), y_var_raw=_t3(raw[1]))),
     )
     with _on(dev):

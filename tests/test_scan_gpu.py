@@ -582,3 +582,29 @@ def test_segmented_kernels_equal_the_unsegmented_ones(kb, monkeypatch, B, L, M, 
             assert ((x.float() - r.float()).abs().max() / (r.float().abs().max() + 1e-30)).item() < 1e-5, n
         else:
             assert torch.equal(x, r), n
+
+
+@pytest.mark.gpu
+def test_forward_without_checkpoints_is_segmented_too(kb, monkeypatch):
+    """Under no_grad nothing is checkpointed; with many sequences the forward still runs in segments, on a small
+    working buffer of its own, and gives what the unsegmented kernel gives."""
+    F = torch.nn.functional
+    g = torch.Generator().manual_seed(11)
+    B, L, M, S = 10, 1024, 1024, 16
+    v = torch.randn(B, L, M, generator=g).cuda()
+    lv = (1 / F.softplus(torch.randn(B, L, M, generator=g))).cuda()
+    k = F.normalize(torch.randn(B, L, S, generator=g), dim=-1).cuda()
+    q = F.normalize(torch.randn(B, L, S, generator=g), dim=-1).cuda()
+    a, p = torch.sigmoid(torch.randn(M, S, generator=g)).cuda(), F.softplus(torch.randn(M, S, generator=g)).cuda()
+    ops = __import__("importlib").import_module("kalman-linear-attention_b200.ops")
+    lib = __import__("importlib").import_module("kalman-linear-attention_b200._lib")
+    assert ops._forward_segments(lib.load(), v.device, B, L, M, S)
+    monkeypatch.delenv("KLA_B200_SEGMENTS", raising=False)
+    with torch.no_grad():
+        y1, yv1, st1 = kb.kla_scan_b200(v, lv, k, q, a, p, time_chunks=1)
+    monkeypatch.setenv("KLA_B200_SEGMENTS", "0")
+    with torch.no_grad():
+        y0, yv0, st0 = kb.kla_scan_b200(v, lv, k, q, a, p, time_chunks=1)
+    torch.cuda.synchronize()
+    lib.check_status()
+    assert torch.equal(y1, y0) and torch.equal(yv1, yv0) and torch.equal(st1.lam, st0.lam) and torch.equal(st1.eta, st0.eta)
