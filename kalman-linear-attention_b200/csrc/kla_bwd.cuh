@@ -36,7 +36,11 @@
 // choose from without doubling the registers: the replay needs half of what
 // the reverse walk needs. All hand-overs go through mbarriers.
 //
-// Measured on B200 at B=8, T=4096, M=1024, S=16 (1.49 ms): the reverse walk alone takes 1.15 ms, the replay alone
+// With SEG a sequence is walked by several CTAs, last stretch first (SegCtl, kla_common.cuh): a CTA takes the two
+// carries and the running sums for da, dp from the CTA that walked the stretch after its own, and hands its own
+// on; the state its walk starts from needs no hand-over, the replay group computes it from the checkpoints.
+//
+// Measured on B200 at B=8, T=4096, M=1024, S=16 (1.49 ms unsegmented, 1.42 ms in 16 segments): the reverse walk alone takes 1.15 ms, the replay alone
 // 0.53 ms, the sums 0.12 ms; side by side they overlap only in part. Variants that were measured and are not kept:
 // the trajectory through tensor memory (tcgen05.st / tcgen05.ld, a third less shared-memory traffic: 1.56 ms),
 // the reverse walk on paired fp32 instructions (a third fewer instructions: 1.68 ms), other register splits between

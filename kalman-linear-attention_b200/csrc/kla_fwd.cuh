@@ -22,6 +22,9 @@
 //                  read-outs of every (step, channel) and store y, y_var.
 // Stages are handed over with mbarriers, so the compute warps see neither
 // global-memory latency nor a CTA-wide barrier inside the time loop.
+// With SEG a sequence is walked by several CTAs one after the other (SegCtl,
+// kla_common.cuh); the filter state travels between them as it is in registers,
+// so the results are those of one CTA walking the whole sequence.
 #pragma once
 
 #include "kla_common.cuh"
