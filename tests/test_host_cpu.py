@@ -190,6 +190,44 @@ def test_register_into_reference_dispatch(oracle_launches):
 
 
 @needs_ref
+def test_fused_layer_route_on_cpu(oracle_launches):
+    """layer.fused_forward with oracle-backed launches: a layer without convolution, gate and skip path (the parts
+    that need the GPU kernels) gives the reference layer's output and parameter gradients; and with the route
+    enabled, CPU tensors still go to the reference method."""
+    sys.path.insert(0, REF_SRC)
+    try:
+        import kla
+
+        fused = importlib.import_module("kalman-linear-attention_b200.layer")
+        cfg = dict(d_state=8, use_conv=False, use_gating=False, use_lambda_skip=False, obs_var_max=2.0)
+        torch.manual_seed(0)
+        ref = kla.KLALayer(32, kla.KLAConfig(backend="torch", **cfg))
+        dut = kla.KLALayer(32, kla.KLAConfig(backend="b200", **cfg))
+        dut.load_state_dict(ref.state_dict())
+        x = torch.randn(2, 20, 32)
+        y_ref = ref(x)
+        y_ref.square().sum().backward()
+        y, st = fused.fused_forward(dut, x, return_state=True)
+        y.square().sum().backward()
+        torch.testing.assert_close(y, y_ref, atol=5e-4, rtol=5e-4)
+        assert st.conv is None and st.ssm.lam.shape == (2, 64, 8)
+        grads = dict(dut.named_parameters())
+        for n, p in ref.named_parameters():
+            if p.grad is not None:
+                torch.testing.assert_close(grads[n].grad, p.grad, atol=2e-3, rtol=2e-3, msg=lambda m, n=n: f"{n}: {m}")
+        # enabled, but not applicable to CPU tensors: the reference method runs (and reaches the b200 callable)
+        kla_b200.register(fuse_layer=True)
+        try:
+            assert not fused._fusable(dut, x, None)
+            torch.testing.assert_close(dut(x), y.detach(), atol=1e-5, rtol=1e-5)
+        finally:
+            kla_b200.unregister()
+        assert kla.KLALayer.forward is fused._ORIG_FORWARD or fused._ORIG_FORWARD is None
+    finally:
+        sys.path.remove(REF_SRC)
+
+
+@needs_ref
 def test_cli_rows_for_the_reference_command_line(capsys):
     """`python -m kla --check-backends` with the b200 row added: listed, described, and reported
     unusable on a machine without a CUDA device (src/kla/__main__.py:104-150, :290-300)."""
